@@ -1,0 +1,72 @@
+// Launch interface of the persistent grouped-GEMM kernel (gemm_sm100.cu).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime_api.h>
+#include <cstdint>
+
+#include "bmoe_b200.h"
+
+namespace bmoe {
+
+// How a CTA obtains its next tile.
+enum SchedMode : uint32_t {
+  kSchedStatic = 0,  // tile = blockIdx.x + i * gridDim.x
+  kSchedQueue = 1,   // global atomic queue (chunked main part + claim-1 tail)
+  kSchedClc = 2,     // one CTA per tile, cluster-launch-control work stealing
+};
+
+// Where a bounded wait gave up (bmoe_device_report::code).
+enum DeviceSite : uint32_t {
+  kSiteNone = 0,
+  kSiteSchedSlot = 1,     // scheduler waiting for a free tile-info slot
+  kSiteSchedPace = 2,     // scheduler waiting for the producer to catch up
+  kSiteSchedClc = 3,      // scheduler waiting for a launch-control answer
+  kSiteProducerInfo = 4,  // producer waiting for tile info
+  kSiteProducerStage = 5, // producer waiting for a free smem stage
+  kSiteMmaInfo = 6,
+  kSiteMmaAccum = 7,      // MMA waiting for a drained accumulator
+  kSiteMmaStage = 8,      // MMA waiting for operand bytes
+  kSiteEpiInfo = 9,
+  kSiteEpiAccum = 10,     // epilogue waiting for a finished accumulator
+};
+
+// Device-side error record; zero-initialised by the host.
+struct DeviceStatus {
+  uint32_t count;  // number of reports (first one owns the fields below)
+  uint32_t code;
+  uint32_t cta;
+  uint32_t role;
+  uint32_t tile;
+  uint32_t stage;
+  uint32_t aux;
+  uint32_t reserved;
+};
+
+struct GemmParams {
+  const CUtensorMap* tmap_a;  // [experts] A_e as {k, M_e}, box {64, 128}
+  const CUtensorMap* tmap_b;  // [experts] B_e as {k, n},   box {64, TILE_N}
+  const CUtensorMap* tmap_d;  // [experts] D_e as {n, M_e}, box {64, 32}
+  const bmoe_tile* tiles;     // device worklist
+  uint32_t tile_count;
+  uint32_t k_blocks;          // ceil(k / 64)
+  uint32_t sched_mode;        // SchedMode
+  uint32_t claim_size;        // queue: tiles per claim in the main part
+  uint32_t main_end;          // queue: [0, main_end) chunked, [main_end, T) singly
+  uint32_t lookahead;         // queue/clc: claims allowed ahead of the producer
+  uint32_t* queue;            // [0] main head, [1] tail head, [2] exited CTAs
+  DeviceStatus* status;
+  uint32_t* tile_visits;      // optional [tile_count]
+  uint32_t* cta_tiles;        // optional [gridDim.x]
+  uint64_t wait_budget_ns;
+};
+
+// Dynamic shared memory the kernel needs for a tile width (128 or 256).
+uint32_t gemm_smem_bytes(uint32_t tile_n);
+uint32_t gemm_stage_count(uint32_t tile_n);
+
+// Enqueues the kernel. grid = persistent CTAs (or the tile count for CLC).
+cudaError_t launch_grouped_gemm(const GemmParams& params, uint32_t tile_n,
+                                uint32_t grid, cudaStream_t stream);
+
+}  // namespace bmoe

@@ -1,0 +1,474 @@
+// C interface, device half: the grouped-GEMM plan (section 3 of bmoe_b200.h).
+//
+// initialize() does everything that can be prepared ahead of a launch: argument
+// checks, policy resolution, H2D copy of the counts, the on-device worklist
+// build, host encoding of one TMA descriptor triple per active expert, queue
+// and status words. run() is a single kernel launch. Behavioural contract
+// (status codes, null / zero handling, stream override) follows
+// baselines/cutlass/cutlass_baseline.cu:195-377 of the reference.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "blackwell_moe/dispatch.hpp"
+#include "bmoe_b200.h"
+#include "gemm_sm100.cuh"
+
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled is resolved through the runtime so the library has no
+// link-time dependency on libcuda.
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult query = cudaDriverEntryPointSymbolNotFound;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault,
+                                &query) != cudaSuccess ||
+        query != cudaDriverEntryPointSuccess) {
+      return nullptr;
+    }
+    return reinterpret_cast<EncodeTiledFn>(sym);
+  }();
+  return fn;
+}
+
+// Row-major BF16 matrix [rows, cols] viewed as a 2-D tensor {cols, rows} with a
+// SWIZZLE_128B box of 64 columns (128 bytes) x box_rows rows.
+bool encode_bf16_matrix(CUtensorMap* map, const void* base, uint64_t rows,
+                        uint64_t cols, uint32_t box_rows) {
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (encode == nullptr) return false;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 2};
+  const cuuint32_t box[2] = {64, box_rows};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  const CUresult rc = encode(
+      map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+      box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return rc == CUDA_SUCCESS;
+}
+
+// Grow-only device allocation.
+struct DeviceBlock {
+  void* ptr = nullptr;
+  size_t bytes = 0;
+  bool reserve(size_t want) {
+    if (want <= bytes) return true;
+    release();
+    if (cudaMalloc(&ptr, want) != cudaSuccess) {
+      ptr = nullptr;
+      return false;
+    }
+    bytes = want;
+    return true;
+  }
+  void release() {
+    if (ptr != nullptr) cudaFree(ptr);
+    ptr = nullptr;
+    bytes = 0;
+  }
+};
+
+bool misaligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; }
+
+}  // namespace
+
+struct bmoe_plan {
+  bool ready = false;
+  bmoe_plan_stats stats{};
+  cudaStream_t default_stream = nullptr;
+  cudaStream_t setup_stream = nullptr;
+  cudaStream_t last_stream = nullptr;
+  cudaEvent_t setup_done = nullptr;
+  int device = -1;
+
+  DeviceBlock counts;     // uint32 [experts]
+  DeviceBlock tmaps;      // CUtensorMap [3][experts]
+  DeviceBlock worklist;   // bmoe_tile [capacity]
+  DeviceBlock workspace;  // worklist builder arrays
+  DeviceBlock control;    // queue words (256 B) + DeviceStatus (256 B)
+
+  std::vector<CUtensorMap> host_maps;
+  std::vector<uint32_t> host_counts;
+
+  bmoe::GemmParams params{};
+  uint32_t grid = 0;
+  uint32_t tile_n = 0;
+
+  void release_all() {
+    counts.release();
+    tmaps.release();
+    worklist.release();
+    workspace.release();
+    control.release();
+    if (setup_done != nullptr) cudaEventDestroy(setup_done);
+    setup_done = nullptr;
+    ready = false;
+  }
+};
+
+namespace {
+
+struct Resolved {
+  uint32_t scheduler;      // policy after "auto" resolution
+  uint32_t order;          // bmoe_worklist_order
+  uint32_t sched_mode;     // bmoe::SchedMode
+  uint32_t claim_size;
+  uint32_t tail_tiles;
+  bool one_cta_per_tile;
+};
+
+Resolved resolve_policy(const bmoe_gemm_args& a, uint32_t tile_m, uint32_t tile_n,
+                        uint32_t cta_count) {
+  Resolved r{};
+  r.scheduler = a.scheduler;
+  r.order = BMOE_ORDER_EXPERT;
+  r.sched_mode = bmoe::kSchedStatic;
+  r.claim_size = 1;
+  r.tail_tiles = 0;
+  r.one_cta_per_tile = false;
+
+  uint32_t policy = a.scheduler;
+  uint32_t claim = a.claim_size == 0 ? 1 : a.claim_size;
+  uint32_t tail = a.hybrid_tail_tiles;
+  if (policy == BMOE_SCHED_AUTO) {
+    // Threshold dispatch on launch-level routing features.
+    namespace bm = blackwell_moe;
+    bm::GemmShape shape;
+    shape.n = a.n;
+    shape.k = a.k;
+    shape.tile_m = tile_m;
+    shape.tile_n = tile_n;
+    const std::vector<uint32_t> counts(a.tokens_per_expert,
+                                       a.tokens_per_expert + a.experts);
+    const bm::RoutingFeatures f = bm::routing_features(counts, shape, cta_count);
+    bm::DispatchSpec spec;
+    spec.cta_count = cta_count;
+    // The tail is two waves of the persistent grid, as in the reference spec
+    // (296 = 2 x 148).
+    spec.hybrid_tail_tiles = 2 * cta_count;
+    const bm::LaunchConfig cfg =
+        bm::resolve_launch_config(bm::select_launch_variant(f), spec);
+    policy = static_cast<uint32_t>(cfg.scheduler);
+    claim = cfg.claim_size;
+    tail = cfg.hybrid_tail_tiles;
+    r.one_cta_per_tile = cfg.one_cta_per_tile;
+    r.scheduler = policy;
+  }
+  switch (policy) {
+    case BMOE_SCHED_EXPERT_ORDER:
+    case BMOE_SCHED_COMPACTED:
+      break;
+    case BMOE_SCHED_STATIC_PERSISTENT:
+      r.order = BMOE_ORDER_SORTED_BY_WORK;
+      break;
+    case BMOE_SCHED_DYNAMIC_QUEUE:
+      r.sched_mode = bmoe::kSchedQueue;
+      r.claim_size = claim;
+      r.tail_tiles = tail;
+      break;
+    case BMOE_SCHED_CLC:
+      r.sched_mode = bmoe::kSchedClc;
+      r.one_cta_per_tile = true;
+      break;
+    default:
+      break;
+  }
+  return r;
+}
+
+}  // namespace
+
+extern "C" {
+
+bmoe_plan* bmoe_plan_create(void) { return new (std::nothrow) bmoe_plan; }
+
+void bmoe_plan_destroy(bmoe_plan* plan) {
+  if (plan == nullptr) return;
+  plan->release_all();
+  delete plan;
+}
+
+int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
+  if (plan == nullptr || args == nullptr) return BMOE_INVALID_ARGUMENT;
+  plan->ready = false;
+  plan->stats = bmoe_plan_stats{};
+  const bmoe_gemm_args& a = *args;
+
+  // ---- argument checks, in the reference's order ----
+  if (a.a == nullptr || a.b == nullptr || a.d == nullptr ||
+      a.tokens_per_expert == nullptr || a.experts == 0 || a.n == 0 || a.k == 0 ||
+      a.n % 8 != 0 || a.k % 8 != 0) {
+    return BMOE_INVALID_ARGUMENT;
+  }
+  if (a.data_type != 0) return BMOE_UNSUPPORTED_DATA_TYPE;
+  if (a.scheduler > BMOE_SCHED_CLC) return BMOE_UNSUPPORTED_SCHEDULER;
+  if (a.experts > BMOE_WORKLIST_MAX_EXPERTS) return BMOE_INVALID_ARGUMENT;
+  if (a.tile_n != 0 && a.tile_n != 128 && a.tile_n != 256) return BMOE_INVALID_ARGUMENT;
+  if (a.cta_group > 1) return BMOE_INVALID_ARGUMENT;
+
+  int device = 0, major = 0, minor = 0, sm_count = 0;
+  if (cudaGetDevice(&device) != cudaSuccess ||
+      cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess ||
+      cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, device) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) {
+    return BMOE_CUDA_ERROR;
+  }
+  // The kernels are built for sm_100a only (tcgen05, TMEM).
+  if (major != 10 || minor != 0) return BMOE_UNSUPPORTED_DEVICE;
+  if (plan->device != device) {
+    plan->release_all();
+    plan->device = device;
+  }
+
+  uint32_t active = 0;
+  for (uint32_t e = 0; e < a.experts; ++e) {
+    if (a.tokens_per_expert[e] == 0) continue;
+    if (a.a[e] == nullptr || a.b[e] == nullptr || a.d[e] == nullptr ||
+        misaligned16(a.a[e]) || misaligned16(a.b[e]) || misaligned16(a.d[e])) {
+      return BMOE_INVALID_ARGUMENT;
+    }
+    ++active;
+  }
+  plan->stats.active_experts = active;
+  plan->default_stream = static_cast<cudaStream_t>(a.stream);
+  plan->setup_stream = plan->default_stream;
+  plan->last_stream = plan->default_stream;
+  if (active == 0) {
+    // A routing result without active experts is valid and launches nothing.
+    plan->ready = true;
+    return BMOE_OK;
+  }
+
+  // ---- engine configuration ----
+  const uint32_t tile_m = 128;
+  const uint32_t tile_n = a.tile_n != 0 ? a.tile_n : (a.n <= 128 ? 128u : 256u);
+  const uint32_t raster =
+      a.raster_along_m < 0 ? BMOE_RASTER_M_FASTEST
+                           : (a.raster_along_m != 0 ? BMOE_RASTER_M_FASTEST
+                                                    : BMOE_RASTER_N_FASTEST);
+  const uint32_t cta_budget =
+      a.cta_count != 0 ? a.cta_count : static_cast<uint32_t>(sm_count);
+  const Resolved policy = resolve_policy(a, tile_m, tile_n, cta_budget);
+
+  const uint64_t tile_total =
+      bmoe_host_tile_count(a.tokens_per_expert, a.experts, a.n, tile_m, tile_n);
+  if (tile_total == 0 || tile_total > 0x7fffffffull) return BMOE_INVALID_ARGUMENT;
+  const uint32_t tiles = static_cast<uint32_t>(tile_total);
+
+  // ---- device storage ----
+  bmoe_worklist_layout layout;
+  if (bmoe_worklist_layout_for(a.experts, &layout) != BMOE_OK) {
+    return BMOE_INVALID_ARGUMENT;
+  }
+  const size_t map_bytes = sizeof(CUtensorMap) * 3 * static_cast<size_t>(a.experts);
+  if (!plan->counts.reserve(sizeof(uint32_t) * a.experts) ||
+      !plan->tmaps.reserve(map_bytes) ||
+      !plan->worklist.reserve(sizeof(bmoe_tile) * static_cast<size_t>(tiles)) ||
+      !plan->workspace.reserve(layout.bytes) || !plan->control.reserve(512)) {
+    return BMOE_CUDA_ERROR;
+  }
+  if (plan->setup_done == nullptr &&
+      cudaEventCreateWithFlags(&plan->setup_done, cudaEventDisableTiming) != cudaSuccess) {
+    return BMOE_CUDA_ERROR;
+  }
+  cudaStream_t stream = plan->setup_stream;
+
+  // ---- counts -> device, worklist built on the device ----
+  plan->host_counts.assign(a.tokens_per_expert, a.tokens_per_expert + a.experts);
+  if (cudaMemcpyAsync(plan->counts.ptr, plan->host_counts.data(),
+                      sizeof(uint32_t) * a.experts, cudaMemcpyHostToDevice,
+                      stream) != cudaSuccess) {
+    return BMOE_CUDA_ERROR;
+  }
+  bmoe_worklist_request request;
+  request.experts = a.experts;
+  request.n = a.n;
+  request.tile_m = tile_m;
+  request.tile_n = tile_n;
+  request.order = policy.order;
+  request.raster = raster;
+  int rc = bmoe_worklist_build(static_cast<const uint32_t*>(plan->counts.ptr), &request,
+                               static_cast<bmoe_tile*>(plan->worklist.ptr), tiles,
+                               plan->workspace.ptr, stream);
+  if (rc != BMOE_OK) return rc;
+
+  // ---- one TMA descriptor triple per active expert ----
+  plan->host_maps.assign(3 * static_cast<size_t>(a.experts), CUtensorMap{});
+  CUtensorMap* const maps_a = plan->host_maps.data();
+  CUtensorMap* const maps_b = maps_a + a.experts;
+  CUtensorMap* const maps_d = maps_b + a.experts;
+  for (uint32_t e = 0; e < a.experts; ++e) {
+    const uint64_t rows = a.tokens_per_expert[e];
+    if (rows == 0) continue;
+    if (!encode_bf16_matrix(&maps_a[e], a.a[e], rows, a.k, 128) ||
+        !encode_bf16_matrix(&maps_b[e], a.b[e], a.n, a.k, tile_n) ||
+        !encode_bf16_matrix(&maps_d[e], a.d[e], rows, a.n, 32)) {
+      return BMOE_CUDA_ERROR;
+    }
+  }
+  if (cudaMemcpyAsync(plan->tmaps.ptr, plan->host_maps.data(), map_bytes,
+                      cudaMemcpyHostToDevice, stream) != cudaSuccess) {
+    return BMOE_CUDA_ERROR;
+  }
+
+  // ---- queue and status words ----
+  const uint32_t tail = policy.tail_tiles < tiles ? policy.tail_tiles : tiles;
+  const uint32_t main_end = tiles - tail;
+  uint32_t control_init[128];
+  std::memset(control_init, 0, sizeof(control_init));
+  control_init[1] = main_end;  // tail counter starts where the main part ends
+  if (cudaMemcpyAsync(plan->control.ptr, control_init, sizeof(control_init),
+                      cudaMemcpyHostToDevice, stream) != cudaSuccess) {
+    return BMOE_CUDA_ERROR;
+  }
+  if (cudaEventRecord(plan->setup_done, stream) != cudaSuccess) return BMOE_CUDA_ERROR;
+
+  // ---- launch parameters ----
+  const CUtensorMap* const dev_maps = static_cast<const CUtensorMap*>(plan->tmaps.ptr);
+  bmoe::GemmParams& p = plan->params;
+  p = bmoe::GemmParams{};
+  p.tmap_a = dev_maps;
+  p.tmap_b = dev_maps + a.experts;
+  p.tmap_d = dev_maps + 2 * static_cast<size_t>(a.experts);
+  p.tiles = static_cast<const bmoe_tile*>(plan->worklist.ptr);
+  p.tile_count = tiles;
+  p.k_blocks = (a.k + 63) / 64;
+  p.sched_mode = policy.sched_mode;
+  p.claim_size = policy.claim_size;
+  p.main_end = main_end;
+  p.lookahead = policy.sched_mode == bmoe::kSchedStatic ? 0u : 1u;
+  p.queue = static_cast<uint32_t*>(plan->control.ptr);
+  p.status = reinterpret_cast<bmoe::DeviceStatus*>(
+      static_cast<uint8_t*>(plan->control.ptr) + 256);
+  p.tile_visits = nullptr;
+  p.cta_tiles = nullptr;
+  p.wait_budget_ns = 1000000000ull;  // 1 s per wait, then the kernel gives up
+
+  plan->tile_n = tile_n;
+  plan->grid = policy.one_cta_per_tile ? tiles : (tiles < cta_budget ? tiles : cta_budget);
+
+  plan->stats.threadblock_count = plan->grid;
+  plan->stats.workspace_bytes = plan->counts.bytes + plan->tmaps.bytes +
+                                plan->worklist.bytes + plan->workspace.bytes +
+                                plan->control.bytes;
+  plan->stats.total_tiles = tiles;
+  plan->stats.tile_m = tile_m;
+  plan->stats.tile_n = tile_n;
+  plan->stats.resolved_scheduler = policy.scheduler;
+  plan->stats.claim_size = policy.claim_size;
+  plan->stats.hybrid_tail_tiles = tail;
+  plan->stats.cta_group = 1;
+  plan->stats.stages = bmoe::gemm_stage_count(tile_n);
+  plan->stats.dynamic_smem_bytes = bmoe::gemm_smem_bytes(tile_n);
+  plan->stats.launches = 0;
+  plan->ready = true;
+  return BMOE_OK;
+}
+
+int bmoe_plan_run(bmoe_plan* plan, void* stream) {
+  if (plan == nullptr || !plan->ready) return BMOE_INVALID_ARGUMENT;
+  if (plan->stats.active_experts == 0) return BMOE_OK;
+  cudaStream_t s = stream == nullptr ? plan->default_stream
+                                     : static_cast<cudaStream_t>(stream);
+  if (s != plan->setup_stream &&
+      cudaStreamWaitEvent(s, plan->setup_done, 0) != cudaSuccess) {
+    return BMOE_CUDA_ERROR;
+  }
+  const cudaError_t err =
+      bmoe::launch_grouped_gemm(plan->params, plan->tile_n, plan->grid, s);
+  plan->last_stream = s;
+  if (err != cudaSuccess) return BMOE_CUDA_ERROR;
+  plan->stats.launches += 1;
+  return BMOE_OK;
+}
+
+int bmoe_plan_stats_get(const bmoe_plan* plan, bmoe_plan_stats* out) {
+  if (out == nullptr) return BMOE_INVALID_ARGUMENT;
+  *out = plan == nullptr ? bmoe_plan_stats{} : plan->stats;
+  return BMOE_OK;
+}
+
+int bmoe_plan_poll(bmoe_plan* plan, bmoe_device_report* report) {
+  if (plan == nullptr || !plan->ready) return BMOE_INVALID_ARGUMENT;
+  if (report != nullptr) std::memset(report, 0, sizeof(*report));
+  if (plan->stats.active_experts == 0) return BMOE_OK;
+  if (cudaStreamSynchronize(plan->last_stream) != cudaSuccess) return BMOE_CUDA_ERROR;
+  bmoe::DeviceStatus st{};
+  if (cudaMemcpy(&st, plan->params.status, sizeof(st), cudaMemcpyDeviceToHost) !=
+      cudaSuccess) {
+    return BMOE_CUDA_ERROR;
+  }
+  if (st.count == 0) return BMOE_OK;
+  if (report != nullptr) {
+    report->code = st.code;
+    report->cta = st.cta;
+    report->role = st.role;
+    report->tile = st.tile;
+    report->stage = st.stage;
+    report->aux = st.aux;
+    report->count = st.count;
+  }
+  // Rearm the status record and the queue so the plan stays usable.
+  uint32_t control_init[128];
+  std::memset(control_init, 0, sizeof(control_init));
+  control_init[1] = plan->params.main_end;
+  cudaMemcpy(plan->control.ptr, control_init, sizeof(control_init), cudaMemcpyHostToDevice);
+  return BMOE_DEVICE_TIMEOUT;
+}
+
+int bmoe_plan_read_worklist(bmoe_plan* plan, bmoe_tile* tiles_host, uint32_t capacity,
+                            uint32_t* count_out) {
+  if (plan == nullptr || !plan->ready) return BMOE_INVALID_ARGUMENT;
+  const uint32_t total = plan->stats.total_tiles;
+  if (count_out != nullptr) *count_out = total;
+  const uint32_t n_copy = capacity < total ? capacity : total;
+  if (n_copy == 0) return BMOE_OK;
+  if (tiles_host == nullptr) return BMOE_INVALID_ARGUMENT;
+  if (cudaStreamSynchronize(plan->setup_stream) != cudaSuccess) return BMOE_CUDA_ERROR;
+  return cudaMemcpy(tiles_host, plan->worklist.ptr, sizeof(bmoe_tile) * n_copy,
+                    cudaMemcpyDeviceToHost) == cudaSuccess
+             ? BMOE_OK
+             : BMOE_CUDA_ERROR;
+}
+
+int bmoe_plan_set_observers(bmoe_plan* plan, uint32_t* tile_visits_dev,
+                            uint32_t* cta_tiles_dev) {
+  if (plan == nullptr || !plan->ready) return BMOE_INVALID_ARGUMENT;
+  plan->params.tile_visits = tile_visits_dev;
+  plan->params.cta_tiles = cta_tiles_dev;
+  return BMOE_OK;
+}
+
+int bmoe_grouped_gemm(const bmoe_gemm_args* args) {
+  if (args == nullptr) return BMOE_INVALID_ARGUMENT;
+  bmoe_plan* plan = bmoe_plan_create();
+  if (plan == nullptr) return BMOE_CUDA_ERROR;
+  int rc = bmoe_plan_initialize(plan, args);
+  if (rc == BMOE_OK) rc = bmoe_plan_run(plan, args->stream);
+  // The plan owns the worklist and descriptors the kernel reads: wait for the
+  // launch before releasing them.
+  if (rc == BMOE_OK) rc = bmoe_plan_poll(plan, nullptr);
+  bmoe_plan_destroy(plan);
+  return rc;
+}
+
+const char* bmoe_build_info(void) {
+  return "bmoe_b200: sm_100a, tcgen05/TMEM/TMA grouped GEMM, CUDA runtime "
+#define BMOE_STR2(x) #x
+#define BMOE_STR(x) BMOE_STR2(x)
+         BMOE_STR(CUDART_VERSION);
+}
+
+}  // extern "C"

@@ -1,0 +1,369 @@
+/*
+ * bmoe_b200.h - C interface of the B200 (sm_100a) MoE grouped-GEMM engine.
+ *
+ * Plain C: pointers, sizes and integer status codes only. Every entry point
+ * names the reference interface it stands in for (paths are relative to the
+ * reference project root). The C++ classes in include/blackwell_moe/ are thin
+ * wrappers over these functions and live in the same shared library.
+ *
+ * Conventions
+ *   - "dev" pointers are CUDA device pointers, "host" pointers are host memory.
+ *   - stream arguments are cudaStream_t values passed as void* (NULL = default).
+ *   - All functions return a bmoe_status value unless stated otherwise and
+ *     never throw.
+ *   - There is no CPU implementation behind the device entry points: without a
+ *     compute-capability-10.0 GPU they return BMOE_UNSUPPORTED_DEVICE or
+ *     BMOE_CUDA_ERROR.
+ */
+#ifndef BMOE_B200_H_
+#define BMOE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------ */
+/* Status codes. Values 0-6 are the ordinals of blackwell_moe::KernelStatus  */
+/* (include/blackwell_moe/kernels/grouped_gemm.cuh:30-38); 7 is appended.    */
+/* ------------------------------------------------------------------------ */
+enum bmoe_status {
+  BMOE_OK = 0,
+  BMOE_INVALID_ARGUMENT = 1,
+  BMOE_UNSUPPORTED_DATA_TYPE = 2,
+  BMOE_UNSUPPORTED_SCHEDULER = 3,
+  BMOE_UNSUPPORTED_DEVICE = 4,
+  BMOE_CUDA_ERROR = 5,
+  BMOE_BACKEND_ERROR = 6, /* reference "CUTLASS error" slot; never returned */
+  BMOE_DEVICE_TIMEOUT = 7 /* a bounded in-kernel wait expired */
+};
+
+/* Replaces kernel_status_string (grouped_gemm.cuh:40; defined only in
+ * baselines/cutlass/cutlass_baseline.cu:165-176 in the reference). */
+const char* bmoe_status_string(int status);
+
+/* Scheduling policies: ordinals of blackwell_moe::SchedulerKind
+ * (include/blackwell_moe/scheduler/scheduler.cuh:12-18) plus CLC. */
+enum bmoe_scheduler {
+  BMOE_SCHED_EXPERT_ORDER = 0,
+  BMOE_SCHED_STATIC_PERSISTENT = 1, /* a.k.a. sorted_static */
+  BMOE_SCHED_DYNAMIC_QUEUE = 2,
+  BMOE_SCHED_COMPACTED = 3,
+  BMOE_SCHED_AUTO = 4,
+  BMOE_SCHED_CLC = 5
+};
+
+/* The 20-byte worklist record, byte-identical to blackwell_moe::ExpertTile
+ * (include/blackwell_moe/work_tile.cuh:13-21). */
+typedef struct bmoe_tile {
+  uint32_t expert_id;
+  uint32_t tile_m;
+  uint32_t tile_n;
+  uint32_t valid_m;
+  uint32_t valid_n;
+} bmoe_tile;
+
+/* ======================================================================== */
+/* 1. Host model: workload generator, worklist, policies, metrics, dispatch  */
+/* ======================================================================== */
+
+/* blackwell_moe::WorkloadConfig (include/blackwell_moe/problem.hpp:16-25).
+ * distribution: 0 uniform, 1 heavy_hitter, 2 sparse, 3 zipf. */
+typedef struct bmoe_workload_config {
+  uint32_t experts;
+  uint32_t distribution;
+  uint64_t total_tokens;
+  uint64_t seed;
+  double zipf_alpha;
+  double heavy_hitter_fraction;
+  double heavy_hitter_token_share;
+  double inactive_expert_fraction;
+} bmoe_workload_config;
+
+/* Replaces generate_workload (src/workload/workload.cpp:100-113).
+ * counts_out: host array [experts]. Invalid configs -> BMOE_INVALID_ARGUMENT. */
+int bmoe_generate_workload(const bmoe_workload_config* config,
+                           uint32_t* counts_out);
+
+/* blackwell_moe::WorkloadMetrics (include/blackwell_moe/workload.hpp:10-19). */
+typedef struct bmoe_workload_metrics {
+  double mean_tokens;
+  double coefficient_of_variation;
+  double max_over_mean;
+  double inactive_expert_ratio;
+  double small_m_expert_ratio;
+  double tile_count_cv;
+  uint32_t active_experts;
+  uint32_t reserved;
+  uint64_t total_tiles;
+} bmoe_workload_metrics;
+
+/* Replaces compute_workload_metrics (src/workload/workload.cpp:127-172). */
+int bmoe_workload_metrics_compute(const uint32_t* counts, uint32_t experts,
+                                  uint32_t n, uint32_t tile_m, uint32_t tile_n,
+                                  bmoe_workload_metrics* out);
+
+/* Worklist orders. */
+enum bmoe_worklist_order {
+  BMOE_ORDER_EXPERT = 0,       /* build_expert_tiles order */
+  BMOE_ORDER_SORTED_BY_WORK = 1 /* order_by_descending_expert_tiles order */
+};
+/* Traversal inside one expert's tile grid. */
+enum bmoe_raster {
+  BMOE_RASTER_N_FASTEST = 0, /* reference order: tile_m outer, tile_n inner */
+  BMOE_RASTER_M_FASTEST = 1  /* tile_n outer, tile_m inner (L2-friendly) */
+};
+
+/* Number of tiles build_expert_tiles would emit. Returns UINT64_MAX when a
+ * tile dimension is zero. */
+uint64_t bmoe_host_tile_count(const uint32_t* counts, uint32_t experts,
+                              uint32_t n, uint32_t tile_m, uint32_t tile_n);
+
+/* Replaces build_expert_tiles / order_by_descending_expert_tiles
+ * (src/scheduler/scheduler.cpp:37-60, 80-103) on the host. Writes at most
+ * `capacity` records and always reports the full count in *count_out. */
+int bmoe_host_build_tiles(const uint32_t* counts, uint32_t experts, uint32_t n,
+                          uint32_t tile_m, uint32_t tile_n, uint32_t order,
+                          uint32_t raster, bmoe_tile* tiles_out,
+                          uint64_t capacity, uint64_t* count_out);
+
+/* blackwell_moe::ScheduleMetrics (scheduler.cuh:26-39). */
+typedef struct bmoe_schedule_metrics {
+  uint64_t total_tiles;
+  uint64_t total_valid_elements;
+  uint64_t total_padded_elements;
+  uint64_t expert_switches;
+  uint64_t min_tiles_per_cta;
+  uint64_t max_tiles_per_cta;
+  double mean_cta_work;
+  double max_cta_work;
+  double cta_work_cv;
+  double tail_ratio;
+  double estimated_utilization;
+  double useful_work_ratio;
+} bmoe_schedule_metrics;
+
+/* Replaces simulate_scheduler + compute_schedule_metrics
+ * (src/scheduler/scheduler.cpp:124-211). tiles_out receives the per-CTA tile
+ * lists back to back (capacity records), cta_offsets_out[cta_count + 1] their
+ * boundaries; either may be NULL. cta_count == 0 -> BMOE_INVALID_ARGUMENT. */
+int bmoe_host_simulate(uint32_t scheduler, const uint32_t* counts,
+                       uint32_t experts, uint32_t n, uint32_t tile_m,
+                       uint32_t tile_n, uint32_t cta_count,
+                       bmoe_tile* tiles_out, uint64_t capacity,
+                       uint64_t* cta_offsets_out,
+                       bmoe_schedule_metrics* metrics_out);
+
+/* RoutingFeatures (python/blackwell_moe_tirx/dispatch.py:16-27). */
+typedef struct bmoe_routing_features {
+  double mean_m;
+  double cv_m;
+  double max_over_mean_m;
+  double inactive_expert_ratio;
+  double small_m_expert_ratio;
+  double expert_tile_cv;
+  double max_expert_tiles_over_mean;
+  uint64_t active_tiles;
+  double tiles_per_cta;
+  double useful_work_ratio;
+} bmoe_routing_features;
+
+/* Replaces routing_features (dispatch.py:42-83). */
+int bmoe_routing_features_compute(const uint32_t* counts, uint32_t experts,
+                                  uint32_t n, uint32_t tile_m, uint32_t tile_n,
+                                  uint32_t cta_count,
+                                  bmoe_routing_features* out);
+
+/* Launch variants, in the order of KERNEL_VERSIONS minus v0_5
+ * (python/blackwell_moe_tirx/kernels/registry.py:45-106). */
+enum bmoe_variant {
+  BMOE_VARIANT_NONPERSISTENT = 0,
+  BMOE_VARIANT_STATIC_WS = 1,
+  BMOE_VARIANT_DYNAMIC_CLAIM1 = 2,
+  BMOE_VARIANT_CHUNKED = 3,
+  BMOE_VARIANT_HYBRID = 4,
+  BMOE_VARIANT_CLC = 5
+};
+
+/* Replaces select_kernel with the default DispatchThresholds
+ * (dispatch.py:30-39, 86-114). thresholds may be NULL (defaults) or point to
+ * six doubles in the field order of DispatchThresholds. */
+int bmoe_select_variant(const bmoe_routing_features* features,
+                        const double* thresholds, uint32_t* variant_out);
+const char* bmoe_variant_name(uint32_t variant);
+
+/* ======================================================================== */
+/* 2. Device worklist builder                                                */
+/* ======================================================================== */
+
+/* Totals written by the builder (device memory, 32 bytes). */
+typedef struct bmoe_worklist_totals {
+  uint32_t total_tiles;
+  uint32_t active_experts;
+  uint64_t total_rows;           /* sum of counts */
+  uint64_t total_valid_elements; /* sum of counts * n */
+  uint32_t overflow;             /* 1 if total_tiles exceeded tile_capacity or 2^32 */
+  uint32_t reserved;
+} bmoe_worklist_totals;
+
+/* Byte offsets of the arrays inside the builder workspace for `experts`. */
+typedef struct bmoe_worklist_layout {
+  size_t bytes;                   /* workspace size */
+  size_t off_totals;              /* bmoe_worklist_totals */
+  size_t off_row_offsets;         /* uint64 [experts + 1] exclusive prefix of counts */
+  size_t off_expert_m_tiles;      /* uint32 [experts] ceil(count / tile_m) */
+  size_t off_expert_tiles;        /* uint32 [experts] m_tiles * n_tiles */
+  size_t off_tile_offsets;        /* uint32 [experts + 1] prefix of expert_tiles by id */
+  size_t off_active_ids;          /* uint32 [experts] ascending ids of experts with
+                                     tokens, padded with 0xFFFFFFFF */
+  size_t off_visit_order;         /* uint32 [experts] expert visited at position p */
+  size_t off_visit_tile_offsets;  /* uint32 [experts + 1] prefix of tiles in visit order */
+} bmoe_worklist_layout;
+
+int bmoe_worklist_layout_for(uint32_t experts, bmoe_worklist_layout* out);
+
+/* Largest expert count the single-CTA planning kernel accepts. */
+#define BMOE_WORKLIST_MAX_EXPERTS 16384u
+
+typedef struct bmoe_worklist_request {
+  uint32_t experts;
+  uint32_t n;
+  uint32_t tile_m;
+  uint32_t tile_n;
+  uint32_t order;  /* bmoe_worklist_order */
+  uint32_t raster; /* bmoe_raster */
+} bmoe_worklist_request;
+
+/* On-device statement of build_expert_tiles /
+ * order_by_descending_expert_tiles (src/scheduler/scheduler.cpp:37-60, 80-103)
+ * and of the active-expert filter of the reference plan
+ * (baselines/cutlass/cutlass_baseline.cu:243-266): two integer kernels,
+ * enqueued on `stream`, no host synchronisation.
+ *   counts_dev    uint32 [experts]
+ *   tiles_dev     bmoe_tile [tile_capacity]; records beyond capacity are
+ *                 dropped and totals.overflow is set
+ *   workspace_dev bmoe_worklist_layout_for(experts).bytes bytes, 256-aligned */
+int bmoe_worklist_build(const uint32_t* counts_dev,
+                        const bmoe_worklist_request* request,
+                        bmoe_tile* tiles_dev, uint32_t tile_capacity,
+                        void* workspace_dev, void* stream);
+
+/* ======================================================================== */
+/* 3. Grouped-GEMM plan                                                      */
+/* ======================================================================== */
+
+/* blackwell_moe::GroupedGemmArguments (grouped_gemm.cuh:12-28) followed by the
+ * engine extensions; zero (raster: negative) selects the engine default. */
+typedef struct bmoe_gemm_args {
+  const void* const* a;              /* host array [experts] of device pointers */
+  const void* const* b;
+  void* const* d;
+  const uint32_t* tokens_per_expert; /* host array [experts] */
+  uint32_t experts;
+  uint32_t n;
+  uint32_t k;
+  uint32_t data_type; /* 0 = BF16 (only supported), 1 = FP8 E4M3 */
+  uint32_t scheduler; /* bmoe_scheduler */
+  uint32_t claim_size;
+  uint32_t hybrid_tail_tiles;
+  uint32_t cta_count;
+  uint32_t tile_n;
+  uint32_t cta_group;
+  int32_t raster_along_m;
+  uint32_t reserved;
+  void* stream;
+} bmoe_gemm_args;
+
+/* blackwell_moe::GroupedGemmPlanStats (grouped_gemm.cuh:42-46) + extensions. */
+typedef struct bmoe_plan_stats {
+  uint32_t active_experts;
+  uint32_t threadblock_count;
+  uint64_t workspace_bytes;
+  uint32_t total_tiles;
+  uint32_t tile_m;
+  uint32_t tile_n;
+  uint32_t resolved_scheduler;
+  uint32_t claim_size;
+  uint32_t hybrid_tail_tiles;
+  uint32_t cta_group;
+  uint32_t stages;
+  uint32_t dynamic_smem_bytes;
+  uint32_t launches; /* kernel launches enqueued by run() since initialize */
+} bmoe_plan_stats;
+
+/* What a kernel recorded when it gave up on a bounded wait. */
+typedef struct bmoe_device_report {
+  uint32_t code;  /* 0 = clean; otherwise a BMOE_DEV_* site code */
+  uint32_t cta;
+  uint32_t role;  /* 0 scheduler, 1 producer, 2 mma, 3 epilogue */
+  uint32_t tile;
+  uint32_t stage;
+  uint32_t aux;
+  uint32_t count; /* CTAs that reported */
+  uint32_t reserved;
+} bmoe_device_report;
+
+typedef struct bmoe_plan bmoe_plan;
+
+/* Replace Bf16GroupedGemmPlan's constructor / destructor / initialize / run /
+ * stats (grouped_gemm.cuh:51-69; behaviour of
+ * baselines/cutlass/cutlass_baseline.cu:179-377). */
+bmoe_plan* bmoe_plan_create(void);
+void bmoe_plan_destroy(bmoe_plan* plan);
+int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args);
+int bmoe_plan_run(bmoe_plan* plan, void* stream);
+int bmoe_plan_stats_get(const bmoe_plan* plan, bmoe_plan_stats* out);
+
+/* Synchronises the stream last used by run() and returns BMOE_DEVICE_TIMEOUT
+ * (filling *report when non-NULL) if a kernel abandoned a wait. */
+int bmoe_plan_poll(bmoe_plan* plan, bmoe_device_report* report);
+
+/* Copies the plan's device worklist back to the host (synchronises). */
+int bmoe_plan_read_worklist(bmoe_plan* plan, bmoe_tile* tiles_host,
+                            uint32_t capacity, uint32_t* count_out);
+
+/* Optional device counters for exact-once checks (NULL disables):
+ *   tile_visits_dev   uint32 [total_tiles], +1 by the CTA that ran the tile
+ *   cta_tiles_dev     uint32 [threadblock_count], tiles run per CTA
+ * The caller zeroes them. Mirrors the probe observables
+ * (include/blackwell_moe/scheduler/scheduler_probe.cuh:24-28). */
+int bmoe_plan_set_observers(bmoe_plan* plan, uint32_t* tile_visits_dev,
+                            uint32_t* cta_tiles_dev);
+
+/* Replaces launch_grouped_gemm_baseline (grouped_gemm.cuh:71). */
+int bmoe_grouped_gemm(const bmoe_gemm_args* args);
+
+/* ======================================================================== */
+/* 4. Scheduler probe                                                        */
+/* ======================================================================== */
+
+/* blackwell_moe::SchedulerProbeArguments (scheduler_probe.cuh:18-30). */
+typedef struct bmoe_probe_args {
+  const bmoe_tile* tiles;
+  uint32_t tile_count;
+  uint32_t cta_count;
+  uint32_t claim_size;
+  uint32_t work_scale;
+  uint32_t* next_tile;
+  uint32_t* tile_visits;
+  uint64_t* tile_checksums;
+  uint32_t* cta_tile_counts;
+  uint64_t* cta_valid_elements;
+  void* stream;
+} bmoe_probe_args;
+
+/* Replaces launch_scheduler_probe / device_scheduler_name
+ * (src/kernels/scheduler_probe.cu:105-141). scheduler: 0 static, 1 queue. */
+int bmoe_probe_launch(uint32_t scheduler, const bmoe_probe_args* args);
+const char* bmoe_probe_scheduler_name(uint32_t scheduler);
+
+/* Library build information ("sm_100a", CUDA runtime version, ...). */
+const char* bmoe_build_info(void);
+
+#ifdef __cplusplus
+} /* extern "C" */
+#endif
+
+#endif /* BMOE_B200_H_ */

@@ -1,0 +1,254 @@
+"""Grouped GEMM on the GPU through the C interface, against the CPU oracle.
+
+Bars: every scheduling policy bit-identical to expert order; max |err| <= 2 BF16
+ulp of the FP32 sequential-k reference (ulp taken at max(|ref|, 2^-6)) and
+relative Frobenius error <= 1e-3; reference known-answer inputs bit-exact."""
+
+import numpy as np
+import pytest
+
+import support
+
+pytestmark = pytest.mark.gpu
+
+POLICIES = [
+    ("expert_order", {}),
+    ("static_persistent", {}),
+    ("dynamic_queue", {}),
+    ("dynamic_queue", {"claim_size": 4}),
+    ("dynamic_queue", {"claim_size": 8, "hybrid_tail_tiles": 7}),
+    ("compacted", {}),
+    ("clc", {}),
+    ("auto", {}),
+]
+
+
+def make_inputs(counts, n, k, seed=2026):
+    import torch
+
+    gen = torch.Generator().manual_seed(seed)
+    a = torch.randn(max(1, sum(counts)), k, generator=gen).to(torch.bfloat16)[: sum(counts)]
+    w = (torch.randn(len(counts), n, k, generator=gen) * k ** -0.5).to(torch.bfloat16)
+    return a, w
+
+
+def bits_of(t):
+    import torch
+
+    return t.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+def run_engine(engine, a, w, counts, policy="expert_order", observers=False, **options):
+    import torch
+
+    n = w.shape[1]
+    a_dev, w_dev = a.cuda(), w.cuda()
+    d_dev = torch.full((max(1, sum(counts)), n), float("nan"), dtype=torch.bfloat16,
+                       device="cuda")[: sum(counts)]
+    plan = engine.GroupedGemmPlan()
+    try:
+        status = plan.initialize_packed(a_dev, w_dev, d_dev, counts, scheduler=policy, **options)
+        assert status == 0, engine._capi.status_string(status)
+        stats = plan.stats()
+        visits = cta = None
+        if observers and stats.total_tiles:
+            visits = torch.zeros(stats.total_tiles, dtype=torch.int32, device="cuda")
+            cta = torch.zeros(stats.threadblock_count, dtype=torch.int32, device="cuda")
+            assert plan.set_observers(visits, cta) == 0
+        assert plan.run() == 0
+        status, report = plan.poll()
+        assert status == 0, (engine._capi.status_string(status), report.code, report.cta,
+                             report.role, report.tile, report.stage, report.aux)
+        worklist = plan.worklist() if stats.total_tiles else None
+        return {"bits": bits_of(d_dev), "stats": stats, "worklist": worklist,
+                "visits": None if visits is None else visits.cpu().numpy(),
+                "cta": None if cta is None else cta.cpu().numpy()}
+    finally:
+        plan.close()
+
+
+def check_against_oracle(oracle, a, w, counts, got_bits):
+    n, k = w.shape[1], w.shape[2]
+    ref = oracle.grouped_gemm(bits_of(a), bits_of(w), counts, n, k, want_f32=True)
+    exact = ref["f32"].astype(np.float64)
+    got = support.bf16_bits_to_f32(got_bits).astype(np.float64)
+    assert np.all(np.isfinite(got)), "unwritten or non-finite outputs"
+    mag = np.maximum(np.abs(exact), 2.0 ** -6)
+    ulp = 2.0 ** (np.floor(np.log2(mag)) - 7)
+    err_ulp = np.abs(got - exact) / ulp
+    assert err_ulp.max() <= 2.0, f"max error {err_ulp.max():.3f} BF16 ulp"
+    rel_fro = np.linalg.norm(got - exact) / max(np.linalg.norm(exact), 1e-30)
+    assert rel_fro <= 1e-3, f"relative Frobenius error {rel_fro:.3e}"
+    return float(err_ulp.max()), float(rel_fro)
+
+
+@pytest.mark.parametrize("name", ["cutlass_baseline_kat", "sm100_dense_kat", "sm100_2sm_kat"])
+def test_reference_known_answers_bit_exact(engine, golden, name):
+    import torch
+
+    counts, n, k, a_bits, w_bits = support.kat_inputs(name)
+    a = torch.from_numpy(a_bits.view(np.int16).copy()).view(torch.bfloat16)
+    w = torch.from_numpy(w_bits.view(np.int16).copy()).view(torch.bfloat16)
+    for tile_n in (0, 128, 256):
+        out = run_engine(engine, a, w, counts, tile_n=tile_n)
+        assert out["stats"].active_experts == sum(c > 0 for c in counts)
+        assert support.sha(out["bits"].reshape(-1)) == golden["gemm_kats"][name]["d_sha256"]
+
+
+def test_pointer_array_form_with_separate_allocations(engine, oracle):
+    """The reference harness allocates A, B, D per expert and leaves null
+    entries for empty experts (baselines/cutlass/test_correctness.cu:60-107)."""
+    import torch
+
+    counts, n, k, a_bits, w_bits = support.kat_inputs("cutlass_baseline_kat")
+    a_all = torch.from_numpy(a_bits.view(np.int16).copy()).view(torch.bfloat16)
+    w_all = torch.from_numpy(w_bits.view(np.int16).copy()).view(torch.bfloat16)
+    bufs, a_ptrs, b_ptrs, d_ptrs, row = [], [], [], [], 0
+    for e, m in enumerate(counts):
+        if m == 0:
+            a_ptrs.append(0); b_ptrs.append(0); d_ptrs.append(0)
+            continue
+        a_e = a_all[row:row + m].clone().cuda()
+        b_e = w_all[e].clone().cuda()
+        d_e = torch.zeros(m, n, dtype=torch.bfloat16, device="cuda")
+        bufs.append((a_e, b_e, d_e))
+        a_ptrs.append(a_e.data_ptr()); b_ptrs.append(b_e.data_ptr()); d_ptrs.append(d_e.data_ptr())
+        row += m
+    plan = engine.GroupedGemmPlan()
+    try:
+        assert plan.initialize(a_ptrs, b_ptrs, d_ptrs, counts, n, k) == 0
+        assert plan.stats().active_experts == 3
+        assert plan.run() == 0 and plan.poll()[0] == 0
+        got = np.concatenate([bits_of(d) for _, _, d in bufs], axis=0)
+        want = oracle.grouped_gemm(a_bits, w_bits, counts, n, k)["bf16"]
+        assert np.array_equal(got, want)
+        # a non-empty expert with a null pointer is rejected
+        bad = list(a_ptrs); bad[0] = 0
+        assert plan.initialize(bad, b_ptrs, d_ptrs, counts, n, k) == engine._capi.INVALID_ARGUMENT
+        assert plan.run() == engine._capi.INVALID_ARGUMENT
+        # misaligned pointer
+        bad = list(a_ptrs); bad[0] += 2
+        assert plan.initialize(bad, b_ptrs, d_ptrs, counts, n, k) == engine._capi.INVALID_ARGUMENT
+    finally:
+        plan.close()
+
+
+def test_no_active_experts_is_success_without_launch(engine):
+    import torch
+
+    w = torch.zeros(3, 64, 64, dtype=torch.bfloat16)
+    a = torch.zeros(0, 64, dtype=torch.bfloat16)
+    out = run_engine(engine, a, w, [0, 0, 0])
+    assert out["stats"].active_experts == 0 and out["stats"].threadblock_count == 0
+    assert out["stats"].launches == 0
+
+
+CASES = [
+    # counts, n, k
+    ([1], 8, 8),
+    ([128], 256, 64),
+    ([129, 0, 1, 255], 264, 72),
+    ([37, 0, 1, 200], 384, 192),
+    ([300, 5, 0, 300, 129], 520, 448),
+    ([65, 67, 68, 61, 63, 57, 61, 70], 1024, 512),
+    ([3] * 40 + [0] * 20 + [500], 256, 1024),
+]
+
+
+@pytest.mark.parametrize("counts,n,k", CASES)
+def test_ragged_cases_all_policies(engine, oracle, counts, n, k):
+    a, w = make_inputs(counts, n, k)
+    base = run_engine(engine, a, w, counts, "expert_order", observers=True, raster_along_m=0)
+    check_against_oracle(oracle, a, w, counts, base["bits"])
+    # the plan's device worklist is the reference worklist, byte for byte
+    assert np.array_equal(base["worklist"],
+                          oracle.build_tiles(counts, n, 128, base["stats"].tile_n))
+    assert np.all(base["visits"] == 1)
+    assert int(base["cta"].sum()) == base["stats"].total_tiles
+    for tile_n in (128, 256):
+        for raster in (0, 1):
+            for policy, opts in POLICIES:
+                out = run_engine(engine, a, w, counts, policy, observers=True, tile_n=tile_n,
+                                 raster_along_m=raster, **opts)
+                assert np.array_equal(out["bits"], base["bits"]), (policy, opts, tile_n, raster)
+                assert np.all(out["visits"] == 1), (policy, opts)
+                assert int(out["cta"].sum()) == out["stats"].total_tiles
+                order = 1 if policy == "static_persistent" else 0
+                if policy != "auto":
+                    assert np.array_equal(
+                        out["worklist"],
+                        oracle.build_tiles(counts, n, 128, tile_n, order=order, raster=raster))
+
+
+def test_policy_specific_launch_shapes(engine):
+    counts, n, k = [300, 5, 0, 300, 129], 520, 128
+    a, w = make_inputs(counts, n, k)
+    clc = run_engine(engine, a, w, counts, "clc")
+    assert clc["stats"].threadblock_count == clc["stats"].total_tiles
+    few = run_engine(engine, a, w, counts, "expert_order", cta_count=3, observers=True)
+    assert few["stats"].threadblock_count == 3
+    tiles = few["stats"].total_tiles
+    assert few["cta"].tolist() == [len(range(c, tiles, 3)) for c in range(3)]
+    hyb = run_engine(engine, a, w, counts, "dynamic_queue", claim_size=8, hybrid_tail_tiles=5,
+                     cta_count=4, observers=True)
+    assert hyb["stats"].claim_size == 8 and hyb["stats"].hybrid_tail_tiles == 5
+    assert np.array_equal(hyb["bits"], few["bits"]) and np.array_equal(clc["bits"], few["bits"])
+
+
+def test_plan_is_reusable_and_reinitialisable(engine, oracle):
+    import torch
+
+    counts, n, k = [200, 0, 77], 256, 256
+    a, w = make_inputs(counts, n, k)
+    a_dev, w_dev = a.cuda(), w.cuda()
+    d_dev = torch.zeros(sum(counts), n, dtype=torch.bfloat16, device="cuda")
+    plan = engine.GroupedGemmPlan()
+    try:
+        assert plan.initialize_packed(a_dev, w_dev, d_dev, counts, scheduler="dynamic_queue",
+                                      claim_size=2) == 0
+        runs = []
+        for _ in range(3):  # the queue rearms itself between launches
+            d_dev.zero_()
+            assert plan.run() == 0 and plan.poll()[0] == 0
+            runs.append(bits_of(d_dev).copy())
+        assert np.array_equal(runs[0], runs[1]) and np.array_equal(runs[0], runs[2])
+        check_against_oracle(oracle, a, w, counts, runs[0])
+        # new routing for the same plan object, on a side stream
+        counts2 = [10, 150, 117]
+        a2, _ = make_inputs(counts2, n, k, seed=7)
+        a2_dev = a2.cuda()
+        side = torch.cuda.Stream()
+        assert plan.initialize_packed(a2_dev, w_dev, d_dev, counts2, scheduler="clc") == 0
+        d_dev.zero_()
+        torch.cuda.synchronize()
+        assert plan.run(side) == 0 and plan.poll()[0] == 0
+        check_against_oracle(oracle, a2, w, counts2, bits_of(d_dev))
+        assert plan.stats().launches == 1
+    finally:
+        plan.close()
+
+
+def test_benchmark_shape_properties(engine, oracle, golden):
+    """Full-size Mixtral-shaped case: policies bit-identical, sampled rows within
+    tolerance of the oracle, every tile run exactly once."""
+    entry = golden["workloads"]["c2_zipf1_e8"]
+    counts, n, k = entry["counts"], 14336, 4096
+    a, w = make_inputs(counts, n, k)
+    base = run_engine(engine, a, w, counts, "expert_order", observers=True)
+    assert np.all(base["visits"] == 1)
+    for policy, opts in [("static_persistent", {}), ("dynamic_queue", {"claim_size": 4}),
+                         ("clc", {}), ("auto", {})]:
+        out = run_engine(engine, a, w, counts, policy, **opts)
+        assert np.array_equal(out["bits"], base["bits"]), policy
+    stride = 257
+    ref = oracle.grouped_gemm(bits_of(a), bits_of(w), counts, n, k, want_f32=True,
+                              row_stride=stride, row_phase=3)
+    rows, row0 = [], 0
+    for m in counts:
+        rows.extend(range(row0 + 3, row0 + m, stride))
+        row0 += m
+    exact = ref["f32"][rows].astype(np.float64)
+    got = support.bf16_bits_to_f32(base["bits"][rows]).astype(np.float64)
+    mag = np.maximum(np.abs(exact), 2.0 ** -6)
+    assert (np.abs(got - exact) / 2.0 ** (np.floor(np.log2(mag)) - 7)).max() <= 2.0
+    assert np.linalg.norm(got - exact) / np.linalg.norm(exact) <= 1e-3
