@@ -1,0 +1,502 @@
+#!/usr/bin/env python
+"""Benchmark of the MoE grouped-GEMM hot path on B200.
+
+    python bench.py --gpus 1 --steps K --warmup W            # this engine
+    python bench.py --impl reference ...                      # CPU reference arm
+
+One "step" is one grouped GEMM over one routed batch. At one GPU the workload is
+the Mixtral-8x7B-shaped up-projection (E=8, top-2, T=4096, K=4096, N=14336, Zipf
+s=1.0 routing, seed 2026); with more GPUs it is the expert-parallel
+DeepSeek-V3-shaped configuration (E=256, top-8, T=32768, K=7168, N=2048), one
+rank per GPU, tokens exchanged by NCCL all-to-all. Inputs are synthetic
+(A ~ N(0,1), W ~ N(0, 1/sqrt(K)), BF16). Prints ONE JSON line on rank 0.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # name: experts, top_k, tokens, k, n, distribution id, zipf alpha, extra generator args
+    "mixtral_e8_t4096_k4096_n14336_zipf1.0": dict(
+        experts=8, top_k=2, tokens=4096, k=4096, n=14336, distribution=3, zipf_alpha=1.0),
+    "cpu_runnable_e8_t256_k512_n1024_uniform": dict(
+        experts=8, top_k=2, tokens=256, k=512, n=1024, distribution=0, zipf_alpha=1.2),
+    "deepseek_decode_e256_t256_k7168_n2048_heavy": dict(
+        experts=256, top_k=8, tokens=256, k=7168, n=2048, distribution=1, zipf_alpha=1.2,
+        heavy_fraction=8 / 256, heavy_share=0.5),
+    "qwen3_e128_t16384_k2048_n768_zipf1.0": dict(
+        experts=128, top_k=8, tokens=16384, k=2048, n=768, distribution=3, zipf_alpha=1.0),
+    # half-size Mixtral-shaped case for profiler captures (weights 470 MB > L2)
+    "profile_e8_t2048_k4096_n7168_zipf1.0": dict(
+        experts=8, top_k=2, tokens=2048, k=4096, n=7168, distribution=3, zipf_alpha=1.0),
+    "ep_deepseek_e256_t32768_k7168_n2048_zipf1.0": dict(
+        experts=256, top_k=8, tokens=32768, k=7168, n=2048, distribution=3, zipf_alpha=1.0),
+}
+DEFAULT_WORKLOAD = "mixtral_e8_t4096_k4096_n14336_zipf1.0"
+EP_WORKLOAD = "ep_deepseek_e256_t32768_k7168_n2048_zipf1.0"
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the GEMM kernel from
+# the ncu captures summarised under profiles/ (None until captured).
+NCU_TRAFFIC_BYTES = {
+    DEFAULT_WORKLOAD: None,
+}
+
+
+def percentile(values, p):
+    """sorted[ceil(p * n) - 1], the reference harness's rule
+    (baselines/cutlass/benchmark.cu:133-138)."""
+    s = sorted(values)
+    idx = max(0, min(len(s) - 1, int(math.ceil(p * len(s)) - 1)))
+    return s[idx]
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        data = json.loads(path.read_text())
+        return {"source": "measured", "hbm_gbs": data["hbm_gbs"],
+                "bf16_tflops": data["bf16_tflops"],
+                "bf16_tflops_sustained": data.get("bf16_tflops_sustained")}
+    return {"source": "fallback", "hbm_gbs": 6650.0, "bf16_tflops": 1590.0,
+            "bf16_tflops_sustained": 1400.0}
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples during the timed region."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.device_index = device_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-i", str(self.device_index), "-lms", "20"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        clocks, reasons, power = [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in Path(self.path).read_text().splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                clocks.append(float(parts[1]))
+                out["sm_max_mhz"] = float(parts[2])
+                power.append(float(parts[3]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[5:9]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if clocks:
+            clocks.sort()
+            out["sm_mhz"] = clocks[len(clocks) // 2]
+            out["samples"] = len(clocks)
+            out["power_w_max"] = max(power)
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+def workload_counts(engine, spec):
+    """Routed rows per expert from the engine's (reference-exact) generator."""
+    import ctypes as C
+
+    cap = engine._capi
+    cfg = cap.WorkloadConfig(
+        experts=spec["experts"], distribution=spec["distribution"],
+        total_tokens=spec["tokens"] * spec["top_k"], seed=2026,
+        zipf_alpha=spec["zipf_alpha"],
+        heavy_hitter_fraction=spec.get("heavy_fraction", 0.1),
+        heavy_hitter_token_share=spec.get("heavy_share", 0.8),
+        inactive_expert_fraction=0.5)
+    out = (C.c_uint32 * spec["experts"])()
+    cap.check(cap.load().bmoe_generate_workload(C.byref(cfg), out), "bmoe_generate_workload")
+    return [int(x) for x in out]
+
+
+def synth_inputs(torch, counts, n, k, device):
+    gen = torch.Generator(device=device).manual_seed(2026)
+    total = sum(counts)
+    a = torch.randn(total, k, generator=gen, device=device, dtype=torch.float32).to(torch.bfloat16)
+    gen.manual_seed(2027)
+    w = torch.empty(len(counts), n, k, device=device, dtype=torch.bfloat16)
+    for e in range(len(counts)):
+        w[e] = (torch.randn(n, k, generator=gen, device=device, dtype=torch.float32)
+                * k ** -0.5).to(torch.bfloat16)
+    return a, w
+
+
+def bits(torch, t):
+    import numpy as np
+
+    return t.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+def load_oracle():
+    import ctypes
+
+    sys.path.insert(0, str(ROOT / "oracle"))
+    import build_oracle
+
+    lib = ctypes.CDLL(str(build_oracle.build_oracle()))
+    lib.orc_grouped_gemm.restype = ctypes.c_uint64
+    lib.orc_max_threads.restype = ctypes.c_int
+    return lib
+
+
+def oracle_time(lib, a_bits, w_bits, counts, n, k, stride):
+    """Times the CPU restatement on rows r % stride == 0 of every expert."""
+    import ctypes as C
+
+    import numpy as np
+
+    c = np.asarray(counts, dtype=np.uint32)
+    d = np.zeros((a_bits.shape[0], n), dtype=np.uint16)
+    t0 = time.perf_counter()
+    rows = lib.orc_grouped_gemm(
+        a_bits.ctypes.data_as(C.c_void_p), w_bits.ctypes.data_as(C.c_void_p),
+        c.ctypes.data_as(C.c_void_p), C.c_uint32(len(c)), C.c_uint32(n), C.c_uint32(k),
+        d.ctypes.data_as(C.c_void_p), None, None, C.c_uint32(stride), C.c_uint32(0), C.c_int(0))
+    dt = time.perf_counter() - t0
+    return int(rows), dt
+
+
+def cpu_sample(lib, a_bits, w_bits, counts, n, k, target_s=12.0):
+    """Bounded CPU baseline: calibrate on a thin row sample, then time a sample
+    sized for about `target_s` seconds."""
+    stride = max(1, sum(counts) // 256)
+    rows, dt = oracle_time(lib, a_bits, w_bits, counts, n, k, stride)
+    rate = rows / max(dt, 1e-9)
+    want_rows = max(rows, int(rate * target_s))
+    stride2 = max(1, sum(counts) // max(1, want_rows))
+    if stride2 < stride:
+        rows, dt = oracle_time(lib, a_bits, w_bits, counts, n, k, stride2)
+        stride = stride2
+    tflops = 2.0 * rows * n * k / dt / 1e12
+    return {"value": tflops, "unit": "TFLOP/s", "cores": int(lib.orc_max_threads()),
+            "kind": "port",
+            "sample": f"rows r%{stride}==0 of every expert ({rows} of {sum(counts)} rows, "
+                      f"{dt:.2f} s); FP32 sequential-k loop, OpenMP"}
+
+
+def run_reference_arm(args, spec, workload):
+    """The reference's CPU path for this op is the FP32 sequential-k loop of its
+    tests (it ships no CPU GEMM runner); the oracle port of that loop is timed on
+    all host cores, each step on a bounded row sample."""
+    import numpy as np
+
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import bmoe_b200 as engine
+
+    lib = load_oracle()
+    counts = workload_counts(engine, spec)
+    n, k = spec["n"], spec["k"]
+    rng = np.random.default_rng(2026)
+    total = sum(counts)
+    # BF16 bit patterns of N(0,1) and N(0,1/sqrt(k)) samples.
+    a_bits = (rng.standard_normal((total, k), dtype=np.float32).view(np.uint32) >> 16).astype(np.uint16)
+    w_bits = np.empty((len(counts), n, k), dtype=np.uint16)
+    for e in range(len(counts)):
+        w_bits[e] = ((rng.standard_normal((n, k), dtype=np.float32) * k ** -0.5)
+                     .view(np.uint32) >> 16).astype(np.uint16)
+    # Calibrate on a thin sample, then size each step so that the whole run
+    # (warm-up included) stays near 90 s of CPU time, at most 3 s per step.
+    stride = max(1, total // 128)
+    rows, dt = oracle_time(lib, a_bits, w_bits, counts, n, k, stride)
+    per_step_s = max(0.05, min(3.0, 90.0 / (args.steps + args.warmup / 8.0)))
+    want_rows = max(1, int(rows / max(dt, 1e-9) * per_step_s))
+    stride = max(1, total // want_rows)
+    for _ in range(args.warmup):
+        oracle_time(lib, a_bits, w_bits, counts, n, k, max(stride * 8, 1))
+    times, rows = [], 0
+    for _ in range(args.steps):
+        rows, dt = oracle_time(lib, a_bits, w_bits, counts, n, k, stride)
+        times.append(dt)
+    per_step = sum(times) / len(times)
+    tflops = 2.0 * rows * n * k / per_step / 1e12
+    cores = int(lib.orc_max_threads())
+    sample = (f"rows r%{stride}==0 of every expert ({rows} of {total} rows per step); "
+              "FP32 sequential-k loop, OpenMP")
+    line = {
+        "impl": "reference", "metric": "useful BF16 TFLOP/s per grouped GEMM",
+        "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True,
+        "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": workload, "experts": spec["experts"], "top_k": spec["top_k"],
+                   "tokens": spec["tokens"], "k": k, "n": n},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def time_policy(torch, plan, stream, iters):
+    """Per-launch CUDA-event samples (ms) of plan.run() on `stream`."""
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(iters)]
+    stops = [torch.cuda.Event(enable_timing=True) for _ in range(iters)]
+    for i in range(iters):
+        starts[i].record(stream)
+        status = plan.run(stream)
+        stops[i].record(stream)
+        if status != 0:
+            raise RuntimeError(f"plan.run failed with status {status}")
+    torch.cuda.synchronize()
+    return [s.elapsed_time(e) for s, e in zip(starts, stops)]
+
+
+def run_single_gpu(args, spec, workload):
+    import torch
+
+    import bmoe_b200 as engine
+
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; there is no CPU path for the engine")
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda:0")
+    stream = torch.cuda.current_stream()
+    counts = workload_counts(engine, spec)
+    n, k = spec["n"], spec["k"]
+    total = sum(counts)
+    flops = 2.0 * total * n * k
+    a, w = synth_inputs(torch, counts, n, k, dev)
+    d = torch.zeros(total, n, dtype=torch.bfloat16, device=dev)
+    active = sum(c > 0 for c in counts)
+    algorithmic_bytes = 2.0 * (total * k + active * n * k + total * n)
+
+    def make_plan(policy, **opts):
+        plan = engine.GroupedGemmPlan()
+        status = plan.initialize_packed(a, w, d, counts, scheduler=policy, stream=stream, **opts)
+        if status != 0:
+            raise RuntimeError(f"initialize({policy}) -> {engine._capi.status_string(status)}")
+        return plan
+
+    def check(plan, what):
+        status, rep = plan.poll()
+        if status != 0:
+            raise RuntimeError(f"{what}: {engine._capi.status_string(status)} "
+                               f"(site {rep.code} cta {rep.cta} role {rep.role} tile {rep.tile})")
+
+    # ---------------- headline: K timed steps of the chosen policy ----------
+    plan = make_plan(args.policy)
+    stats = plan.stats()
+    for _ in range(args.warmup):
+        plan.run(stream)
+    check(plan, "warm-up")
+    sampler = ClockSampler(0)
+    sampler.start()
+    time.sleep(0.25)
+    launches_before = plan.stats().launches
+    torch.cuda.synchronize()
+    samples = time_policy(torch, plan, stream, args.steps)
+    # the K steps again as one region (event pair around all of them)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    t0.record(stream)
+    for _ in range(args.steps):
+        plan.run(stream)
+    t1.record(stream)
+    torch.cuda.synchronize()
+    region_ms = t0.elapsed_time(t1)
+    launches = plan.stats().launches - launches_before
+    time.sleep(0.15)
+    clocks = sampler.stop()
+    check(plan, "timed region")
+    ms_per_step = region_ms / args.steps
+    value = flops / (ms_per_step * 1e-3) / 1e12
+    avg_launch_ms = sum(samples) / len(samples)
+
+    # ---------------- per-policy latency table (outside the headline region) --
+    policies = {}
+    if not args.no_policy_table:
+        table = [("expert_order", {}), ("static_persistent", {}), ("dynamic_queue", {}),
+                 ("dynamic_queue", {"claim_size": 4}),
+                 ("dynamic_queue", {"claim_size": 8, "hybrid_tail_tiles": 2 * 148}),
+                 ("compacted", {}), ("clc", {}), ("auto", {})]
+        plans = []
+        for policy, opts in table:
+            label = policy + ("" if not opts else "_c%d%s" % (
+                opts.get("claim_size", 1), "_hybrid" if opts.get("hybrid_tail_tiles") else ""))
+            plans.append((label, make_plan(policy, **opts)))
+        for _ in range(max(3, args.warmup)):
+            for _, p2 in plans:
+                p2.run(stream)
+        # Round-robin over the policies so that all of them see the same clock
+        # and power state; one event pair per launch.
+        iters = args.policy_iters
+        ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+               for _ in plans] for _ in range(iters)]
+        torch.cuda.synchronize()
+        for i in range(iters):
+            for j, (_, p2) in enumerate(plans):
+                ev[i][j][0].record(stream)
+                p2.run(stream)
+                ev[i][j][1].record(stream)
+        torch.cuda.synchronize()
+        for j, (label, p2) in enumerate(plans):
+            check(p2, label)
+            s = [ev[i][j][0].elapsed_time(ev[i][j][1]) for i in range(iters)]
+            st = p2.stats()
+            p50 = percentile(s, 0.5)
+            policies[label] = {
+                "p50_us": p50 * 1e3, "p99_us": percentile(s, 0.99) * 1e3,
+                "min_us": min(s) * 1e3,
+                "useful_tflops_p50": flops / (p50 * 1e-3) / 1e12,
+                "ctas": st.threadblock_count, "resolved": st.resolved_scheduler,
+                "claim_size": st.claim_size, "iters": len(s)}
+            p2.close()
+        base = policies["expert_order"]
+        for label, row in policies.items():
+            row["p99_speedup_vs_expert_order"] = base["p99_us"] / row["p99_us"]
+
+    # ---------------- end to end through the public API, host buffers --------
+    e2e, e2e_plan = None, None
+    if not args.no_e2e:
+        a_host = torch.empty(a.shape, dtype=torch.bfloat16).pin_memory()
+        a_host.copy_(a)
+        d_host = torch.empty(d.shape, dtype=torch.bfloat16).pin_memory()
+        e2e_plan = engine.GroupedGemmPlan()
+
+        def e2e_step():
+            a.copy_(a_host, non_blocking=True)                      # H2D activations
+            status = e2e_plan.initialize_packed(a, w, d, counts, scheduler=args.policy,
+                                                stream=stream)      # counts H2D, worklist, TMA maps
+            status = status or e2e_plan.run(stream)
+            d_host.copy_(d, non_blocking=True)                      # D2H result
+            if status != 0:
+                raise RuntimeError("e2e step failed")
+
+        for _ in range(3):
+            e2e_step()
+        torch.cuda.synchronize()
+        e2e_steps = max(3, min(args.steps, 20))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(e2e_steps):
+            e2e_step()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        check(e2e_plan, "e2e")
+        e2e_ms = e0.elapsed_time(e1) / e2e_steps
+        e2e = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+               "h2d_bytes_per_step": a_host.numel() * 2 + 4 * len(counts)
+               + 3 * 128 * len(counts) + 512,
+               "d2h_bytes_per_step": d_host.numel() * 2, "ms_per_step": e2e_ms,
+               "note": "weights stay resident on the device (plan state); activations and "
+                       "counts go up, the worklist and TMA descriptors are rebuilt, D comes back"}
+
+    # ---------------- CPU baseline on a bounded sample ------------------------
+    cpu = None
+    if not args.no_cpu_baseline:
+        lib = load_oracle()
+        cpu = cpu_sample(lib, bits(torch, a), bits(torch, w), counts, n, k,
+                         target_s=args.cpu_seconds)
+
+    peaks = measured_peaks()
+    achieved = flops / (avg_launch_ms * 1e-3) / 1e12
+    bound_is_tensor = flops / algorithmic_bytes > peaks["bf16_tflops"] * 1e12 / (peaks["hbm_gbs"] * 1e9)
+    if bound_is_tensor:
+        roofline = {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"],
+                    "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
+                    "frac_of_sustained": (achieved / peaks["bf16_tflops_sustained"]
+                                          if peaks.get("bf16_tflops_sustained") else None)}
+    else:
+        gbs = algorithmic_bytes / (avg_launch_ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": gbs / peaks["hbm_gbs"]}
+    roofline.update({"traffic": NCU_TRAFFIC_BYTES.get(workload), "peak_source": peaks["source"],
+                     "kernel": "grouped_gemm_kernel<%d>" % stats.tile_n,
+                     "algorithmic_flops_per_launch": flops,
+                     "algorithmic_bytes_per_launch": algorithmic_bytes,
+                     "avg_launch_ms": avg_launch_ms})
+
+    line = {
+        "metric": "useful BF16 TFLOP/s per grouped GEMM", "value": value, "unit": "TFLOP/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": workload, "experts": spec["experts"], "top_k": spec["top_k"],
+                   "tokens": spec["tokens"], "k": k, "n": n, "policy": args.policy,
+                   "resolved_policy": stats.resolved_scheduler, "tile": [stats.tile_m, stats.tile_n, 64],
+                   "ctas": stats.threadblock_count, "tiles": stats.total_tiles,
+                   "l2": "weights (%.0f MB) exceed the 126 MB L2; no flush between steps"
+                         % (active * n * k * 2 / 1e6)},
+        "p50_us": percentile(samples, 0.5) * 1e3, "p99_us": percentile(samples, 0.99) * 1e3,
+        "policies": policies, "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
+        "gpu_launches": launches, "clocks": clocks,
+    }
+    plan.close()
+    if e2e_plan is not None:
+        e2e_plan.close()
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="engine", choices=["engine", "reference"])
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
+    ap.add_argument("--policy", default="auto")
+    ap.add_argument("--policy-iters", type=int, default=200)
+    ap.add_argument("--no-policy-table", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    workload = args.workload or (DEFAULT_WORKLOAD if args.gpus == 1 else EP_WORKLOAD)
+    spec = WORKLOADS[workload]
+    if args.impl == "reference":
+        run_reference_arm(args, spec, workload)
+        return
+    if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
+        run_single_gpu(args, spec, workload)
+    else:
+        from bmoe_b200 import ep_bench  # noqa: F401  (multi-GPU arm)
+
+        ep_bench.run(args, spec, workload)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,8 +1,11 @@
 """Grouped GEMM on the GPU through the C interface, against the CPU oracle.
 
 Bars: every scheduling policy bit-identical to expert order; max |err| <= 2 BF16
-ulp of the FP32 sequential-k reference (ulp taken at max(|ref|, 2^-6)) and
-relative Frobenius error <= 1e-3; reference known-answer inputs bit-exact."""
+ulp of the unrounded FP32 sequential-k reference (ulp taken at max(|ref|, 2^-6));
+relative Frobenius error <= 1e-3 against the reference's BF16 output (rounding
+any exact value to BF16 already moves it by about 1.6e-3 in this norm, so the
+comparison is between the two BF16 results); reference known-answer inputs
+bit-exact."""
 
 import numpy as np
 import pytest
@@ -77,7 +80,8 @@ def check_against_oracle(oracle, a, w, counts, got_bits):
     ulp = 2.0 ** (np.floor(np.log2(mag)) - 7)
     err_ulp = np.abs(got - exact) / ulp
     assert err_ulp.max() <= 2.0, f"max error {err_ulp.max():.3f} BF16 ulp"
-    rel_fro = np.linalg.norm(got - exact) / max(np.linalg.norm(exact), 1e-30)
+    want = support.bf16_bits_to_f32(ref["bf16"]).astype(np.float64)
+    rel_fro = np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30)
     assert rel_fro <= 1e-3, f"relative Frobenius error {rel_fro:.3e}"
     return float(err_ulp.max()), float(rel_fro)
 
@@ -251,4 +255,5 @@ def test_benchmark_shape_properties(engine, oracle, golden):
     got = support.bf16_bits_to_f32(base["bits"][rows]).astype(np.float64)
     mag = np.maximum(np.abs(exact), 2.0 ** -6)
     assert (np.abs(got - exact) / 2.0 ** (np.floor(np.log2(mag)) - 7)).max() <= 2.0
-    assert np.linalg.norm(got - exact) / np.linalg.norm(exact) <= 1e-3
+    want = support.bf16_bits_to_f32(ref["bf16"][rows]).astype(np.float64)
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 1e-3
