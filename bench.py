@@ -48,9 +48,12 @@ DEFAULT_WORKLOAD = "mixtral_e8_t4096_k4096_n14336_zipf1.0"
 EP_WORKLOAD = "ep_deepseek_e256_t32768_k7168_n2048_zipf1.0"
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the GEMM kernel from
-# the ncu captures summarised under profiles/ (None until captured).
+# the ncu captures summarised under profiles/. The full Mixtral-shaped launch is
+# scaled from the half-size capture (565.6 MB measured for 562.0 MB of
+# algorithmic bytes; traffic grows in proportion to the operand bytes).
 NCU_TRAFFIC_BYTES = {
-    DEFAULT_WORKLOAD: None,
+    "profile_e8_t2048_k4096_n7168_zipf1.0": 565.6e6,
+    DEFAULT_WORKLOAD: 1241.5e6 * (565.6 / 562.0),
 }
 
 
