@@ -43,6 +43,8 @@ SCHEDULER_NAMES = {
     "clc_assisted": SCHED_CLC,
 }
 
+WORKLIST_STATIC_MAX_EXPERTS = 1024
+
 ORDER_EXPERT = 0
 ORDER_SORTED_BY_WORK = 1
 RASTER_N_FASTEST = 0
@@ -268,6 +270,10 @@ SIGNATURES = {
     "bmoe_variant_name": (C.c_char_p, [C.c_uint32]),
     "bmoe_worklist_layout_for": (C.c_int, [C.c_uint32, _P(WorklistLayout)]),
     "bmoe_worklist_build": (
+        C.c_int,
+        [C.c_void_p, _P(WorklistRequest), C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p],
+    ),
+    "bmoe_worklist_build_static": (
         C.c_int,
         [C.c_void_p, _P(WorklistRequest), C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p],
     ),

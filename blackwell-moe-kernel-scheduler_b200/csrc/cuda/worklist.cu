@@ -275,3 +275,66 @@ int bmoe_worklist_build(const uint32_t* counts_dev,
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------
+// Allocation-free variant: the auxiliary arrays live in the library image.
+// ------------------------------------------------------------------------
+namespace bmoe {
+namespace {
+
+// Room for bmoe_worklist_layout_for(BMOE_WORKLIST_STATIC_MAX_EXPERTS): 33792
+// bytes, rounded up. Every GPU that loads the library holds this until exit.
+constexpr size_t kStaticScratchBytes = 34 * 1024;
+static __device__ __align__(256) unsigned char g_worklist_scratch[kStaticScratchBytes];
+
+// In host code `g_worklist_scratch` is only a handle for the runtime, not a
+// device address; the address is looked up once per device, with that device
+// current, and cached here.
+constexpr int kMaxDevices = 64;
+void* g_scratch_address[kMaxDevices] = {};
+
+}  // namespace
+}  // namespace bmoe
+
+extern "C" int bmoe_worklist_build_static(const uint32_t* counts_dev,
+                                          const bmoe_worklist_request* request,
+                                          bmoe_tile* tiles_dev, uint32_t tile_capacity,
+                                          bmoe_worklist_totals* totals_out_dev,
+                                          void* stream) {
+  if (request == nullptr || request->experts == 0 ||
+      request->experts > BMOE_WORKLIST_STATIC_MAX_EXPERTS) {
+    return BMOE_INVALID_ARGUMENT;  // beyond what the fixed array can hold
+  }
+  bmoe_worklist_layout layout;
+  if (bmoe_worklist_layout_for(request->experts, &layout) != BMOE_OK ||
+      layout.bytes > bmoe::kStaticScratchBytes) {
+    return BMOE_INVALID_ARGUMENT;
+  }
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess) return BMOE_CUDA_ERROR;
+  if (device < 0 || device >= bmoe::kMaxDevices) return BMOE_UNSUPPORTED_DEVICE;
+  if (bmoe::g_scratch_address[device] == nullptr) {
+    // First use on this device (keep it outside stream capture).
+    void* address = nullptr;
+    if (cudaGetSymbolAddress(&address, bmoe::g_worklist_scratch) != cudaSuccess ||
+        address == nullptr) {
+      return BMOE_CUDA_ERROR;
+    }
+    bmoe::g_scratch_address[device] = address;
+  }
+  void* const scratch = bmoe::g_scratch_address[device];
+  // The planning kernel writes every array element and every totals field it
+  // or the expansion kernel later reads, so nothing needs clearing here.
+  const int rc = bmoe_worklist_build(counts_dev, request, tiles_dev, tile_capacity,
+                                     scratch, stream);
+  if (rc != BMOE_OK) return rc;
+  if (totals_out_dev != nullptr) {
+    const void* totals = static_cast<const unsigned char*>(scratch) + layout.off_totals;
+    if (cudaMemcpyAsync(totals_out_dev, totals, sizeof(bmoe_worklist_totals),
+                        cudaMemcpyDeviceToDevice,
+                        static_cast<cudaStream_t>(stream)) != cudaSuccess) {
+      return BMOE_CUDA_ERROR;
+    }
+  }
+  return BMOE_OK;
+}

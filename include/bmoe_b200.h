@@ -250,6 +250,40 @@ int bmoe_worklist_build(const uint32_t* counts_dev,
                         bmoe_tile* tiles_dev, uint32_t tile_capacity,
                         void* workspace_dev, void* stream);
 
+/* Largest expert count bmoe_worklist_build_static accepts. */
+#define BMOE_WORKLIST_STATIC_MAX_EXPERTS 1024u
+
+/* Allocation-free variant of bmoe_worklist_build. It has no counterpart in the
+ * reference. It exists for callers that must not allocate device memory at the
+ * point where routing counts become known: code running inside a serving loop
+ * whose memory pool is fixed up front, a plug-in that is handed buffers by its
+ * host framework and is forbidden from calling cudaMalloc (which also
+ * synchronises the device), or a caller that has already handed all free
+ * memory to another allocator. The builder's auxiliary arrays (prefix sums,
+ * active-expert list, visiting order) live in a fixed array inside the library
+ * image instead of a caller-provided workspace; the caller passes only the
+ * inputs and the outputs:
+ *   counts_dev       uint32 [experts]                       (input)
+ *   tiles_dev        bmoe_tile [tile_capacity]              (output)
+ *   totals_out_dev   one bmoe_worklist_totals, may be NULL  (output)
+ * Limits and rules:
+ *   - request->experts <= BMOE_WORKLIST_STATIC_MAX_EXPERTS, otherwise
+ *     BMOE_INVALID_ARGUMENT is returned and nothing is launched. The array
+ *     costs about 34 KB of device memory on every GPU that loads the library,
+ *     for the life of the process.
+ *   - No cudaMalloc / cudaFree or other allocating call is made.
+ *   - The first call on each device looks up the device address of the array
+ *     (cudaGetSymbolAddress); make that first call outside any stream capture.
+ *   - All calls on one device share the array. Every word a call reads from it
+ *     is written by that call first, so stale contents from an earlier call
+ *     are harmless, but two calls whose kernels overlap on the GPU (different
+ *     streams, no ordering between them) race and give undefined results. */
+int bmoe_worklist_build_static(const uint32_t* counts_dev,
+                               const bmoe_worklist_request* request,
+                               bmoe_tile* tiles_dev, uint32_t tile_capacity,
+                               bmoe_worklist_totals* totals_out_dev,
+                               void* stream);
+
 /* ======================================================================== */
 /* 3. Grouped-GEMM plan                                                      */
 /* ======================================================================== */
