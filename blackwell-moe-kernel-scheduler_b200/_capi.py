@@ -288,6 +288,15 @@ SIGNATURES = {
     "bmoe_grouped_gemm": (C.c_int, [_P(GemmArgs)]),
     "bmoe_probe_launch": (C.c_int, [C.c_uint32, _P(ProbeArgs)]),
     "bmoe_probe_scheduler_name": (C.c_char_p, [C.c_uint32]),
+    "bmoe_ep_place_experts": (
+        C.c_int,
+        [_u32p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
+         _u32p, _P(C.c_uint64)],
+    ),
+    "bmoe_gather_rows": (
+        C.c_int,
+        [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint32, C.c_void_p],
+    ),
     "bmoe_build_info": (C.c_char_p, []),
 }
 

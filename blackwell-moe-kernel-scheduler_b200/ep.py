@@ -1,0 +1,222 @@
+"""Expert-parallel layer: experts sharded across ranks, tokens exchanged by
+all-to-all, the local grouped GEMM run by the sm_100a engine.
+
+The reference has no multi-GPU code (agent/search_space.yaml:10-13); this layer
+adds the one exchange step the path needs. One process per GPU
+(``torch.distributed``, NCCL over NVLink); the only collectives are a small
+count all-gather and one all-to-all each side of the GEMM. Remote rows land in
+local HBM through NCCL before any CTA touches them.
+
+Per step and rank:
+  1. count this rank's routed rows per expert, all-gather the counts
+  2. gather token rows into send order (by owner rank, then expert id)
+  3. all-to-all dispatch
+  4. gather received rows (source-major) into the expert-major packed ``A``
+  5. grouped GEMM over the local experts (any scheduling policy)
+  6. inverse gather, all-to-all combine, inverse gather to assignment order
+
+Placement is fixed per deployment (weights live on their owner):
+``place_experts`` balances GEMM tiles per rank.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import Sequence
+
+from . import _capi
+
+
+def place_experts(global_counts: Sequence[int], ranks: int, n: int, *, tile_m: int = 128,
+                  tile_n: int = 256, max_experts_per_rank: int = 0):
+    """Expert -> owner rank by tile-count balance; returns (owner list, tiles per rank)."""
+    experts = len(global_counts)
+    counts = (C.c_uint32 * max(1, experts))(*[int(c) for c in global_counts])
+    owner = (C.c_uint32 * max(1, experts))()
+    loads = (C.c_uint64 * max(1, ranks))()
+    _capi.check(
+        _capi.load().bmoe_ep_place_experts(counts, experts, ranks, n, tile_m, tile_n,
+                                           max_experts_per_rank, owner, loads),
+        "bmoe_ep_place_experts")
+    return [int(x) for x in owner][:experts], [int(x) for x in loads][:ranks]
+
+
+class CudaOps:
+    """Device operations of the layer, all through the engine's C interface."""
+
+    def __init__(self, scheduler="auto", **plan_options):
+        from .engine import GroupedGemmPlan
+
+        self._lib = _capi.load()
+        self._plan = GroupedGemmPlan()
+        self.scheduler = scheduler
+        self.plan_options = plan_options
+        self.launches = 0
+
+    def gather_rows(self, src, index, out=None):
+        import torch
+
+        rows = int(index.numel())
+        width = int(src.shape[1])
+        if out is None:
+            out = torch.empty(rows, width, dtype=src.dtype, device=src.device)
+        if not src.is_cuda:
+            raise RuntimeError("the engine has no CPU path: gather_rows needs CUDA tensors")
+        stream = torch.cuda.current_stream().cuda_stream
+        _capi.check(
+            self._lib.bmoe_gather_rows(src.data_ptr(), out.data_ptr(), index.data_ptr(), rows,
+                                       int(src.shape[0]), width * src.element_size(),
+                                       stream or None),
+            "bmoe_gather_rows")
+        if rows:
+            self.launches += 1
+        return out
+
+    def grouped_gemm(self, a, w, counts, out=None):
+        import torch
+
+        total = int(sum(counts))
+        n = int(w.shape[1])
+        if out is None:
+            out = torch.empty(total, n, dtype=a.dtype, device=a.device)
+        if total == 0:
+            return out
+        stream = torch.cuda.current_stream()
+        _capi.check(self._plan.initialize_packed(a, w, out, counts, scheduler=self.scheduler,
+                                                 stream=stream, **self.plan_options),
+                    "bmoe_plan_initialize")
+        _capi.check(self._plan.run(stream), "bmoe_plan_run")
+        self.launches += 3  # worklist plan + expand, grouped GEMM
+        return out
+
+    def poll(self):
+        status, report = self._plan.poll()
+        if status not in (_capi.OK, _capi.INVALID_ARGUMENT):  # INVALID = never initialised
+            raise _capi.EngineError(status, f"grouped GEMM (site {report.code}, cta {report.cta})")
+
+
+class ExpertParallelLayer:
+    """One expert-parallel grouped GEMM (e.g. an MoE up-projection)."""
+
+    def __init__(self, owner: Sequence[int], n: int, k: int, *, rank: int, world: int,
+                 group=None, ops=None):
+        self.owner = [int(o) for o in owner]
+        self.experts = len(self.owner)
+        self.n, self.k = n, k
+        self.rank, self.world = rank, world
+        self.group = group
+        self.ops = ops if ops is not None else CudaOps()
+        # Experts in send order: by owner rank, then expert id.
+        self.send_order = sorted(range(self.experts), key=lambda e: (self.owner[e], e))
+        self.local_experts = [e for e in range(self.experts) if self.owner[e] == rank]
+        self.timings = {}
+
+    # -- collectives (skipped when there is a single rank) --
+    def _all_gather_counts(self, local_counts):
+        import torch
+        import torch.distributed as dist
+
+        if self.world == 1:
+            return local_counts.reshape(1, -1)
+        flat = torch.empty(self.world * self.experts, dtype=local_counts.dtype,
+                           device=local_counts.device)
+        dist.all_gather_into_tensor(flat, local_counts, group=self.group)
+        return flat.reshape(self.world, self.experts)
+
+    def _all_to_all(self, send, send_splits, recv_splits):
+        import torch
+        import torch.distributed as dist
+
+        if self.world == 1:
+            return send
+        recv = torch.empty(sum(recv_splits), send.shape[1], dtype=send.dtype, device=send.device)
+        dist.all_to_all_single(recv, send, recv_splits, send_splits, group=self.group)
+        return recv
+
+    def forward(self, x, expert_ids, w_local, record_events=False):
+        """x [T_local, k]; expert_ids [T_local, top_k] int64 (device of x);
+        w_local [len(local_experts), n, k] in ascending expert id.
+        Returns y [T_local * top_k, n]: row j is token j // top_k routed to
+        expert_ids.flatten()[j]."""
+        import torch
+
+        dev = x.device
+        top_k = int(expert_ids.shape[1])
+        flat_ids = expert_ids.reshape(-1)
+        assignments = int(flat_ids.numel())
+        marks = []
+
+        def mark(name):
+            if record_events and x.is_cuda:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record(torch.cuda.current_stream())
+                marks.append((name, ev))
+
+        mark("start")
+        # 1. counts
+        local_counts = torch.bincount(flat_ids, minlength=self.experts).to(torch.int64)
+        counts_all = self._all_gather_counts(local_counts).cpu()  # [world, experts], host
+        mine = counts_all[self.rank]
+        send_splits = [0] * self.world
+        for e in range(self.experts):
+            send_splits[self.owner[e]] += int(mine[e])
+        recv_matrix = counts_all[:, self.local_experts]            # [world, E_local]
+        recv_splits = [int(v) for v in recv_matrix.sum(dim=1)]
+        local_m = [int(v) for v in recv_matrix.sum(dim=0)]
+        mark("counts")
+
+        # 2. send order: stable sort of the assignments by position of their expert
+        position = torch.empty(self.experts, dtype=torch.int64)
+        position[torch.tensor(self.send_order, dtype=torch.int64)] = torch.arange(self.experts)
+        keys = position.to(dev)[flat_ids]
+        perm = torch.sort(keys, stable=True).indices               # assignment ids in send order
+        send = self.ops.gather_rows(x, torch.div(perm, top_k, rounding_mode="floor"))
+        mark("pack")
+
+        # 3. dispatch
+        recv = self._all_to_all(send, send_splits, recv_splits)
+        mark("dispatch")
+
+        # 4. source-major -> expert-major. Segment (e, s) of the packed A starts at
+        # recv_offset[s] + prefix of source s over local experts before e.
+        seg_len = recv_matrix.t().contiguous().reshape(-1)          # (e, s) order
+        src_base = torch.cumsum(torch.tensor([0] + recv_splits[:-1], dtype=torch.int64), 0)
+        within = torch.cumsum(recv_matrix, dim=1) - recv_matrix      # [world, E_local]
+        seg_start = (src_base[:, None] + within).t().contiguous().reshape(-1)
+        seg_len_d, seg_start_d = seg_len.to(dev), seg_start.to(dev)
+        total_local = int(sum(local_m))
+        out_start = torch.cumsum(seg_len_d, 0) - seg_len_d
+        index = (torch.repeat_interleave(seg_start_d - out_start, seg_len_d,
+                                         output_size=total_local)
+                 + torch.arange(total_local, device=dev, dtype=torch.int64))
+        a_packed = self.ops.gather_rows(recv, index)
+        mark("unpack")
+
+        # 5. local grouped GEMM
+        d_packed = self.ops.grouped_gemm(a_packed, w_local, local_m)
+        mark("gemm")
+
+        # 6. back: expert-major -> source-major, combine, -> assignment order
+        inverse = torch.empty(total_local, dtype=torch.int64, device=dev)
+        inverse[index] = torch.arange(total_local, device=dev, dtype=torch.int64)
+        d_send = self.ops.gather_rows(d_packed, inverse)
+        mark("repack")
+        d_recv = self._all_to_all(d_send, recv_splits, send_splits)
+        mark("combine")
+        inv_perm = torch.empty(assignments, dtype=torch.int64, device=dev)
+        inv_perm[perm] = torch.arange(assignments, device=dev, dtype=torch.int64)
+        y = self.ops.gather_rows(d_recv, inv_perm)
+        mark("finish")
+        self._marks = marks
+        self.last_local_m = local_m
+        return y
+
+    def phase_times_ms(self):
+        """Per-phase device times of the last forward(record_events=True)."""
+        import torch
+
+        torch.cuda.synchronize()
+        out = {}
+        for (_, a), (name, b) in zip(self._marks[:-1], self._marks[1:]):
+            out[name] = a.elapsed_time(b)
+        return out

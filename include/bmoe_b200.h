@@ -393,6 +393,30 @@ typedef struct bmoe_probe_args {
 int bmoe_probe_launch(uint32_t scheduler, const bmoe_probe_args* args);
 const char* bmoe_probe_scheduler_name(uint32_t scheduler);
 
+/* ======================================================================== */
+/* 5. Expert-parallel helpers (no counterpart in the reference, which has no  */
+/*    multi-GPU code: agent/search_space.yaml:10-13)                          */
+/* ======================================================================== */
+
+/* Expert -> rank placement by tile-count balance. global_counts: host
+ * uint32 [experts], summed over all ranks. Experts are taken in (more tiles
+ * first, lower id first) order and given to the rank with the fewest tiles so
+ * far (lowest rank on ties). max_experts_per_rank == 0 means no cap.
+ * owner_out: host uint32 [experts]; rank_tiles_out: host uint64 [ranks] or NULL. */
+int bmoe_ep_place_experts(const uint32_t* global_counts, uint32_t experts,
+                          uint32_t ranks, uint32_t n, uint32_t tile_m,
+                          uint32_t tile_n, uint32_t max_experts_per_rank,
+                          uint32_t* owner_out, uint64_t* rank_tiles_out);
+
+/* Row gather on the device: dst[i, :] = src[index[i], :], rows of row_bytes
+ * bytes (a multiple of 16; both bases 16-byte aligned). index_dev: int64
+ * [rows]; entries outside [0, src_rows) leave the destination row untouched.
+ * The token permutation either side of the grouped GEMM (dispatch order,
+ * expert-major packing, and their inverses). */
+int bmoe_gather_rows(const void* src_dev, void* dst_dev, const int64_t* index_dev,
+                     uint64_t rows, uint64_t src_rows, uint32_t row_bytes,
+                     void* stream);
+
 /* Library build information ("sm_100a", CUDA runtime version, ...). */
 const char* bmoe_build_info(void);
 
