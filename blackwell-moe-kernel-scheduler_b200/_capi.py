@@ -285,6 +285,7 @@ SIGNATURES = {
     "bmoe_plan_poll": (C.c_int, [C.c_void_p, _P(DeviceReport)]),
     "bmoe_plan_read_worklist": (C.c_int, [C.c_void_p, _P(Tile), C.c_uint32, _u32p]),
     "bmoe_plan_set_observers": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
+    "bmoe_plan_set_trace": (C.c_int, [C.c_void_p, C.c_void_p]),
     "bmoe_grouped_gemm": (C.c_int, [_P(GemmArgs)]),
     "bmoe_probe_launch": (C.c_int, [C.c_uint32, _P(ProbeArgs)]),
     "bmoe_probe_scheduler_name": (C.c_char_p, [C.c_uint32]),

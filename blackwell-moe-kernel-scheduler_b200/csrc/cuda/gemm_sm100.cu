@@ -1,7 +1,8 @@
 // Persistent, warp-specialised BF16 grouped GEMM for sm_100a.
 //
 // One CTA (256 threads) per SM walks a device worklist of 20-byte tile records
-// and computes, per record, a 128 x TILE_N block of
+// and computes, per record, a 128 x TILE_N block (one CTA) or a 256 x TILE_N
+// block (a pair of CTAs in one cluster, tcgen05 cta_group::2) of
 //     D_e[M_e, n] = A_e[M_e, k] * B_e[n, k]^T        (FP32 accumulate, BF16 out)
 // Roles:
 //   warp 0  TMA producer   A box 64x128 + B box 64xTILE_N per 64-wide k-block
@@ -31,9 +32,9 @@ namespace bmoe {
 namespace {
 
 constexpr uint32_t kThreads = 256;
-constexpr uint32_t kTileM = 128;
+constexpr uint32_t kCtaRows = 128;                      // accumulator rows per CTA (TMEM lanes)
 constexpr uint32_t kBlockK = 64;                        // BF16 elements per k-block (128 B)
-constexpr uint32_t kABytes = kTileM * kBlockK * 2;      // 16 KiB
+constexpr uint32_t kABytes = kCtaRows * kBlockK * 2;    // 16 KiB
 constexpr uint32_t kSchedSlots = 4;
 constexpr uint32_t kEpiWarps = 4;
 constexpr uint32_t kStoreCols = 64;                     // columns per TMA store box
@@ -42,11 +43,19 @@ constexpr uint32_t kStoreBytes = kStoreRows * kStoreCols * 2;  // 4 KiB
 constexpr uint32_t kStagingBytes = kEpiWarps * 2 * kStoreBytes;
 constexpr int32_t kSentinel = -1;
 
-template <uint32_t TILE_N>
+// PAIR = false: one CTA computes a 128 x TILE_N tile (tcgen05 cta_group::1).
+// PAIR = true : two CTAs of a cluster compute a 256 x TILE_N tile together
+//               (cta_group::2). Each CTA loads its own 128 rows of A and its
+//               own half (TILE_N / 2 rows) of B and owns 128 accumulator rows;
+//               the even-ranked CTA ("leader") schedules tiles and issues MMAs.
+template <uint32_t TILE_N, bool PAIR>
 struct Config {
-  static constexpr uint32_t kStages = TILE_N == 256 ? 4 : 6;
-  static constexpr uint32_t kBBytes = TILE_N * kBlockK * 2;
-  static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+  static constexpr uint32_t kGroup = PAIR ? 2 : 1;
+  static constexpr uint32_t kBRows = TILE_N / kGroup;           // B rows this CTA loads
+  static constexpr uint32_t kBBytes = kBRows * kBlockK * 2;
+  static constexpr uint32_t kStages = (kABytes + kBBytes) == 49152 ? 4 : 6;
+  static constexpr uint32_t kCtaStageBytes = kABytes + kBBytes;  // bytes this CTA loads
+  static constexpr uint32_t kTxBytes = kCtaStageBytes * kGroup;  // bytes counted on the full barrier
   static constexpr uint32_t kTmemCols = 2 * TILE_N;
   // Offsets from the 1024-byte aligned base of dynamic shared memory.
   static constexpr uint32_t kOffA = 0;
@@ -60,6 +69,9 @@ struct Config {
   static constexpr uint32_t kOffMisc = kOffSlots + kSchedSlots * 32;
   static constexpr uint32_t kBytes = kOffMisc + 32;
   static constexpr uint32_t kDynamicSmem = kBytes + 1024;  // alignment slack
+  // Readers of one tile-info slot: producer + 4 epilogue warps per CTA, plus
+  // the MMA lane of the leader.
+  static constexpr uint32_t kSlotReaders = 5 * kGroup + 1;
 };
 
 struct TileInfo {
@@ -97,10 +109,10 @@ __device__ __forceinline__ void report(const GemmParams& p, uint32_t site,
   }
 }
 
-template <uint32_t TILE_N>
+template <uint32_t TILE_N, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
-  using Cfg = Config<TILE_N>;
+  using Cfg = Config<TILE_N, PAIR>;
   extern __shared__ uint8_t smem_raw[];
   // Swizzled TMA boxes and UMMA descriptors assume 1024-byte aligned tiles.
   const uint32_t raw_addr = ptx::smem_addr(smem_raw);
@@ -127,6 +139,42 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   const uint32_t lane = threadIdx.x & 31;
   const uint64_t budget = p.wait_budget_ns;
 
+  // Position inside the pair and the scheduling unit (CTA or CTA pair).
+  const uint32_t cta_rank = PAIR ? ptx::cluster_cta_rank() : 0u;
+  const bool leader = cta_rank == 0;
+  const uint32_t unit = PAIR ? blockIdx.x / 2 : blockIdx.x;
+  const uint32_t units = PAIR ? gridDim.x / 2 : gridDim.x;
+
+  // Barrier helpers that hide where the barrier lives. In pair mode the
+  // operand-full, accumulator-empty and slot-empty barriers of the LEADER are
+  // the live ones; the peer reaches them through cluster addresses.
+  auto wait = [&](uint32_t bar, uint32_t parity) -> bool {
+    if constexpr (PAIR) {
+      return ptx::mbar_wait_cluster(bar, parity, abort_word, budget);
+    } else {
+      return ptx::mbar_wait(bar, parity, abort_word, budget);
+    }
+  };
+  auto arrive_at_leader = [&](uint32_t bar) {
+    if constexpr (PAIR) {
+      ptx::mbar_arrive_cluster(ptx::map_to_cta(bar, 0));
+    } else {
+      ptx::mbar_arrive(bar);
+    }
+  };
+
+  // Optional per-CTA wait accounting (cycles spent blocked, per role and
+  // barrier kind); costs one predictable branch per wait when disabled.
+  const bool tracing = p.trace != nullptr;
+  auto timed_wait = [&](uint32_t bar, uint32_t parity, uint64_t& bucket) -> bool {
+    if (!tracing) return wait(bar, parity);
+    const long long t0 = clock64();
+    const bool ok = wait(bar, parity);
+    bucket += static_cast<uint64_t>(clock64() - t0);
+    return ok;
+  };
+  const long long kernel_t0 = tracing ? clock64() : 0;
+
   // ------------------------------------------------------------- set-up --
   if (threadIdx.x == 0) {
     for (uint32_t s = 0; s < Cfg::kStages; ++s) {
@@ -135,11 +183,11 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     }
     for (uint32_t b = 0; b < 2; ++b) {
       ptx::mbar_init(bar_tmem_full(b), 1);
-      ptx::mbar_init(bar_tmem_empty(b), kEpiWarps);
+      ptx::mbar_init(bar_tmem_empty(b), kEpiWarps * Cfg::kGroup);
     }
     for (uint32_t s = 0; s < kSchedSlots; ++s) {
       ptx::mbar_init(bar_sched_full(s), 1);
-      ptx::mbar_init(bar_sched_empty(s), 2 + kEpiWarps);  // producer, MMA, 4 epilogue warps
+      ptx::mbar_init(bar_sched_empty(s), Cfg::kSlotReaders);
     }
     ptx::mbar_init(bar_clc, 1);
     misc->abort_word = 0;
@@ -148,38 +196,66 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     ptx::fence_barrier_init();
   }
   if (warp == 1) {
-    ptx::tmem_alloc(base + Cfg::kOffMisc, Cfg::kTmemCols);  // -> misc->tmem_base
-    ptx::tmem_relinquish();
+    if constexpr (PAIR) {
+      ptx::tmem_alloc_pair(base + Cfg::kOffMisc, Cfg::kTmemCols);  // -> misc->tmem_base
+      ptx::tmem_relinquish_pair();
+    } else {
+      ptx::tmem_alloc(base + Cfg::kOffMisc, Cfg::kTmemCols);
+      ptx::tmem_relinquish();
+    }
   }
   ptx::tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (PAIR) {
+    ptx::cluster_sync();  // both CTAs' barriers exist before any remote arrive
+  } else {
+    __syncthreads();
+  }
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = misc->tmem_base;
 
   // ---------------------------------------------------------- scheduler --
   if (warp == 2) {
-    if (lane == 0) {
+    if (lane == 0 && leader) {
       uint32_t published = 0;
       bool alive = true;
-      // Publishes one decoded record (or the sentinel) to the next ring slot.
+      const uint32_t peer_slots = PAIR ? ptx::map_to_cta(base + Cfg::kOffSlots, 1) : 0u;
+      // Publishes one decoded record (or the sentinel) to the next ring slot
+      // (of both CTAs in pair mode).
       auto publish = [&](int32_t tile_index) -> bool {
         const uint32_t slot = published % kSchedSlots;
         const uint32_t round = (published / kSchedSlots) & 1u;
-        if (!ptx::mbar_wait(bar_sched_empty(slot), round ^ 1u, abort_word, budget)) {
+        if (!wait(bar_sched_empty(slot), round ^ 1u)) {
           report(p, kSiteSchedSlot, 0, static_cast<uint32_t>(tile_index), slot, published);
           return false;
         }
-        volatile TileInfo* info = &slots[slot];
-        info->tile = tile_index;
+        TileInfo rec{};
+        rec.tile = tile_index;
         if (tile_index != kSentinel) {
-          const bmoe_tile rec = p.tiles[tile_index];
-          info->expert = rec.expert_id;
-          info->row0 = rec.tile_m * kTileM;
-          info->col0 = rec.tile_n * TILE_N;
-          info->valid_m = rec.valid_m;
-          info->valid_n = rec.valid_n;
+          const bmoe_tile t = p.tiles[tile_index];
+          rec.expert = t.expert_id;
+          rec.row0 = t.tile_m * (kCtaRows * Cfg::kGroup);
+          rec.col0 = t.tile_n * TILE_N;
+          rec.valid_m = t.valid_m;
+          rec.valid_n = t.valid_n;
         }
+        volatile TileInfo* info = &slots[slot];
+        info->tile = rec.tile;
+        info->expert = rec.expert;
+        info->row0 = rec.row0;
+        info->col0 = rec.col0;
+        info->valid_m = rec.valid_m;
+        info->valid_n = rec.valid_n;
         ptx::mbar_arrive(bar_sched_full(slot));
+        if constexpr (PAIR) {
+          const uint32_t remote = peer_slots + slot * 32;
+          ptx::st_cluster_u32(remote + 0, static_cast<uint32_t>(rec.tile));
+          ptx::st_cluster_u32(remote + 4, rec.expert);
+          ptx::st_cluster_u32(remote + 8, rec.row0);
+          ptx::st_cluster_u32(remote + 12, rec.col0);
+          ptx::st_cluster_u32(remote + 16, rec.valid_m);
+          ptx::st_cluster_u32(remote + 20, rec.valid_n);
+          ptx::mbar_arrive_cluster(ptx::map_to_cta(bar_sched_full(slot), 1));  // release
+        }
         ++published;
         return true;
       };
@@ -206,7 +282,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       };
 
       if (p.sched_mode == kSchedStatic) {
-        for (uint32_t t = blockIdx.x; alive && t < p.tile_count; t += gridDim.x) {
+        for (uint32_t t = unit; alive && t < p.tile_count; t += units) {
           alive = publish(static_cast<int32_t>(t));
         }
       } else if (p.sched_mode == kSchedQueue) {
@@ -228,9 +304,9 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           if (t >= p.tile_count) break;
           alive = publish(static_cast<int32_t>(t));
         }
-      } else {  // kSchedClc
+      } else {  // kSchedClc: one CTA (pair) per tile, steal units not yet started
         uint32_t clc_round = 0;
-        uint32_t t = blockIdx.x;
+        uint32_t t = unit;
         if (t < p.tile_count) alive = publish(static_cast<int32_t>(t));
         while (alive) {
           if (!pace()) { alive = false; break; }
@@ -245,8 +321,8 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           uint32_t stolen = 0;
           const bool got = ptx::clc_query(clc_response, &stolen);
           ptx::fence_async_shared();
-          if (!got) break;  // no pending CTA left; must not ask again
-          t = stolen;
+          if (!got) break;  // no pending unit left; must not ask again
+          t = PAIR ? stolen / 2 : stolen;
           if (t < p.tile_count) alive = publish(static_cast<int32_t>(t));
         }
       }
@@ -261,20 +337,21 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       uint32_t reads = 0;
       uint32_t stage = 0, stage_round = 0;
       uint32_t last_expert = 0xffffffffu;
+      uint64_t t_info = 0, t_stage = 0;
       while (true) {
         const uint32_t slot = reads % kSchedSlots;
         const uint32_t round = (reads / kSchedSlots) & 1u;
-        if (!ptx::mbar_wait(bar_sched_full(slot), round, abort_word, budget)) {
+        if (!timed_wait(bar_sched_full(slot), round, t_info)) {
           report(p, kSiteProducerInfo, 1, reads, slot, 0);
           break;
         }
         const int32_t tile = slots[slot].tile;
         const uint32_t expert = slots[slot].expert;
-        const uint32_t row0 = slots[slot].row0;
-        const uint32_t col0 = slots[slot].col0;
-        ptx::mbar_arrive(bar_sched_empty(slot));
+        const uint32_t row0 = slots[slot].row0 + cta_rank * kCtaRows;
+        const uint32_t col0 = slots[slot].col0 + cta_rank * Cfg::kBRows;
+        arrive_at_leader(bar_sched_empty(slot));
         ++reads;
-        misc->producer_reads = reads;
+        if (leader) misc->producer_reads = reads;
         if (tile == kSentinel) break;
 
         const CUtensorMap* const map_a = p.tmap_a + expert;
@@ -286,19 +363,32 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         }
         bool ok = true;
         for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
-          if (!ptx::mbar_wait(bar_empty(stage), stage_round ^ 1u, abort_word, budget)) {
+          if (!timed_wait(bar_empty(stage), stage_round ^ 1u, t_stage)) {
             report(p, kSiteProducerStage, 1, static_cast<uint32_t>(tile), stage, kb);
             ok = false;
             break;
           }
-          ptx::mbar_arrive_expect_tx(bar_full(stage), Cfg::kStageBytes);
-          ptx::tma_load_2d(base + Cfg::kOffA + stage * kABytes, map_a, bar_full(stage),
-                           static_cast<int32_t>(kb * kBlockK), static_cast<int32_t>(row0));
-          ptx::tma_load_2d(base + Cfg::kOffB + stage * Cfg::kBBytes, map_b, bar_full(stage),
-                           static_cast<int32_t>(kb * kBlockK), static_cast<int32_t>(col0));
+          const uint32_t dst_a = base + Cfg::kOffA + stage * kABytes;
+          const uint32_t dst_b = base + Cfg::kOffB + stage * Cfg::kBBytes;
+          const int32_t k0 = static_cast<int32_t>(kb * kBlockK);
+          if constexpr (PAIR) {
+            // Both CTAs' bytes are counted on the leader's barrier.
+            if (leader) ptx::mbar_arrive_expect_tx(bar_full(stage), Cfg::kTxBytes);
+            const uint32_t full = ptx::map_to_cta(bar_full(stage), 0);
+            ptx::tma_load_2d_pair(dst_a, map_a, full, k0, static_cast<int32_t>(row0));
+            ptx::tma_load_2d_pair(dst_b, map_b, full, k0, static_cast<int32_t>(col0));
+          } else {
+            ptx::mbar_arrive_expect_tx(bar_full(stage), Cfg::kTxBytes);
+            ptx::tma_load_2d(dst_a, map_a, bar_full(stage), k0, static_cast<int32_t>(row0));
+            ptx::tma_load_2d(dst_b, map_b, bar_full(stage), k0, static_cast<int32_t>(col0));
+          }
           if (++stage == Cfg::kStages) { stage = 0; stage_round ^= 1u; }
         }
         if (!ok) break;
+      }
+      if (tracing) {
+        p.trace[blockIdx.x * kTraceWords + 0] = t_info;
+        p.trace[blockIdx.x * kTraceWords + 1] = t_stage;
       }
     }
     __syncwarp();
@@ -306,15 +396,16 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
 
   // ---------------------------------------------------------------- MMA --
   else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = ptx::make_bf16_idesc(kTileM, TILE_N);
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = ptx::make_bf16_idesc(kCtaRows * Cfg::kGroup, TILE_N);
       uint32_t reads = 0;
       uint32_t stage = 0, stage_round = 0;
       uint32_t buf = 0, buf_round = 0;
+      uint64_t t_info = 0, t_accum = 0, t_operands = 0;
       while (true) {
         const uint32_t slot = reads % kSchedSlots;
         const uint32_t round = (reads / kSchedSlots) & 1u;
-        if (!ptx::mbar_wait(bar_sched_full(slot), round, abort_word, budget)) {
+        if (!timed_wait(bar_sched_full(slot), round, t_info)) {
           report(p, kSiteMmaInfo, 2, reads, slot, 0);
           break;
         }
@@ -323,8 +414,8 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         ++reads;
         if (tile == kSentinel) break;
 
-        // The epilogue must have drained this accumulator buffer.
-        if (!ptx::mbar_wait(bar_tmem_empty(buf), buf_round ^ 1u, abort_word, budget)) {
+        // The epilogue(s) must have drained this accumulator buffer.
+        if (!timed_wait(bar_tmem_empty(buf), buf_round ^ 1u, t_accum)) {
           report(p, kSiteMmaAccum, 2, static_cast<uint32_t>(tile), buf, 0);
           break;
         }
@@ -332,7 +423,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         const uint32_t d_tmem = tmem_base + buf * TILE_N;
         bool ok = true;
         for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
-          if (!ptx::mbar_wait(bar_full(stage), stage_round, abort_word, budget)) {
+          if (!timed_wait(bar_full(stage), stage_round, t_operands)) {
             report(p, kSiteMmaStage, 2, static_cast<uint32_t>(tile), stage, kb);
             ok = false;
             break;
@@ -345,15 +436,36 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
 #pragma unroll
           for (uint32_t ks = 0; ks < kBlockK / 16; ++ks) {
             // 16 BF16 = 32 bytes along k inside the 128-byte swizzle row.
-            ptx::umma_bf16_ss(d_tmem, a_desc + 2 * ks, b_desc + 2 * ks, idesc,
-                              (kb | ks) != 0 ? 1u : 0u);
+            const uint32_t acc = (kb | ks) != 0 ? 1u : 0u;
+            if constexpr (PAIR) {
+              ptx::umma_bf16_ss_pair(d_tmem, a_desc + 2 * ks, b_desc + 2 * ks, idesc, acc);
+            } else {
+              ptx::umma_bf16_ss(d_tmem, a_desc + 2 * ks, b_desc + 2 * ks, idesc, acc);
+            }
           }
-          ptx::umma_commit(bar_empty(stage));  // stage reusable once these MMAs retire
+          // The stage is reusable (in both CTAs) once these MMAs retire.
+          if constexpr (PAIR) {
+            ptx::umma_commit_pair(bar_empty(stage));
+            ptx::umma_commit_pair(ptx::map_to_cta(bar_empty(stage), 1));
+          } else {
+            ptx::umma_commit(bar_empty(stage));
+          }
           if (++stage == Cfg::kStages) { stage = 0; stage_round ^= 1u; }
         }
         if (!ok) break;
-        ptx::umma_commit(bar_tmem_full(buf));  // accumulator complete
+        // Accumulator complete: wake the epilogue of both CTAs.
+        if constexpr (PAIR) {
+          ptx::umma_commit_pair(bar_tmem_full(buf));
+          ptx::umma_commit_pair(ptx::map_to_cta(bar_tmem_full(buf), 1));
+        } else {
+          ptx::umma_commit(bar_tmem_full(buf));
+        }
         if (++buf == 2) { buf = 0; buf_round ^= 1u; }
+      }
+      if (tracing) {
+        p.trace[blockIdx.x * kTraceWords + 2] = t_info;
+        p.trace[blockIdx.x * kTraceWords + 3] = t_accum;
+        p.trace[blockIdx.x * kTraceWords + 4] = t_operands;
       }
     }
     __syncwarp();
@@ -363,15 +475,17 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   else if (warp >= 4) {
     const uint32_t quad = warp & 3u;  // TMEM lane quadrant this warp may read
     const uint32_t staging = base + Cfg::kOffStaging + quad * 2 * kStoreBytes;
+    const uint32_t row_in_tile = cta_rank * kCtaRows + quad * kStoreRows;
     uint32_t reads = 0;
     uint32_t buf = 0, buf_round = 0;
     uint32_t sbuf = 0;
     uint32_t last_expert = 0xffffffffu;
     uint32_t tiles_done = 0;
+    uint64_t t_info = 0, t_accum = 0, t_drain = 0;
     while (true) {
       const uint32_t slot = reads % kSchedSlots;
       const uint32_t round = (reads / kSchedSlots) & 1u;
-      if (!ptx::mbar_wait(bar_sched_full(slot), round, abort_word, budget)) {
+      if (!timed_wait(bar_sched_full(slot), round, t_info)) {
         if (lane == 0 && quad == 0) report(p, kSiteEpiInfo, 3, reads, slot, 0);
         break;
       }
@@ -382,11 +496,11 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       const uint32_t valid_m = slots[slot].valid_m;
       const uint32_t valid_n = slots[slot].valid_n;
       __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(bar_sched_empty(slot));
+      if (lane == 0) arrive_at_leader(bar_sched_empty(slot));
       ++reads;
       if (tile == kSentinel) break;
 
-      if (!ptx::mbar_wait(bar_tmem_full(buf), buf_round, abort_word, budget)) {
+      if (!timed_wait(bar_tmem_full(buf), buf_round, t_accum)) {
         if (lane == 0 && quad == 0) {
           report(p, kSiteEpiAccum, 3, static_cast<uint32_t>(tile), buf, 0);
         }
@@ -398,9 +512,10 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       if (lane == 0 && expert != last_expert) ptx::tensormap_acquire(map_d);
       last_expert = expert;
 
-      const bool has_rows = quad * kStoreRows < valid_m;
+      const bool has_rows = row_in_tile < valid_m;
       const uint32_t chunks = has_rows ? (valid_n + kStoreCols - 1) / kStoreCols : 0;
       const uint32_t lane_taddr = tmem_base + ((quad * 32u) << 16) + buf * TILE_N;
+      const long long drain_t0 = tracing ? clock64() : 0;
       for (uint32_t c = 0; c < chunks; ++c) {
         uint32_t lo[32], hi[32];
         ptx::tmem_load_32x32(lane_taddr + c * kStoreCols, lo);
@@ -411,7 +526,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           // buffer back before the (slower) conversion and store.
           ptx::tc_fence_before_sync();
           __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(bar_tmem_empty(buf));
+          if (lane == 0) arrive_at_leader(bar_tmem_empty(buf));
         }
         // The store issued two chunks ago read from this staging buffer.
         if (lane == 0) ptx::tma_store_wait_read<1>();
@@ -441,7 +556,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         if (lane == 0) {
           ptx::tma_store_2d(map_d, staging + sbuf * kStoreBytes,
                             static_cast<int32_t>(col0 + c * kStoreCols),
-                            static_cast<int32_t>(row0 + quad * kStoreRows));
+                            static_cast<int32_t>(row0 + row_in_tile));
           ptx::tma_store_commit();
         }
         sbuf ^= 1u;
@@ -450,16 +565,23 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         // Nothing to read for this warp (rows beyond the ragged edge).
         ptx::tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(bar_tmem_empty(buf));
+        if (lane == 0) arrive_at_leader(bar_tmem_empty(buf));
       }
+      if (tracing) t_drain += static_cast<uint64_t>(clock64() - drain_t0);
       if (++buf == 2) { buf = 0; buf_round ^= 1u; }
       ++tiles_done;
-      if (quad == 0 && lane == 0 && p.tile_visits != nullptr) {
+      if (leader && quad == 0 && lane == 0 && p.tile_visits != nullptr) {
         atomicAdd(&p.tile_visits[tile], 1u);
       }
     }
     if (lane == 0) ptx::tma_store_wait_all();
     if (quad == 0 && lane == 0) misc->tiles_done = tiles_done;
+    if (tracing && quad == 0 && lane == 0) {
+      p.trace[blockIdx.x * kTraceWords + 5] = t_info;
+      p.trace[blockIdx.x * kTraceWords + 6] = t_accum;
+      p.trace[blockIdx.x * kTraceWords + 7] = t_drain;
+      p.trace[blockIdx.x * kTraceWords + 8] = tiles_done;
+    }
     __syncwarp();
   }
 
@@ -471,18 +593,31 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     while (ptx::global_timer_ns() - start < 200000) __nanosleep(1000);
   }
   ptx::tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (PAIR) {
+    // Neither CTA may leave while its partner can still touch its shared
+    // memory (remote arrives, the pair MMA reading both operand halves).
+    ptx::cluster_sync();
+  } else {
+    __syncthreads();
+  }
   ptx::tc_fence_after_sync();
   if (warp == 1) {
-    ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    if constexpr (PAIR) {
+      ptx::tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
+    } else {
+      ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
   }
-  if (threadIdx.x == 0) {
-    if (p.cta_tiles != nullptr) p.cta_tiles[blockIdx.x] = misc->tiles_done;
+  if (tracing && threadIdx.x == 0) {
+    p.trace[blockIdx.x * kTraceWords + 9] = static_cast<uint64_t>(clock64() - kernel_t0);
+  }
+  if (threadIdx.x == 0 && leader) {
+    if (p.cta_tiles != nullptr) p.cta_tiles[unit] = misc->tiles_done;
     if (p.sched_mode == kSchedQueue) {
-      // The last CTA to leave rearms the queue for the next launch.
+      // The last unit to leave rearms the queue for the next launch.
       __threadfence();
       const uint32_t exited = atomicAdd(&p.queue[2], 1u);
-      if (exited + 1 == gridDim.x) {
+      if (exited + 1 == units) {
         p.queue[0] = 0;
         p.queue[1] = p.main_end;
         p.queue[2] = 0;
@@ -492,40 +627,55 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   }
 }
 
-template <uint32_t TILE_N>
-cudaError_t launch_impl(const GemmParams& params, uint32_t grid, cudaStream_t stream) {
-  using Cfg = Config<TILE_N>;
+template <uint32_t TILE_N, bool PAIR>
+cudaError_t launch_impl(const GemmParams& params, uint32_t units, cudaStream_t stream) {
+  using Cfg = Config<TILE_N, PAIR>;
   // The opt-in shared-memory size is a per-device function attribute.
   static bool configured[64] = {};
   int device = 0;
   cudaError_t err = cudaGetDevice(&device);
   if (err != cudaSuccess) return err;
   if (device < 0 || device >= 64 || !configured[device]) {
-    err = cudaFuncSetAttribute(grouped_gemm_kernel<TILE_N>,
+    err = cudaFuncSetAttribute(grouped_gemm_kernel<TILE_N, PAIR>,
                                cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(Cfg::kDynamicSmem));
     if (err != cudaSuccess) return err;
     if (device >= 0 && device < 64) configured[device] = true;
   }
-  grouped_gemm_kernel<TILE_N><<<grid, kThreads, Cfg::kDynamicSmem, stream>>>(params);
-  return cudaPeekAtLastError();
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(units * Cfg::kGroup);
+  config.blockDim = dim3(kThreads);
+  config.dynamicSmemBytes = Cfg::kDynamicSmem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeClusterDimension;
+  attribute[0].val.clusterDim.x = Cfg::kGroup;
+  attribute[0].val.clusterDim.y = 1;
+  attribute[0].val.clusterDim.z = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  err = cudaLaunchKernelEx(&config, grouped_gemm_kernel<TILE_N, PAIR>, params);
+  return err != cudaSuccess ? err : cudaPeekAtLastError();
 }
 
 }  // namespace
 
-uint32_t gemm_smem_bytes(uint32_t tile_n) {
-  return tile_n == 256 ? Config<256>::kDynamicSmem : Config<128>::kDynamicSmem;
+uint32_t gemm_smem_bytes(uint32_t tile_n, uint32_t cta_group) {
+  if (cta_group == 2) return Config<256, true>::kDynamicSmem;
+  return tile_n == 256 ? Config<256, false>::kDynamicSmem : Config<128, false>::kDynamicSmem;
 }
 
-uint32_t gemm_stage_count(uint32_t tile_n) {
-  return tile_n == 256 ? Config<256>::kStages : Config<128>::kStages;
+uint32_t gemm_stage_count(uint32_t tile_n, uint32_t cta_group) {
+  if (cta_group == 2) return Config<256, true>::kStages;
+  return tile_n == 256 ? Config<256, false>::kStages : Config<128, false>::kStages;
 }
 
 cudaError_t launch_grouped_gemm(const GemmParams& params, uint32_t tile_n,
-                                uint32_t grid, cudaStream_t stream) {
-  if (grid == 0) return cudaSuccess;
-  if (tile_n == 256) return launch_impl<256>(params, grid, stream);
-  if (tile_n == 128) return launch_impl<128>(params, grid, stream);
+                                uint32_t cta_group, uint32_t units, cudaStream_t stream) {
+  if (units == 0) return cudaSuccess;
+  if (cta_group == 2 && tile_n == 256) return launch_impl<256, true>(params, units, stream);
+  if (cta_group == 1 && tile_n == 256) return launch_impl<256, false>(params, units, stream);
+  if (cta_group == 1 && tile_n == 128) return launch_impl<128, false>(params, units, stream);
   return cudaErrorInvalidValue;
 }
 

@@ -45,7 +45,7 @@ struct DeviceStatus {
 
 struct GemmParams {
   const CUtensorMap* tmap_a;  // [experts] A_e as {k, M_e}, box {64, 128}
-  const CUtensorMap* tmap_b;  // [experts] B_e as {k, n},   box {64, TILE_N}
+  const CUtensorMap* tmap_b;  // [experts] B_e as {k, n},   box {64, TILE_N / cta_group}
   const CUtensorMap* tmap_d;  // [experts] D_e as {n, M_e}, box {64, 32}
   const bmoe_tile* tiles;     // device worklist
   uint32_t tile_count;
@@ -58,15 +58,26 @@ struct GemmParams {
   DeviceStatus* status;
   uint32_t* tile_visits;      // optional [tile_count]
   uint32_t* cta_tiles;        // optional [gridDim.x]
+  uint64_t* trace;            // optional [gridDim.x][kTraceWords] wait accounting
   uint64_t wait_budget_ns;
 };
 
-// Dynamic shared memory the kernel needs for a tile width (128 or 256).
-uint32_t gemm_smem_bytes(uint32_t tile_n);
-uint32_t gemm_stage_count(uint32_t tile_n);
+// Words per CTA of GemmParams::trace (SM cycles):
+//   0 producer waiting for tile info      1 producer waiting for a free stage
+//   2 MMA waiting for tile info           3 MMA waiting for a drained accumulator
+//   4 MMA waiting for operand bytes       5 epilogue waiting for tile info
+//   6 epilogue waiting for an accumulator 7 epilogue draining (ld, convert, store)
+//   8 tiles run by this CTA               9 kernel cycles of this CTA
+constexpr uint32_t kTraceWords = 16;
 
-// Enqueues the kernel. grid = persistent CTAs (or the tile count for CLC).
+// Dynamic shared memory / operand stages for a tile width (128 or 256) and CTA
+// group (1 = single CTA, 2 = CTA pair computing 256-row tiles; needs tile_n 256).
+uint32_t gemm_smem_bytes(uint32_t tile_n, uint32_t cta_group);
+uint32_t gemm_stage_count(uint32_t tile_n, uint32_t cta_group);
+
+// Enqueues the kernel on `units` scheduling units: persistent CTAs (or CTA
+// pairs), or the tile count for CLC. The grid is units * cta_group CTAs.
 cudaError_t launch_grouped_gemm(const GemmParams& params, uint32_t tile_n,
-                                uint32_t grid, cudaStream_t stream);
+                                uint32_t cta_group, uint32_t units, cudaStream_t stream);
 
 }  // namespace bmoe

@@ -103,8 +103,9 @@ struct bmoe_plan {
   std::vector<uint32_t> host_counts;
 
   bmoe::GemmParams params{};
-  uint32_t grid = 0;
+  uint32_t units = 0;      // persistent CTAs or CTA pairs (tile count for CLC)
   uint32_t tile_n = 0;
+  uint32_t cta_group = 1;
 
   void release_all() {
     counts.release();
@@ -216,7 +217,9 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
   if (a.scheduler > BMOE_SCHED_CLC) return BMOE_UNSUPPORTED_SCHEDULER;
   if (a.experts > BMOE_WORKLIST_MAX_EXPERTS) return BMOE_INVALID_ARGUMENT;
   if (a.tile_n != 0 && a.tile_n != 128 && a.tile_n != 256) return BMOE_INVALID_ARGUMENT;
-  if (a.cta_group > 1) return BMOE_INVALID_ARGUMENT;
+  if (a.cta_group > 2) return BMOE_INVALID_ARGUMENT;
+  // CTA pairs compute 256 x 256 tiles; a narrower tile has no pair variant.
+  if (a.cta_group == 2 && a.tile_n != 0 && a.tile_n != 256) return BMOE_INVALID_ARGUMENT;
 
   int device = 0, major = 0, minor = 0, sm_count = 0;
   if (cudaGetDevice(&device) != cudaSuccess ||
@@ -252,15 +255,18 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
   }
 
   // ---- engine configuration ----
-  const uint32_t tile_m = 128;
-  const uint32_t tile_n = a.tile_n != 0 ? a.tile_n : (a.n <= 128 ? 128u : 256u);
+  const uint32_t cta_group = a.cta_group == 2 ? 2u : 1u;
+  const uint32_t tile_m = 128 * cta_group;
+  const uint32_t tile_n =
+      cta_group == 2 ? 256u : (a.tile_n != 0 ? a.tile_n : (a.n <= 128 ? 128u : 256u));
   const uint32_t raster =
       a.raster_along_m < 0 ? BMOE_RASTER_M_FASTEST
                            : (a.raster_along_m != 0 ? BMOE_RASTER_M_FASTEST
                                                     : BMOE_RASTER_N_FASTEST);
-  const uint32_t cta_budget =
-      a.cta_count != 0 ? a.cta_count : static_cast<uint32_t>(sm_count);
-  const Resolved policy = resolve_policy(a, tile_m, tile_n, cta_budget);
+  // Scheduling units: persistent CTAs, or CTA pairs (one per two SMs).
+  const uint32_t sm_units = static_cast<uint32_t>(sm_count) / cta_group;
+  const uint32_t unit_budget = a.cta_count != 0 ? a.cta_count : (sm_units ? sm_units : 1u);
+  const Resolved policy = resolve_policy(a, tile_m, tile_n, unit_budget);
 
   const uint64_t tile_total =
       bmoe_host_tile_count(a.tokens_per_expert, a.experts, a.n, tile_m, tile_n);
@@ -313,7 +319,7 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
     const uint64_t rows = a.tokens_per_expert[e];
     if (rows == 0) continue;
     if (!encode_bf16_matrix(&maps_a[e], a.a[e], rows, a.k, 128) ||
-        !encode_bf16_matrix(&maps_b[e], a.b[e], a.n, a.k, tile_n) ||
+        !encode_bf16_matrix(&maps_b[e], a.b[e], a.n, a.k, tile_n / cta_group) ||
         !encode_bf16_matrix(&maps_d[e], a.d[e], rows, a.n, 32)) {
       return BMOE_CUDA_ERROR;
     }
@@ -357,9 +363,10 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
   p.wait_budget_ns = 1000000000ull;  // 1 s per wait, then the kernel gives up
 
   plan->tile_n = tile_n;
-  plan->grid = policy.one_cta_per_tile ? tiles : (tiles < cta_budget ? tiles : cta_budget);
+  plan->cta_group = cta_group;
+  plan->units = policy.one_cta_per_tile ? tiles : (tiles < unit_budget ? tiles : unit_budget);
 
-  plan->stats.threadblock_count = plan->grid;
+  plan->stats.threadblock_count = plan->units * cta_group;
   plan->stats.workspace_bytes = plan->counts.bytes + plan->tmaps.bytes +
                                 plan->worklist.bytes + plan->workspace.bytes +
                                 plan->control.bytes;
@@ -369,9 +376,9 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
   plan->stats.resolved_scheduler = policy.scheduler;
   plan->stats.claim_size = policy.claim_size;
   plan->stats.hybrid_tail_tiles = tail;
-  plan->stats.cta_group = 1;
-  plan->stats.stages = bmoe::gemm_stage_count(tile_n);
-  plan->stats.dynamic_smem_bytes = bmoe::gemm_smem_bytes(tile_n);
+  plan->stats.cta_group = cta_group;
+  plan->stats.stages = bmoe::gemm_stage_count(tile_n, cta_group);
+  plan->stats.dynamic_smem_bytes = bmoe::gemm_smem_bytes(tile_n, cta_group);
   plan->stats.launches = 0;
   plan->ready = true;
   return BMOE_OK;
@@ -387,7 +394,7 @@ int bmoe_plan_run(bmoe_plan* plan, void* stream) {
     return BMOE_CUDA_ERROR;
   }
   const cudaError_t err =
-      bmoe::launch_grouped_gemm(plan->params, plan->tile_n, plan->grid, s);
+      bmoe::launch_grouped_gemm(plan->params, plan->tile_n, plan->cta_group, plan->units, s);
   plan->last_stream = s;
   if (err != cudaSuccess) return BMOE_CUDA_ERROR;
   plan->stats.launches += 1;
@@ -448,6 +455,12 @@ int bmoe_plan_set_observers(bmoe_plan* plan, uint32_t* tile_visits_dev,
   if (plan == nullptr || !plan->ready) return BMOE_INVALID_ARGUMENT;
   plan->params.tile_visits = tile_visits_dev;
   plan->params.cta_tiles = cta_tiles_dev;
+  return BMOE_OK;
+}
+
+int bmoe_plan_set_trace(bmoe_plan* plan, uint64_t* trace_dev) {
+  if (plan == nullptr || !plan->ready) return BMOE_INVALID_ARGUMENT;
+  plan->params.trace = trace_dev;
   return BMOE_OK;
 }
 

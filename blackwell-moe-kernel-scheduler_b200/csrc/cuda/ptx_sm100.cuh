@@ -237,6 +237,126 @@ __device__ __forceinline__ void tmem_load_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// ------------------------------------------------------- CTA pair (cluster) --
+// Two CTAs of one cluster act as a pair ("cta_group::2"): the even-ranked CTA
+// issues one 256-row MMA over both CTAs' operand tiles and accumulators.
+
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+
+// Address of the same shared-memory location in CTA `rank` of this cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_smem, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem), "r"(rank));
+  return remote;
+}
+
+// All threads of every CTA in the cluster.
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// Arrive on an mbarrier given by a cluster-wide shared address (own or peer CTA).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar)
+               : "memory");
+}
+
+__device__ __forceinline__ bool mbar_test_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+
+// mbar_wait with cluster-scope acquire (arrivals may come from the peer CTA).
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
+                                                  volatile uint32_t* abort_word,
+                                                  uint64_t budget_ns) {
+  if (mbar_test_cluster(bar, parity)) return true;
+  uint64_t start = 0;
+  for (uint32_t spin = 1;; ++spin) {
+    if (mbar_test_cluster(bar, parity)) return true;
+    if ((spin & 0x3f) == 0) {
+      if (*abort_word != 0) return false;
+      const uint64_t now = global_timer_ns();
+      if (start == 0) {
+        start = now;
+      } else if (now - start > budget_ns) {
+        *abort_word = 1;
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t value) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(value) : "memory");
+}
+
+// Pair form of tma_load_2d: the destination is this CTA's shared memory, the
+// mbarrier may belong to the peer CTA (cluster-wide address). No multicast.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst_smem, const void* tmap,
+                                                 uint32_t cluster_bar, int32_t c0, int32_t c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];" ::"r"(dst_smem),
+      "l"(tmap), "r"(cluster_bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t columns) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   dst_smem),
+               "r"(columns)
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t columns) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr),
+               "r"(columns)
+               : "memory");
+}
+
+// 256 x N x 16 MMA over both CTAs of the pair; issued by one thread of the
+// even-ranked CTA. Descriptors name the same offsets in both CTAs' memories.
+__device__ __forceinline__ void umma_bf16_ss_pair(uint32_t d_tmem, uint64_t a_desc,
+                                                  uint64_t b_desc, uint32_t idesc,
+                                                  uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Arrives on ONE mbarrier (cluster-wide address, own or peer CTA) once all
+// pair MMAs issued so far by this thread have finished.
+__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+          cluster_bar)
+      : "memory");
+}
+
 // ---------------------------------------------------- cluster launch control --
 
 // Asks the hardware to cancel one not-yet-started CTA of this grid. The

@@ -171,6 +171,13 @@ class GroupedGemmPlan:
         ))
 
 
+    def set_trace(self, trace=None) -> int:
+        """``trace``: CUDA int64 tensor [threadblock_count, 16] of wait-cycle counters."""
+        self._trace = trace
+        return int(self._lib.bmoe_plan_set_trace(
+            self._handle, trace.data_ptr() if trace is not None else None))
+
+
 def grouped_gemm(a, w, d, tokens_per_expert: Sequence[int], **options) -> None:
     """One-shot packed grouped GEMM on the current CUDA device; raises on error."""
     plan = GroupedGemmPlan()

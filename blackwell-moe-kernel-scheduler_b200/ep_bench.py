@@ -69,13 +69,14 @@ def run(args, spec, workload):
     n, k, top_k, tokens = spec["n"], spec["k"], spec["top_k"], spec["tokens"]
     ids_all = _routing(torch, spec)
     global_counts = torch.bincount(ids_all.reshape(-1), minlength=spec["experts"]).tolist()
-    owner, rank_tiles = ep.place_experts(global_counts, world, n, tile_m=128, tile_n=256)
+    owner, rank_tiles = ep.place_experts(global_counts, world, n, tile_m=128 * args.cta_group,
+                                         tile_n=256)
     lo, hi = tokens * rank // world, tokens * (rank + 1) // world
     ids_local = ids_all[lo:hi].to(dev)
     gen = torch.Generator(device=dev).manual_seed(4000 + rank)
     x_local = torch.randn(hi - lo, k, generator=gen, device=dev,
                           dtype=torch.float32).to(torch.bfloat16)
-    ops = ep.CudaOps(scheduler=args.policy)
+    ops = ep.CudaOps(scheduler=args.policy, cta_group=args.cta_group)
     layer = ep.ExpertParallelLayer(owner, n, k, rank=rank, world=world, ops=ops)
     w_local = _expert_weights(torch, layer.local_experts, n, k, dev)
     total_flops = 2.0 * tokens * top_k * n * k

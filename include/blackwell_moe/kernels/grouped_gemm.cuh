@@ -40,11 +40,13 @@ struct GroupedGemmArguments {
   // kDynamicQueue only: the last `hybrid_tail_tiles` tiles are claimed one at a
   // time from a second counter, the rest in chunks of claim_size.
   std::uint32_t hybrid_tail_tiles = 0;
-  // Persistent CTAs to launch (default: one per SM). Ignored by kClc.
+  // Persistent scheduling units to launch: CTAs, or CTA pairs when cta_group
+  // is 2 (default: one CTA per SM). Ignored by kClc.
   std::uint32_t cta_count = 0;
   // Output tile width: 128 or 256 (default 256). Tile height is 128 per CTA.
   std::uint32_t tile_n = 0;
-  // 1 = one CTA per tile, 2 = two-CTA cluster tiles of 256 rows (default 1).
+  // 1 = one CTA computes a 128-row tile; 2 = two CTAs of a cluster compute a
+  // 256 x 256 tile together (default 1).
   std::uint32_t cta_group = 0;
   // 0 = worklist in the reference order (tile_n fastest); 1 = tile_m fastest
   // inside each expert, which keeps the expert's rows in L2 while its weights

@@ -360,11 +360,22 @@ int bmoe_plan_read_worklist(bmoe_plan* plan, bmoe_tile* tiles_host,
 
 /* Optional device counters for exact-once checks (NULL disables):
  *   tile_visits_dev   uint32 [total_tiles], +1 by the CTA that ran the tile
- *   cta_tiles_dev     uint32 [threadblock_count], tiles run per CTA
+ *   cta_tiles_dev     uint32 [threadblock_count], tiles run per scheduling unit
+ *                     (CTA, or CTA pair when cta_group is 2: then only the first
+ *                     threadblock_count / 2 entries are written)
  * The caller zeroes them. Mirrors the probe observables
  * (include/blackwell_moe/scheduler/scheduler_probe.cuh:24-28). */
 int bmoe_plan_set_observers(bmoe_plan* plan, uint32_t* tile_visits_dev,
                             uint32_t* cta_tiles_dev);
+
+/* Optional wait accounting (NULL disables): trace_dev is uint64
+ * [threadblock_count][16]; per CTA, SM cycles spent blocked per role:
+ *   [0] producer/tile info  [1] producer/free stage   [2] MMA/tile info
+ *   [3] MMA/drained accumulator  [4] MMA/operand bytes [5] epilogue/tile info
+ *   [6] epilogue/finished accumulator  [7] epilogue draining
+ *   [8] tiles run  [9] kernel cycles. The caller zeroes it. No reference
+ * counterpart (the reference measures with ncu only, tools/profile_ncu.sh). */
+int bmoe_plan_set_trace(bmoe_plan* plan, uint64_t* trace_dev);
 
 /* Replaces launch_grouped_gemm_baseline (grouped_gemm.cuh:71). */
 int bmoe_grouped_gemm(const bmoe_gemm_args* args);

@@ -93,8 +93,8 @@ def test_reference_known_answers_bit_exact(engine, golden, name):
     counts, n, k, a_bits, w_bits = support.kat_inputs(name)
     a = torch.from_numpy(a_bits.view(np.int16).copy()).view(torch.bfloat16)
     w = torch.from_numpy(w_bits.view(np.int16).copy()).view(torch.bfloat16)
-    for tile_n in (0, 128, 256):
-        out = run_engine(engine, a, w, counts, tile_n=tile_n)
+    for tile_n, group in ((0, 0), (128, 1), (256, 1), (256, 2)):
+        out = run_engine(engine, a, w, counts, tile_n=tile_n, cta_group=group)
         assert out["stats"].active_experts == sum(c > 0 for c in counts)
         assert support.sha(out["bits"].reshape(-1)) == golden["gemm_kats"][name]["d_sha256"]
 
@@ -169,19 +169,24 @@ def test_ragged_cases_all_policies(engine, oracle, counts, n, k):
                           oracle.build_tiles(counts, n, 128, base["stats"].tile_n))
     assert np.all(base["visits"] == 1)
     assert int(base["cta"].sum()) == base["stats"].total_tiles
-    for tile_n in (128, 256):
+    # (tile_n, cta_group): single-CTA tiles of 128 x 128 / 128 x 256, and CTA pairs
+    # computing 256 x 256 tiles. All of them must agree bit for bit.
+    for tile_n, group in ((128, 1), (256, 1), (256, 2)):
         for raster in (0, 1):
             for policy, opts in POLICIES:
                 out = run_engine(engine, a, w, counts, policy, observers=True, tile_n=tile_n,
-                                 raster_along_m=raster, **opts)
-                assert np.array_equal(out["bits"], base["bits"]), (policy, opts, tile_n, raster)
-                assert np.all(out["visits"] == 1), (policy, opts)
+                                 cta_group=group, raster_along_m=raster, **opts)
+                key = (policy, opts, tile_n, group, raster)
+                assert np.array_equal(out["bits"], base["bits"]), key
+                assert np.all(out["visits"] == 1), key
                 assert int(out["cta"].sum()) == out["stats"].total_tiles
+                assert out["stats"].cta_group == group and out["stats"].tile_m == 128 * group
                 order = 1 if policy == "static_persistent" else 0
                 if policy != "auto":
                     assert np.array_equal(
                         out["worklist"],
-                        oracle.build_tiles(counts, n, 128, tile_n, order=order, raster=raster))
+                        oracle.build_tiles(counts, n, 128 * group, tile_n, order=order,
+                                           raster=raster))
 
 
 def test_policy_specific_launch_shapes(engine):
@@ -241,9 +246,10 @@ def test_benchmark_shape_properties(engine, oracle, golden):
     base = run_engine(engine, a, w, counts, "expert_order", observers=True)
     assert np.all(base["visits"] == 1)
     for policy, opts in [("static_persistent", {}), ("dynamic_queue", {"claim_size": 4}),
-                         ("clc", {}), ("auto", {})]:
+                         ("clc", {}), ("auto", {}), ("expert_order", {"cta_group": 2}),
+                         ("dynamic_queue", {"cta_group": 2}), ("clc", {"cta_group": 2})]:
         out = run_engine(engine, a, w, counts, policy, **opts)
-        assert np.array_equal(out["bits"], base["bits"]), policy
+        assert np.array_equal(out["bits"], base["bits"]), (policy, opts)
     stride = 257
     ref = oracle.grouped_gemm(bits_of(a), bits_of(w), counts, n, k, want_f32=True,
                               row_stride=stride, row_phase=3)
