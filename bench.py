@@ -180,6 +180,15 @@ def load_oracle():
     return lib
 
 
+def host_threads() -> int:
+    """Host threads the CPU arm may use (launchers such as torchrun export
+    OMP_NUM_THREADS=1, which is not what this arm is meant to measure)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def oracle_time(lib, a_bits, w_bits, counts, n, k, stride):
     """Times the CPU restatement on rows r % stride == 0 of every expert."""
     import ctypes as C
@@ -192,7 +201,8 @@ def oracle_time(lib, a_bits, w_bits, counts, n, k, stride):
     rows = lib.orc_grouped_gemm(
         a_bits.ctypes.data_as(C.c_void_p), w_bits.ctypes.data_as(C.c_void_p),
         c.ctypes.data_as(C.c_void_p), C.c_uint32(len(c)), C.c_uint32(n), C.c_uint32(k),
-        d.ctypes.data_as(C.c_void_p), None, None, C.c_uint32(stride), C.c_uint32(0), C.c_int(0))
+        d.ctypes.data_as(C.c_void_p), None, None, C.c_uint32(stride), C.c_uint32(0),
+        C.c_int(host_threads()))
     dt = time.perf_counter() - t0
     return int(rows), dt
 
@@ -209,7 +219,7 @@ def cpu_sample(lib, a_bits, w_bits, counts, n, k, target_s=12.0):
         rows, dt = oracle_time(lib, a_bits, w_bits, counts, n, k, stride2)
         stride = stride2
     tflops = 2.0 * rows * n * k / dt / 1e12
-    return {"value": tflops, "unit": "TFLOP/s", "cores": int(lib.orc_max_threads()),
+    return {"value": tflops, "unit": "TFLOP/s", "cores": host_threads(),
             "kind": "port",
             "sample": f"rows r%{stride}==0 of every expert ({rows} of {sum(counts)} rows, "
                       f"{dt:.2f} s); FP32 sequential-k loop, OpenMP"}
@@ -252,7 +262,7 @@ def run_reference_arm(args, spec, workload):
         times.append(dt)
     per_step = sum(times) / len(times)
     tflops = 2.0 * rows * n * k / per_step / 1e12
-    cores = int(lib.orc_max_threads())
+    cores = host_threads()
     sample = (f"rows r%{stride}==0 of every expert ({rows} of {total} rows per step); "
               "FP32 sequential-k loop, OpenMP")
     line = {
@@ -495,6 +505,7 @@ def main():
     ap.add_argument("--no-policy-table", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-single-gpu-ref", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     args = ap.parse_args()
     if args.warmup < 3:

@@ -401,7 +401,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       uint32_t reads = 0;
       uint32_t stage = 0, stage_round = 0;
       uint32_t buf = 0, buf_round = 0;
-      uint64_t t_info = 0, t_accum = 0, t_operands = 0;
+      uint64_t t_info = 0, t_accum = 0, t_operands = 0, t_issue = 0;
       while (true) {
         const uint32_t slot = reads % kSchedSlots;
         const uint32_t round = (reads / kSchedSlots) & 1u;
@@ -429,6 +429,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             break;
           }
           ptx::tc_fence_after_sync();
+          const long long issue_t0 = tracing ? clock64() : 0;
           const uint64_t a_desc =
               ptx::make_kmajor_sw128_desc(base + Cfg::kOffA + stage * kABytes);
           const uint64_t b_desc =
@@ -450,6 +451,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           } else {
             ptx::umma_commit(bar_empty(stage));
           }
+          if (tracing) t_issue += static_cast<uint64_t>(clock64() - issue_t0);
           if (++stage == Cfg::kStages) { stage = 0; stage_round ^= 1u; }
         }
         if (!ok) break;
@@ -466,6 +468,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         p.trace[blockIdx.x * kTraceWords + 2] = t_info;
         p.trace[blockIdx.x * kTraceWords + 3] = t_accum;
         p.trace[blockIdx.x * kTraceWords + 4] = t_operands;
+        p.trace[blockIdx.x * kTraceWords + 10] = t_issue;
       }
     }
     __syncwarp();

@@ -68,6 +68,7 @@ struct GemmParams {
 //   4 MMA waiting for operand bytes       5 epilogue waiting for tile info
 //   6 epilogue waiting for an accumulator 7 epilogue draining (ld, convert, store)
 //   8 tiles run by this CTA               9 kernel cycles of this CTA
+//   10 MMA lane issuing tcgen05.mma / commit
 constexpr uint32_t kTraceWords = 16;
 
 // Dynamic shared memory / operand stages for a tile width (128 or 256) and CTA

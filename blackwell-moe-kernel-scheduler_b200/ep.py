@@ -111,6 +111,22 @@ class ExpertParallelLayer:
         self.local_experts = [e for e in range(self.experts) if self.owner[e] == rank]
         self.timings = {}
 
+    def _host_tables(self):
+        import torch
+
+        if not hasattr(self, "_tables"):
+            owner_t = torch.tensor(self.owner, dtype=torch.int64)
+            local_t = torch.tensor(self.local_experts, dtype=torch.int64)
+            position = torch.empty(self.experts, dtype=torch.int64)
+            position[torch.tensor(self.send_order, dtype=torch.int64)] = torch.arange(self.experts)
+            self._tables = (owner_t, local_t, position)
+        return self._tables
+
+    def _position_on(self, dev):
+        if getattr(self, "_position_dev", None) is None or self._position_dev.device != dev:
+            self._position_dev = self._host_tables()[2].to(dev)
+        return self._position_dev
+
     # -- collectives (skipped when there is a single rank) --
     def _all_gather_counts(self, local_counts):
         import torch
@@ -154,21 +170,20 @@ class ExpertParallelLayer:
 
         mark("start")
         # 1. counts
-        local_counts = torch.bincount(flat_ids, minlength=self.experts).to(torch.int64)
+        # scatter_add instead of bincount: no device synchronisation to size the output
+        local_counts = torch.zeros(self.experts, dtype=torch.int64, device=dev)
+        local_counts.scatter_add_(0, flat_ids, torch.ones_like(flat_ids))
         counts_all = self._all_gather_counts(local_counts).cpu()  # [world, experts], host
-        mine = counts_all[self.rank]
-        send_splits = [0] * self.world
-        for e in range(self.experts):
-            send_splits[self.owner[e]] += int(mine[e])
-        recv_matrix = counts_all[:, self.local_experts]            # [world, E_local]
-        recv_splits = [int(v) for v in recv_matrix.sum(dim=1)]
-        local_m = [int(v) for v in recv_matrix.sum(dim=0)]
+        owner_t, local_t, position = self._host_tables()
+        send_splits = torch.zeros(self.world, dtype=torch.int64).scatter_add_(
+            0, owner_t, counts_all[self.rank]).tolist()
+        recv_matrix = counts_all[:, local_t]                        # [world, E_local]
+        recv_splits = recv_matrix.sum(dim=1).tolist()
+        local_m = recv_matrix.sum(dim=0).tolist()
         mark("counts")
 
         # 2. send order: stable sort of the assignments by position of their expert
-        position = torch.empty(self.experts, dtype=torch.int64)
-        position[torch.tensor(self.send_order, dtype=torch.int64)] = torch.arange(self.experts)
-        keys = position.to(dev)[flat_ids]
+        keys = self._position_on(dev)[flat_ids]
         perm = torch.sort(keys, stable=True).indices               # assignment ids in send order
         send = self.ops.gather_rows(x, torch.div(perm, top_k, rounding_mode="floor"))
         mark("pack")
@@ -177,6 +192,20 @@ class ExpertParallelLayer:
         recv = self._all_to_all(send, send_splits, recv_splits)
         mark("dispatch")
 
+        total_local = int(sum(local_m))
+        if self.world == 1:
+            # A single rank receives its own send buffer, which is already
+            # expert-major: nothing to re-pack in either direction.
+            d_packed = self.ops.grouped_gemm(recv, w_local, local_m)
+            mark("gemm")
+            inv_perm = torch.empty(assignments, dtype=torch.int64, device=dev)
+            inv_perm[perm] = torch.arange(assignments, device=dev, dtype=torch.int64)
+            y = self.ops.gather_rows(d_packed, inv_perm)
+            mark("finish")
+            self._marks = marks
+            self.last_local_m = local_m
+            return y
+
         # 4. source-major -> expert-major. Segment (e, s) of the packed A starts at
         # recv_offset[s] + prefix of source s over local experts before e.
         seg_len = recv_matrix.t().contiguous().reshape(-1)          # (e, s) order
@@ -184,7 +213,6 @@ class ExpertParallelLayer:
         within = torch.cumsum(recv_matrix, dim=1) - recv_matrix      # [world, E_local]
         seg_start = (src_base[:, None] + within).t().contiguous().reshape(-1)
         seg_len_d, seg_start_d = seg_len.to(dev), seg_start.to(dev)
-        total_local = int(sum(local_m))
         out_start = torch.cumsum(seg_len_d, 0) - seg_len_d
         index = (torch.repeat_interleave(seg_start_d - out_start, seg_len_d,
                                          output_size=total_local)

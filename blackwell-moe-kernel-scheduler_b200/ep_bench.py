@@ -52,6 +52,9 @@ def run(args, spec, workload):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        # keep stdout to the one JSON line (NCCL_DEBUG=VERSION prints a banner there)
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=dev)
 
     def barrier():
@@ -143,6 +146,38 @@ def run(args, spec, workload):
     e2e_ms = max_over_ranks(e0.elapsed_time(e1) / e2e_steps)
     ops.poll()
 
+    # The same workload on ONE GPU (rank 0 alone, no exchange), so that strong
+    # scaling can be read from a single run.
+    single_gpu = None
+    if world > 1 and not args.no_single_gpu_ref:
+        if rank == 0:
+            del w_local, layer, ops
+            torch.cuda.empty_cache()
+            solo_owner = [0] * spec["experts"]
+            solo_ops = ep.CudaOps(scheduler=args.policy, cta_group=args.cta_group)
+            solo = ep.ExpertParallelLayer(solo_owner, n, k, rank=0, world=1, ops=solo_ops)
+            w_all = _expert_weights(torch, list(range(spec["experts"])), n, k, dev)
+            gen.manual_seed(4000)
+            x_all = torch.randn(tokens, k, generator=gen, device=dev,
+                                dtype=torch.float32).to(torch.bfloat16)
+            ids_dev = ids_all.to(dev)
+            for _ in range(3):
+                solo.forward(x_all, ids_dev, w_all)
+            torch.cuda.synchronize()
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            solo_steps = max(3, min(args.steps, 10))
+            s0.record(stream)
+            for _ in range(solo_steps):
+                solo.forward(x_all, ids_dev, w_all)
+            s1.record(stream)
+            torch.cuda.synchronize()
+            solo_ops.poll()
+            solo_ms = s0.elapsed_time(s1) / solo_steps
+            single_gpu = {"value": total_flops / (solo_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                          "ms_per_step": solo_ms, "steps": solo_steps}
+            del w_all, x_all
+        dist.barrier()
+
     if world > 1:
         dist.barrier()
     if rank != 0:
@@ -164,6 +199,9 @@ def run(args, spec, workload):
                    "rank_tiles": rank_tiles, "rank0_rows": local_rows,
                    "max_rank_rows": rows_max, "mean_rank_rows": tokens * top_k / world,
                    "l2": "per-rank weights exceed the 126 MB L2; no flush between steps",
+                   "note": "with more than one GPU the benchmark runs the expert-parallel "
+                           "configuration; the one-GPU line of bench.py runs the "
+                           "Mixtral-shaped grouped GEMM, see single_gpu_same_workload",
                    "step": "count all-gather + pack + all-to-all dispatch + unpack + "
                            "grouped GEMM + repack + all-to-all combine + un-permute"},
         "p50_us": bench.percentile(step_samples, 0.5) * 1e3,
@@ -175,6 +213,7 @@ def run(args, spec, workload):
                      "kernel": "grouped_gemm_kernel (rank 0, GEMM phase only)",
                      "avg_launch_ms": gemm_ms_local},
         "cpu_baseline": None,
+        "single_gpu_same_workload": single_gpu,
         "e2e": {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                 "h2d_bytes_per_step": x_host.numel() * 2 * world,
                 "d2h_bytes_per_step": y_host.numel() * 2 * world, "ms_per_step": e2e_ms},

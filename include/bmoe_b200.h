@@ -373,7 +373,7 @@ int bmoe_plan_set_observers(bmoe_plan* plan, uint32_t* tile_visits_dev,
  *   [0] producer/tile info  [1] producer/free stage   [2] MMA/tile info
  *   [3] MMA/drained accumulator  [4] MMA/operand bytes [5] epilogue/tile info
  *   [6] epilogue/finished accumulator  [7] epilogue draining
- *   [8] tiles run  [9] kernel cycles. The caller zeroes it. No reference
+ *   [8] tiles run  [9] kernel cycles  [10] MMA lane issuing. The caller zeroes it. No reference
  * counterpart (the reference measures with ncu only, tools/profile_ncu.sh). */
 int bmoe_plan_set_trace(bmoe_plan* plan, uint64_t* trace_dev);
 
