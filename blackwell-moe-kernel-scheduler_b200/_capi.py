@@ -184,7 +184,7 @@ class GemmArgs(C.Structure):
         ("tile_n", C.c_uint32),
         ("cta_group", C.c_uint32),
         ("raster_along_m", C.c_int32),
-        ("reserved", C.c_uint32),
+        ("output_f32", C.c_uint32),
         ("stream", C.c_void_p),
     ]
 
@@ -204,6 +204,7 @@ class PlanStats(C.Structure):
         ("stages", C.c_uint32),
         ("dynamic_smem_bytes", C.c_uint32),
         ("launches", C.c_uint32),
+        ("sm_count", C.c_uint32),
     ]
 
 

@@ -109,7 +109,9 @@ __device__ __forceinline__ void report(const GemmParams& p, uint32_t site,
   }
 }
 
-template <uint32_t TILE_N, bool PAIR>
+// OUT_F32 = true writes the FP32 accumulators unrounded (row-major FP32 D) instead
+// of BF16; everything up to the epilogue is identical.
+template <uint32_t TILE_N, bool PAIR, bool OUT_F32>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   using Cfg = Config<TILE_N, PAIR>;
@@ -332,45 +334,54 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   }
 
   // ----------------------------------------------------------- producer --
+  // The whole warp walks the loop converged; one elected lane issues the
+  // arrivals and the TMA loads.
   else if (warp == 0) {
-    if (lane == 0) {
-      uint32_t reads = 0;
-      uint32_t stage = 0, stage_round = 0;
-      uint32_t last_expert = 0xffffffffu;
-      uint64_t t_info = 0, t_stage = 0;
-      while (true) {
-        const uint32_t slot = reads % kSchedSlots;
-        const uint32_t round = (reads / kSchedSlots) & 1u;
-        if (!timed_wait(bar_sched_full(slot), round, t_info)) {
-          report(p, kSiteProducerInfo, 1, reads, slot, 0);
-          break;
-        }
-        const int32_t tile = slots[slot].tile;
-        const uint32_t expert = slots[slot].expert;
-        const uint32_t row0 = slots[slot].row0 + cta_rank * kCtaRows;
-        const uint32_t col0 = slots[slot].col0 + cta_rank * Cfg::kBRows;
+    uint32_t reads = 0;
+    uint32_t stage = 0, stage_round = 0;
+    uint32_t last_expert = 0xffffffffu;
+    uint64_t t_info = 0, t_stage = 0;
+    while (true) {
+      const uint32_t slot = reads % kSchedSlots;
+      const uint32_t round = (reads / kSchedSlots) & 1u;
+      if (!timed_wait(bar_sched_full(slot), round, t_info)) {
+        if (lane == 0) report(p, kSiteProducerInfo, 1, reads, slot, 0);
+        break;
+      }
+      const int32_t tile = slots[slot].tile;
+      const uint32_t expert = slots[slot].expert;
+      const uint32_t row0 = slots[slot].row0 + cta_rank * kCtaRows;
+      const uint32_t col0 = slots[slot].col0 + cta_rank * Cfg::kBRows;
+      __syncwarp();
+      ++reads;
+      if (ptx::elect_one()) {
         arrive_at_leader(bar_sched_empty(slot));
-        ++reads;
         if (leader) misc->producer_reads = reads;
-        if (tile == kSentinel) break;
+      }
+      if (tile == kSentinel) break;
 
-        const CUtensorMap* const map_a = p.tmap_a + expert;
-        const CUtensorMap* const map_b = p.tmap_b + expert;
-        if (expert != last_expert) {
+      const CUtensorMap* const map_a = p.tmap_a + expert;
+      const CUtensorMap* const map_b = p.tmap_b + expert;
+      if (expert != last_expert) {
+        if (ptx::elect_one()) {
           ptx::tensormap_acquire(map_a);
           ptx::tensormap_acquire(map_b);
-          last_expert = expert;
         }
-        bool ok = true;
-        for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
-          if (!timed_wait(bar_empty(stage), stage_round ^ 1u, t_stage)) {
+        last_expert = expert;
+      }
+      bool ok = true;
+      for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+        if (!timed_wait(bar_empty(stage), stage_round ^ 1u, t_stage)) {
+          if (lane == 0) {
             report(p, kSiteProducerStage, 1, static_cast<uint32_t>(tile), stage, kb);
-            ok = false;
-            break;
           }
-          const uint32_t dst_a = base + Cfg::kOffA + stage * kABytes;
-          const uint32_t dst_b = base + Cfg::kOffB + stage * Cfg::kBBytes;
-          const int32_t k0 = static_cast<int32_t>(kb * kBlockK);
+          ok = false;
+          break;
+        }
+        const uint32_t dst_a = base + Cfg::kOffA + stage * kABytes;
+        const uint32_t dst_b = base + Cfg::kOffB + stage * Cfg::kBBytes;
+        const int32_t k0 = static_cast<int32_t>(kb * kBlockK);
+        if (ptx::elect_one()) {
           if constexpr (PAIR) {
             // Both CTAs' bytes are counted on the leader's barrier.
             if (leader) ptx::mbar_arrive_expect_tx(bar_full(stage), Cfg::kTxBytes);
@@ -382,41 +393,44 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             ptx::tma_load_2d(dst_a, map_a, bar_full(stage), k0, static_cast<int32_t>(row0));
             ptx::tma_load_2d(dst_b, map_b, bar_full(stage), k0, static_cast<int32_t>(col0));
           }
-          if (++stage == Cfg::kStages) { stage = 0; stage_round ^= 1u; }
         }
-        if (!ok) break;
+        if (++stage == Cfg::kStages) { stage = 0; stage_round ^= 1u; }
       }
-      if (tracing) {
-        p.trace[blockIdx.x * kTraceWords + 0] = t_info;
-        p.trace[blockIdx.x * kTraceWords + 1] = t_stage;
-      }
+      if (!ok) break;
+    }
+    if (tracing && lane == 0) {
+      p.trace[blockIdx.x * kTraceWords + 0] = t_info;
+      p.trace[blockIdx.x * kTraceWords + 1] = t_stage;
     }
     __syncwarp();
   }
 
   // ---------------------------------------------------------------- MMA --
+  // Leader CTA only. The warp stays converged; one elected lane (always the
+  // same one, so tcgen05.commit covers its MMAs) issues the tensor-core work.
   else if (warp == 1) {
-    if (lane == 0 && leader) {
+    if (leader) {
       constexpr uint32_t idesc = ptx::make_bf16_idesc(kCtaRows * Cfg::kGroup, TILE_N);
       uint32_t reads = 0;
       uint32_t stage = 0, stage_round = 0;
       uint32_t buf = 0, buf_round = 0;
-      uint64_t t_info = 0, t_accum = 0, t_operands = 0, t_issue = 0;
+      uint64_t t_info = 0, t_accum = 0, t_operands = 0;
       while (true) {
         const uint32_t slot = reads % kSchedSlots;
         const uint32_t round = (reads / kSchedSlots) & 1u;
         if (!timed_wait(bar_sched_full(slot), round, t_info)) {
-          report(p, kSiteMmaInfo, 2, reads, slot, 0);
+          if (lane == 0) report(p, kSiteMmaInfo, 2, reads, slot, 0);
           break;
         }
         const int32_t tile = slots[slot].tile;
-        ptx::mbar_arrive(bar_sched_empty(slot));
+        __syncwarp();
+        if (ptx::elect_one()) ptx::mbar_arrive(bar_sched_empty(slot));
         ++reads;
         if (tile == kSentinel) break;
 
         // The epilogue(s) must have drained this accumulator buffer.
         if (!timed_wait(bar_tmem_empty(buf), buf_round ^ 1u, t_accum)) {
-          report(p, kSiteMmaAccum, 2, static_cast<uint32_t>(tile), buf, 0);
+          if (lane == 0) report(p, kSiteMmaAccum, 2, static_cast<uint32_t>(tile), buf, 0);
           break;
         }
         ptx::tc_fence_after_sync();
@@ -424,51 +438,54 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         bool ok = true;
         for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
           if (!timed_wait(bar_full(stage), stage_round, t_operands)) {
-            report(p, kSiteMmaStage, 2, static_cast<uint32_t>(tile), stage, kb);
+            if (lane == 0) {
+              report(p, kSiteMmaStage, 2, static_cast<uint32_t>(tile), stage, kb);
+            }
             ok = false;
             break;
           }
           ptx::tc_fence_after_sync();
-          const long long issue_t0 = tracing ? clock64() : 0;
           const uint64_t a_desc =
               ptx::make_kmajor_sw128_desc(base + Cfg::kOffA + stage * kABytes);
           const uint64_t b_desc =
               ptx::make_kmajor_sw128_desc(base + Cfg::kOffB + stage * Cfg::kBBytes);
+          if (ptx::elect_one()) {
 #pragma unroll
-          for (uint32_t ks = 0; ks < kBlockK / 16; ++ks) {
-            // 16 BF16 = 32 bytes along k inside the 128-byte swizzle row.
-            const uint32_t acc = (kb | ks) != 0 ? 1u : 0u;
+            for (uint32_t ks = 0; ks < kBlockK / 16; ++ks) {
+              // 16 BF16 = 32 bytes along k inside the 128-byte swizzle row.
+              const uint32_t acc = (kb | ks) != 0 ? 1u : 0u;
+              if constexpr (PAIR) {
+                ptx::umma_bf16_ss_pair(d_tmem, a_desc + 2 * ks, b_desc + 2 * ks, idesc, acc);
+              } else {
+                ptx::umma_bf16_ss(d_tmem, a_desc + 2 * ks, b_desc + 2 * ks, idesc, acc);
+              }
+            }
+            // The stage is reusable (in both CTAs) once these MMAs retire.
             if constexpr (PAIR) {
-              ptx::umma_bf16_ss_pair(d_tmem, a_desc + 2 * ks, b_desc + 2 * ks, idesc, acc);
+              ptx::umma_commit_pair(bar_empty(stage));
+              ptx::umma_commit_pair(ptx::map_to_cta(bar_empty(stage), 1));
             } else {
-              ptx::umma_bf16_ss(d_tmem, a_desc + 2 * ks, b_desc + 2 * ks, idesc, acc);
+              ptx::umma_commit(bar_empty(stage));
+            }
+            if (kb + 1 == p.k_blocks) {
+              // Accumulator complete: wake the epilogue of both CTAs.
+              if constexpr (PAIR) {
+                ptx::umma_commit_pair(bar_tmem_full(buf));
+                ptx::umma_commit_pair(ptx::map_to_cta(bar_tmem_full(buf), 1));
+              } else {
+                ptx::umma_commit(bar_tmem_full(buf));
+              }
             }
           }
-          // The stage is reusable (in both CTAs) once these MMAs retire.
-          if constexpr (PAIR) {
-            ptx::umma_commit_pair(bar_empty(stage));
-            ptx::umma_commit_pair(ptx::map_to_cta(bar_empty(stage), 1));
-          } else {
-            ptx::umma_commit(bar_empty(stage));
-          }
-          if (tracing) t_issue += static_cast<uint64_t>(clock64() - issue_t0);
           if (++stage == Cfg::kStages) { stage = 0; stage_round ^= 1u; }
         }
         if (!ok) break;
-        // Accumulator complete: wake the epilogue of both CTAs.
-        if constexpr (PAIR) {
-          ptx::umma_commit_pair(bar_tmem_full(buf));
-          ptx::umma_commit_pair(ptx::map_to_cta(bar_tmem_full(buf), 1));
-        } else {
-          ptx::umma_commit(bar_tmem_full(buf));
-        }
         if (++buf == 2) { buf = 0; buf_round ^= 1u; }
       }
-      if (tracing) {
+      if (tracing && lane == 0) {
         p.trace[blockIdx.x * kTraceWords + 2] = t_info;
         p.trace[blockIdx.x * kTraceWords + 3] = t_accum;
         p.trace[blockIdx.x * kTraceWords + 4] = t_operands;
-        p.trace[blockIdx.x * kTraceWords + 10] = t_issue;
       }
     }
     __syncwarp();
@@ -516,13 +533,15 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       last_expert = expert;
 
       const bool has_rows = row_in_tile < valid_m;
-      const uint32_t chunks = has_rows ? (valid_n + kStoreCols - 1) / kStoreCols : 0;
+      // One store box is 128 bytes wide: 64 BF16 or 32 FP32 columns.
+      constexpr uint32_t kChunkCols = OUT_F32 ? 32u : kStoreCols;
+      const uint32_t chunks = has_rows ? (valid_n + kChunkCols - 1) / kChunkCols : 0;
       const uint32_t lane_taddr = tmem_base + ((quad * 32u) << 16) + buf * TILE_N;
       const long long drain_t0 = tracing ? clock64() : 0;
       for (uint32_t c = 0; c < chunks; ++c) {
         uint32_t lo[32], hi[32];
-        ptx::tmem_load_32x32(lane_taddr + c * kStoreCols, lo);
-        ptx::tmem_load_32x32(lane_taddr + c * kStoreCols + 32, hi);
+        ptx::tmem_load_32x32(lane_taddr + c * kChunkCols, lo);
+        if constexpr (!OUT_F32) ptx::tmem_load_32x32(lane_taddr + c * kChunkCols + 32, hi);
         ptx::tmem_load_wait();
         if (c + 1 == chunks) {
           // All of this warp's accumulator rows are in registers: hand the
@@ -536,29 +555,37 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         __syncwarp();
         const uint32_t row_smem = staging + sbuf * kStoreBytes + lane * 128u;
         const uint32_t sw = lane & 7u;
+        if constexpr (OUT_F32) {
 #pragma unroll
-        for (uint32_t j = 0; j < 4; ++j) {
-          ptx::st_shared_v4(
-              row_smem + ((j ^ sw) << 4),
-              ptx::pack_bf16x2(__uint_as_float(lo[8 * j + 0]), __uint_as_float(lo[8 * j + 1])),
-              ptx::pack_bf16x2(__uint_as_float(lo[8 * j + 2]), __uint_as_float(lo[8 * j + 3])),
-              ptx::pack_bf16x2(__uint_as_float(lo[8 * j + 4]), __uint_as_float(lo[8 * j + 5])),
-              ptx::pack_bf16x2(__uint_as_float(lo[8 * j + 6]), __uint_as_float(lo[8 * j + 7])));
-        }
+          for (uint32_t j = 0; j < 8; ++j) {
+            ptx::st_shared_v4(row_smem + ((j ^ sw) << 4), lo[4 * j + 0], lo[4 * j + 1],
+                              lo[4 * j + 2], lo[4 * j + 3]);
+          }
+        } else {
 #pragma unroll
-        for (uint32_t j = 0; j < 4; ++j) {
-          ptx::st_shared_v4(
-              row_smem + (((j + 4) ^ sw) << 4),
-              ptx::pack_bf16x2(__uint_as_float(hi[8 * j + 0]), __uint_as_float(hi[8 * j + 1])),
-              ptx::pack_bf16x2(__uint_as_float(hi[8 * j + 2]), __uint_as_float(hi[8 * j + 3])),
-              ptx::pack_bf16x2(__uint_as_float(hi[8 * j + 4]), __uint_as_float(hi[8 * j + 5])),
-              ptx::pack_bf16x2(__uint_as_float(hi[8 * j + 6]), __uint_as_float(hi[8 * j + 7])));
+          for (uint32_t j = 0; j < 4; ++j) {
+            ptx::st_shared_v4(
+                row_smem + ((j ^ sw) << 4),
+                ptx::pack_bf16x2(__uint_as_float(lo[8 * j + 0]), __uint_as_float(lo[8 * j + 1])),
+                ptx::pack_bf16x2(__uint_as_float(lo[8 * j + 2]), __uint_as_float(lo[8 * j + 3])),
+                ptx::pack_bf16x2(__uint_as_float(lo[8 * j + 4]), __uint_as_float(lo[8 * j + 5])),
+                ptx::pack_bf16x2(__uint_as_float(lo[8 * j + 6]), __uint_as_float(lo[8 * j + 7])));
+          }
+#pragma unroll
+          for (uint32_t j = 0; j < 4; ++j) {
+            ptx::st_shared_v4(
+                row_smem + (((j + 4) ^ sw) << 4),
+                ptx::pack_bf16x2(__uint_as_float(hi[8 * j + 0]), __uint_as_float(hi[8 * j + 1])),
+                ptx::pack_bf16x2(__uint_as_float(hi[8 * j + 2]), __uint_as_float(hi[8 * j + 3])),
+                ptx::pack_bf16x2(__uint_as_float(hi[8 * j + 4]), __uint_as_float(hi[8 * j + 5])),
+                ptx::pack_bf16x2(__uint_as_float(hi[8 * j + 6]), __uint_as_float(hi[8 * j + 7])));
+          }
         }
         ptx::fence_async_shared();
         __syncwarp();
         if (lane == 0) {
           ptx::tma_store_2d(map_d, staging + sbuf * kStoreBytes,
-                            static_cast<int32_t>(col0 + c * kStoreCols),
+                            static_cast<int32_t>(col0 + c * kChunkCols),
                             static_cast<int32_t>(row0 + row_in_tile));
           ptx::tma_store_commit();
         }
@@ -630,7 +657,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   }
 }
 
-template <uint32_t TILE_N, bool PAIR>
+template <uint32_t TILE_N, bool PAIR, bool OUT_F32>
 cudaError_t launch_impl(const GemmParams& params, uint32_t units, cudaStream_t stream) {
   using Cfg = Config<TILE_N, PAIR>;
   // The opt-in shared-memory size is a per-device function attribute.
@@ -639,7 +666,7 @@ cudaError_t launch_impl(const GemmParams& params, uint32_t units, cudaStream_t s
   cudaError_t err = cudaGetDevice(&device);
   if (err != cudaSuccess) return err;
   if (device < 0 || device >= 64 || !configured[device]) {
-    err = cudaFuncSetAttribute(grouped_gemm_kernel<TILE_N, PAIR>,
+    err = cudaFuncSetAttribute(grouped_gemm_kernel<TILE_N, PAIR, OUT_F32>,
                                cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(Cfg::kDynamicSmem));
     if (err != cudaSuccess) return err;
@@ -657,7 +684,7 @@ cudaError_t launch_impl(const GemmParams& params, uint32_t units, cudaStream_t s
   attribute[0].val.clusterDim.z = 1;
   config.attrs = attribute;
   config.numAttrs = 1;
-  err = cudaLaunchKernelEx(&config, grouped_gemm_kernel<TILE_N, PAIR>, params);
+  err = cudaLaunchKernelEx(&config, grouped_gemm_kernel<TILE_N, PAIR, OUT_F32>, params);
   return err != cudaSuccess ? err : cudaPeekAtLastError();
 }
 
@@ -674,11 +701,17 @@ uint32_t gemm_stage_count(uint32_t tile_n, uint32_t cta_group) {
 }
 
 cudaError_t launch_grouped_gemm(const GemmParams& params, uint32_t tile_n,
-                                uint32_t cta_group, uint32_t units, cudaStream_t stream) {
+                                uint32_t cta_group, bool out_f32, uint32_t units,
+                                cudaStream_t stream) {
   if (units == 0) return cudaSuccess;
-  if (cta_group == 2 && tile_n == 256) return launch_impl<256, true>(params, units, stream);
-  if (cta_group == 1 && tile_n == 256) return launch_impl<256, false>(params, units, stream);
-  if (cta_group == 1 && tile_n == 128) return launch_impl<128, false>(params, units, stream);
+  if (out_f32) {
+    if (cta_group == 2 && tile_n == 256) return launch_impl<256, true, true>(params, units, stream);
+    if (cta_group == 1 && tile_n == 256) return launch_impl<256, false, true>(params, units, stream);
+    return cudaErrorInvalidValue;
+  }
+  if (cta_group == 2 && tile_n == 256) return launch_impl<256, true, false>(params, units, stream);
+  if (cta_group == 1 && tile_n == 256) return launch_impl<256, false, false>(params, units, stream);
+  if (cta_group == 1 && tile_n == 128) return launch_impl<128, false, false>(params, units, stream);
   return cudaErrorInvalidValue;
 }
 

@@ -46,7 +46,7 @@ struct DeviceStatus {
 struct GemmParams {
   const CUtensorMap* tmap_a;  // [experts] A_e as {k, M_e}, box {64, 128}
   const CUtensorMap* tmap_b;  // [experts] B_e as {k, n},   box {64, TILE_N / cta_group}
-  const CUtensorMap* tmap_d;  // [experts] D_e as {n, M_e}, box {64, 32}
+  const CUtensorMap* tmap_d;  // [experts] D_e as {n, M_e}, box {64, 32} BF16 / {32, 32} FP32
   const bmoe_tile* tiles;     // device worklist
   uint32_t tile_count;
   uint32_t k_blocks;          // ceil(k / 64)
@@ -78,7 +78,9 @@ uint32_t gemm_stage_count(uint32_t tile_n, uint32_t cta_group);
 
 // Enqueues the kernel on `units` scheduling units: persistent CTAs (or CTA
 // pairs), or the tile count for CLC. The grid is units * cta_group CTAs.
+// out_f32 selects the FP32-output epilogue (tile_n 256 only).
 cudaError_t launch_grouped_gemm(const GemmParams& params, uint32_t tile_n,
-                                uint32_t cta_group, uint32_t units, cudaStream_t stream);
+                                uint32_t cta_group, bool out_f32, uint32_t units,
+                                cudaStream_t stream);
 
 }  // namespace bmoe

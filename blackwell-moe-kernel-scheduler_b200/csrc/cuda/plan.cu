@@ -42,18 +42,21 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-// Row-major BF16 matrix [rows, cols] viewed as a 2-D tensor {cols, rows} with a
-// SWIZZLE_128B box of 64 columns (128 bytes) x box_rows rows.
-bool encode_bf16_matrix(CUtensorMap* map, const void* base, uint64_t rows,
-                        uint64_t cols, uint32_t box_rows) {
+// Row-major matrix [rows, cols] of BF16 (or FP32) viewed as a 2-D tensor
+// {cols, rows} with a SWIZZLE_128B box of 128 bytes (64 BF16 / 32 FP32 columns)
+// x box_rows rows.
+bool encode_matrix(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
+                   uint32_t box_rows, bool fp32) {
   EncodeTiledFn encode = encode_tiled_fn();
   if (encode == nullptr) return false;
+  const uint32_t elem = fp32 ? 4u : 2u;
   const cuuint64_t dims[2] = {cols, rows};
-  const cuuint64_t strides[1] = {cols * 2};
-  const cuuint32_t box[2] = {64, box_rows};
+  const cuuint64_t strides[1] = {cols * elem};
+  const cuuint32_t box[2] = {128u / elem, box_rows};
   const cuuint32_t elem_strides[2] = {1, 1};
   const CUresult rc = encode(
-      map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+      map, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+      const_cast<void*>(base), dims, strides,
       box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return rc == CUDA_SUCCESS;
@@ -106,6 +109,7 @@ struct bmoe_plan {
   uint32_t units = 0;      // persistent CTAs or CTA pairs (tile count for CLC)
   uint32_t tile_n = 0;
   uint32_t cta_group = 1;
+  bool out_f32 = false;
 
   void release_all() {
     counts.release();
@@ -255,10 +259,13 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
   }
 
   // ---- engine configuration ----
+  const bool out_f32 = a.output_f32 != 0;
+  if (out_f32 && a.tile_n == 128) return BMOE_INVALID_ARGUMENT;  // FP32 epilogue: 256-wide tiles
   const uint32_t cta_group = a.cta_group == 2 ? 2u : 1u;
   const uint32_t tile_m = 128 * cta_group;
   const uint32_t tile_n =
-      cta_group == 2 ? 256u : (a.tile_n != 0 ? a.tile_n : (a.n <= 128 ? 128u : 256u));
+      (cta_group == 2 || out_f32) ? 256u
+                                  : (a.tile_n != 0 ? a.tile_n : (a.n <= 128 ? 128u : 256u));
   const uint32_t raster =
       a.raster_along_m < 0 ? BMOE_RASTER_M_FASTEST
                            : (a.raster_along_m != 0 ? BMOE_RASTER_M_FASTEST
@@ -318,9 +325,9 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
   for (uint32_t e = 0; e < a.experts; ++e) {
     const uint64_t rows = a.tokens_per_expert[e];
     if (rows == 0) continue;
-    if (!encode_bf16_matrix(&maps_a[e], a.a[e], rows, a.k, 128) ||
-        !encode_bf16_matrix(&maps_b[e], a.b[e], a.n, a.k, tile_n / cta_group) ||
-        !encode_bf16_matrix(&maps_d[e], a.d[e], rows, a.n, 32)) {
+    if (!encode_matrix(&maps_a[e], a.a[e], rows, a.k, 128, false) ||
+        !encode_matrix(&maps_b[e], a.b[e], a.n, a.k, tile_n / cta_group, false) ||
+        !encode_matrix(&maps_d[e], a.d[e], rows, a.n, 32, out_f32)) {
       return BMOE_CUDA_ERROR;
     }
   }
@@ -364,6 +371,7 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
 
   plan->tile_n = tile_n;
   plan->cta_group = cta_group;
+  plan->out_f32 = out_f32;
   plan->units = policy.one_cta_per_tile ? tiles : (tiles < unit_budget ? tiles : unit_budget);
 
   plan->stats.threadblock_count = plan->units * cta_group;
@@ -380,6 +388,7 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
   plan->stats.stages = bmoe::gemm_stage_count(tile_n, cta_group);
   plan->stats.dynamic_smem_bytes = bmoe::gemm_smem_bytes(tile_n, cta_group);
   plan->stats.launches = 0;
+  plan->stats.sm_count = static_cast<uint32_t>(sm_count);
   plan->ready = true;
   return BMOE_OK;
 }
@@ -394,7 +403,8 @@ int bmoe_plan_run(bmoe_plan* plan, void* stream) {
     return BMOE_CUDA_ERROR;
   }
   const cudaError_t err =
-      bmoe::launch_grouped_gemm(plan->params, plan->tile_n, plan->cta_group, plan->units, s);
+      bmoe::launch_grouped_gemm(plan->params, plan->tile_n, plan->cta_group, plan->out_f32,
+                                plan->units, s);
   plan->last_stream = s;
   if (err != cudaSuccess) return BMOE_CUDA_ERROR;
   plan->stats.launches += 1;

@@ -22,6 +22,21 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 
+// True in exactly one lane of a fully converged warp (the same lane on every
+// call), so the surrounding loop stays warp-uniform and addresses, descriptors
+// and coordinates can live in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t elected;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(elected));
+  return elected != 0;
+}
+
 // ---------------------------------------------------------------- mbarrier --
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t arrivals) {
@@ -49,16 +64,22 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
                : "memory");
 }
 
+// Upper bound, in nanoseconds, on how long one try_wait may keep the thread
+// suspended in hardware before it returns false; a waiting warp then costs no
+// issue slots. The bounded-wait loops re-check their abort word and time
+// budget at this granularity.
+constexpr uint32_t kSuspendHintNs = 500000;
+
 __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   uint32_t done;
   asm volatile(
       "{\n\t"
       ".reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t"
       "}"
       : "=r"(done)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
       : "memory");
   return done != 0;
 }
@@ -271,11 +292,11 @@ __device__ __forceinline__ bool mbar_test_cluster(uint32_t bar, uint32_t parity)
   asm volatile(
       "{\n\t"
       ".reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t"
       "}"
       : "=r"(done)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
       : "memory");
   return done != 0;
 }

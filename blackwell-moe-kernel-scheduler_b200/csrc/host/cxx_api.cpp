@@ -32,6 +32,7 @@ bmoe_gemm_args to_c_args(const GroupedGemmArguments& args) {
   c.tile_n = args.tile_n;
   c.cta_group = args.cta_group;
   c.raster_along_m = args.raster_along_m;
+  c.output_f32 = 0;
   c.stream = args.stream;
   return c;
 }

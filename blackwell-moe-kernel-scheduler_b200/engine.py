@@ -84,6 +84,7 @@ class GroupedGemmPlan:
         tile_n: int = 0,
         cta_group: int = 0,
         raster_along_m: int = -1,
+        output_f32: bool = False,
     ) -> int:
         """Pointer-array form of the reference arguments. Returns a status."""
         experts = len(tokens_per_expert)
@@ -107,7 +108,7 @@ class GroupedGemmPlan:
             tile_n=tile_n,
             cta_group=cta_group,
             raster_along_m=raster_along_m,
-            reserved=0,
+            output_f32=1 if output_f32 else 0,
             stream=_stream_ptr(stream),
         )
         return int(self._lib.bmoe_plan_initialize(self._handle, C.byref(args)))
@@ -119,6 +120,9 @@ class GroupedGemmPlan:
         k and n are multiples of 8."""
         experts = len(tokens_per_expert)
         n, k = int(w.shape[1]), int(w.shape[2])
+        d_elem = 4 if options.get("output_f32") else 2
+        if d.element_size() != d_elem:
+            return _capi.INVALID_ARGUMENT
         if int(w.shape[0]) != experts or int(a.shape[1]) != k or int(d.shape[1]) != n:
             return _capi.INVALID_ARGUMENT
         if not (a.is_contiguous() and w.is_contiguous() and d.is_contiguous()):
@@ -132,7 +136,7 @@ class GroupedGemmPlan:
         for e, c in enumerate(tokens_per_expert):
             a_ptrs.append(a_base + row * k * 2)
             b_ptrs.append(w_base + e * n * k * 2)
-            d_ptrs.append(d_base + row * n * 2)
+            d_ptrs.append(d_base + row * n * d_elem)
             row += int(c)
         self._keep = (a, w, d)
         return self.initialize(a_ptrs, b_ptrs, d_ptrs, tokens_per_expert, n, k, **options)

@@ -306,7 +306,8 @@ typedef struct bmoe_gemm_args {
   uint32_t tile_n;
   uint32_t cta_group;
   int32_t raster_along_m;
-  uint32_t reserved;
+  uint32_t output_f32; /* 0: D is BF16 (reference contract); 1: D is row-major FP32,
+                          the unrounded accumulators (direct_cute_gemm.cuh:16-18) */
   void* stream;
 } bmoe_gemm_args;
 
@@ -325,6 +326,7 @@ typedef struct bmoe_plan_stats {
   uint32_t stages;
   uint32_t dynamic_smem_bytes;
   uint32_t launches; /* kernel launches enqueued by run() since initialize */
+  uint32_t sm_count; /* multiprocessors of the plan's device */
 } bmoe_plan_stats;
 
 /* What a kernel recorded when it gave up on a bounded wait. */
