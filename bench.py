@@ -360,7 +360,7 @@ def run_single_gpu(args, spec, workload):
     # ---------------- per-policy latency table (outside the headline region) --
     policies = {}
     if not args.no_policy_table:
-        g = args.cta_group
+        g = stats.cta_group
         table = [("expert_order", {}), ("static_persistent", {}), ("dynamic_queue", {}),
                  ("dynamic_queue", {"claim_size": 4}),
                  ("dynamic_queue", {"claim_size": 8, "hybrid_tail_tiles": 2 * 148 // g}),
@@ -500,7 +500,8 @@ def main():
     # dynamic_queue with claim 1 measured fastest on the headline workload; "auto"
     # (the reference's threshold rule) and every other policy are in the table.
     ap.add_argument("--policy", default="dynamic_queue")
-    ap.add_argument("--cta-group", type=int, default=2, choices=[1, 2])
+    ap.add_argument("--cta-group", type=int, default=0, choices=[0, 1, 2],
+                    help="0 = engine picks per routing (default)")
     ap.add_argument("--policy-iters", type=int, default=200)
     ap.add_argument("--no-policy-table", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -261,7 +261,20 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
   // ---- engine configuration ----
   const bool out_f32 = a.output_f32 != 0;
   if (out_f32 && a.tile_n == 128) return BMOE_INVALID_ARGUMENT;  // FP32 epilogue: 256-wide tiles
-  const uint32_t cta_group = a.cta_group == 2 ? 2u : 1u;
+  // cta_group 0 = choose: CTA pairs (256-row tiles, a third less operand traffic
+  // per FLOP) unless 256-row tiles would pad the routed rows by more than 10 %
+  // over 128-row tiles, as they do for small-M (decode-like) routing.
+  uint32_t cta_group = a.cta_group;
+  if (cta_group == 0) {
+    uint64_t padded128 = 0, padded256 = 0;
+    for (uint32_t e = 0; e < a.experts; ++e) {
+      const uint64_t rows = a.tokens_per_expert[e];
+      padded128 += (rows + 127) / 128 * 128;
+      padded256 += (rows + 255) / 256 * 256;
+    }
+    const bool pair_ok = (a.tile_n == 0 || a.tile_n == 256) && a.n > 128;
+    cta_group = (pair_ok && padded256 * 10 <= padded128 * 11) ? 2u : 1u;
+  }
   const uint32_t tile_m = 128 * cta_group;
   const uint32_t tile_n =
       (cta_group == 2 || out_f32) ? 256u

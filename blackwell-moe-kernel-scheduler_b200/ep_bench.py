@@ -72,7 +72,7 @@ def run(args, spec, workload):
     n, k, top_k, tokens = spec["n"], spec["k"], spec["top_k"], spec["tokens"]
     ids_all = _routing(torch, spec)
     global_counts = torch.bincount(ids_all.reshape(-1), minlength=spec["experts"]).tolist()
-    owner, rank_tiles = ep.place_experts(global_counts, world, n, tile_m=128 * args.cta_group,
+    owner, rank_tiles = ep.place_experts(global_counts, world, n, tile_m=256 if args.cta_group != 1 else 128,
                                          tile_n=256)
     lo, hi = tokens * rank // world, tokens * (rank + 1) // world
     ids_local = ids_all[lo:hi].to(dev)

@@ -46,7 +46,8 @@ struct GroupedGemmArguments {
   // Output tile width: 128 or 256 (default 256). Tile height is 128 per CTA.
   std::uint32_t tile_n = 0;
   // 1 = one CTA computes a 128-row tile; 2 = two CTAs of a cluster compute a
-  // 256 x 256 tile together (default 1).
+  // 256 x 256 tile together; 0 = the engine picks (pairs unless 256-row tiles
+  // would pad the routed rows by more than 10 % over 128-row tiles).
   std::uint32_t cta_group = 0;
   // 0 = worklist in the reference order (tile_n fastest); 1 = tile_m fastest
   // inside each expert, which keeps the expert's rows in L2 while its weights

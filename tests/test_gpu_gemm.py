@@ -263,3 +263,45 @@ def test_benchmark_shape_properties(engine, oracle, golden):
     assert (np.abs(got - exact) / 2.0 ** (np.floor(np.log2(mag)) - 7)).max() <= 2.0
     want = support.bf16_bits_to_f32(ref["bf16"][rows]).astype(np.float64)
     assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 1e-3
+
+
+def test_fp32_output_epilogue(engine, oracle):
+    """FP32 D (the unrounded accumulators, the direct-launcher contract): exact on the
+    reference's known-answer inputs, within FP32 accumulation noise of the
+    sequential-k oracle on random data, identical across policies and CTA groups,
+    and its BF16 rounding equals the BF16 epilogue's output."""
+    import torch
+
+    counts, n, k = [300, 5, 0, 129], 520, 448
+    a, w = make_inputs(counts, n, k)
+    ref = oracle.grouped_gemm(bits_of(a), bits_of(w), counts, n, k, want_f32=True)
+    outs = []
+    for policy, group in (("expert_order", 1), ("dynamic_queue", 2), ("clc", 1)):
+        d = torch.full((sum(counts), n), float("nan"), dtype=torch.float32, device="cuda")
+        plan = engine.GroupedGemmPlan()
+        try:
+            assert plan.initialize_packed(a.cuda(), w.cuda(), d, counts, scheduler=policy,
+                                          cta_group=group, output_f32=True) == 0
+            assert plan.run() == 0 and plan.poll()[0] == 0
+        finally:
+            plan.close()
+        outs.append(d.cpu().numpy())
+    assert np.all(np.isfinite(outs[0]))
+    assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
+    scale = np.abs(ref["f32"]).max()
+    assert np.abs(outs[0] - ref["f32"]).max() <= 64 * 2.0 ** -24 * scale * np.sqrt(k)
+    bf16 = run_engine(engine, a, w, counts)["bits"]
+    assert np.array_equal(support.f32_to_bf16_bits(outs[0]).reshape(bf16.shape), bf16)
+    # exact sums on the reference's known-answer inputs
+    c2, n2, k2, a_bits, w_bits = support.kat_inputs("sm100_dense_kat")
+    a2 = torch.from_numpy(a_bits.view(np.int16).copy()).view(torch.bfloat16)
+    w2 = torch.from_numpy(w_bits.view(np.int16).copy()).view(torch.bfloat16)
+    d2 = torch.zeros(sum(c2), n2, dtype=torch.float32, device="cuda")
+    plan = engine.GroupedGemmPlan()
+    try:
+        assert plan.initialize_packed(a2.cuda(), w2.cuda(), d2, c2, output_f32=True) == 0
+        assert plan.run() == 0 and plan.poll()[0] == 0
+    finally:
+        plan.close()
+    exact = oracle.grouped_gemm(a_bits, w_bits, c2, n2, k2, want_f32=True)["f32"]
+    assert np.array_equal(d2.cpu().numpy(), exact)
