@@ -49,11 +49,12 @@ EP_WORKLOAD = "ep_deepseek_e256_t32768_k7168_n2048_zipf1.0"
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the GEMM kernel from
 # the ncu captures summarised under profiles/. The full Mixtral-shaped launch is
-# scaled from the half-size capture (565.6 MB measured for 562.0 MB of
-# algorithmic bytes; traffic grows in proportion to the operand bytes).
+# scaled from the half-size capture of the CTA-pair kernel (564.0 MB measured for
+# 562.0 MB of algorithmic bytes; traffic grows in proportion to the operand bytes).
 NCU_TRAFFIC_BYTES = {
-    "profile_e8_t2048_k4096_n7168_zipf1.0": 565.6e6,
-    DEFAULT_WORKLOAD: 1241.5e6 * (565.6 / 562.0),
+    "profile_e8_t2048_k4096_n7168_zipf1.0": 564.0e6,
+    DEFAULT_WORKLOAD: 1241.5e6 * (564.0 / 562.0),
+    "deepseek_decode_e256_t256_k7168_n2048_heavy": 7.473e9,
 }
 
 
