@@ -57,6 +57,44 @@ def build_reference() -> Path | None:
     return REF_LIB
 
 
+HARNESS_DIR = REF_DIR / "bin"
+# The reference's own GPU harness programs. They are compiled UNMODIFIED from the
+# reference checkout, but against THIS repository's headers and engine library:
+# running them on a B200 is the drop-in check for the GPU entry points.
+HARNESS_SOURCES = {
+    "ref_grouped_gemm_benchmark": "baselines/cutlass/benchmark.cu",
+    "ref_scheduler_gpu_benchmark": "benchmarks/scheduler_gpu_benchmark.cu",
+    "ref_test_scheduler_probe": "tests/test_scheduler_probe.cu",
+    "ref_sm100_dense_benchmark": "benchmarks/sm100_dense_benchmark.cu",
+    "ref_sm100_2sm_benchmark": "benchmarks/sm100_2sm_benchmark.cu",
+    "ref_direct_cute_benchmark": "benchmarks/direct_cute_benchmark.cu",
+}
+
+
+def build_reference_harness() -> list[Path]:
+    """nvcc-compile the reference's GPU harness against include/ + libbmoe_b200.so."""
+    built = []
+    if not reference_available():
+        return sorted(HARNESS_DIR.glob("ref_*")) if HARNESS_DIR.exists() else built
+    repo = ORACLE_DIR.parent
+    lib_dir = repo / "blackwell-moe-kernel-scheduler_b200" / "lib"
+    lib = lib_dir / "libbmoe_b200.so"
+    if not lib.exists():
+        return built
+    HARNESS_DIR.mkdir(parents=True, exist_ok=True)
+    for name, rel in HARNESS_SOURCES.items():
+        src = REFERENCE_ROOT / rel
+        out = HARNESS_DIR / name
+        if _stale(out, [src, lib]):
+            _run(["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-std=c++17",
+                  f"-I{repo / 'include'}", "-DBLACKWELL_MOE_CUTLASS_REVISION=\"none\"",
+                  str(src), f"-L{lib_dir}", "-lbmoe_b200", "-Xlinker", "-rpath", "-Xlinker",
+                  "$ORIGIN/../../../blackwell-moe-kernel-scheduler_b200/lib", "-o", str(out)])
+        built.append(out)
+    return built
+
+
 if __name__ == "__main__":
     print(build_oracle())
     print(build_reference())
+    print(build_reference_harness())
