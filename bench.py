@@ -525,6 +525,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-single-gpu-ref", action="store_true")
+    ap.add_argument("--ep-groups", type=int, default=4,
+                    help="expert groups pipelined through exchange and GEMM (multi-GPU)")
+    ap.add_argument("--comm-sms", type=int, default=8,
+                    help="SMs the pipelined GEMM leaves to the exchange kernels")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     args = ap.parse_args()
     if args.warmup < 3:

@@ -48,7 +48,7 @@ class CudaOps:
         from .engine import GroupedGemmPlan
 
         self._lib = _capi.load()
-        self._plan = GroupedGemmPlan()
+        self._plans = [GroupedGemmPlan()]
         self.scheduler = scheduler
         self.plan_options = plan_options
         self.launches = 0
@@ -72,9 +72,16 @@ class CudaOps:
             self.launches += 1
         return out
 
-    def grouped_gemm(self, a, w, counts, out=None):
+    def grouped_gemm(self, a, w, counts, out=None, slot=0):
+        """``slot`` selects the plan object; launches that may be in flight at the
+        same time (pipelined expert groups) must use different slots."""
         import torch
 
+        from .engine import GroupedGemmPlan
+
+        while len(self._plans) <= slot:
+            self._plans.append(GroupedGemmPlan())
+        plan = self._plans[slot]
         total = int(sum(counts))
         n = int(w.shape[1])
         if out is None:
@@ -82,24 +89,29 @@ class CudaOps:
         if total == 0:
             return out
         stream = torch.cuda.current_stream()
-        _capi.check(self._plan.initialize_packed(a, w, out, counts, scheduler=self.scheduler,
-                                                 stream=stream, **self.plan_options),
+        _capi.check(plan.initialize_packed(a, w, out, counts, scheduler=self.scheduler,
+                                           stream=stream, **self.plan_options),
                     "bmoe_plan_initialize")
-        _capi.check(self._plan.run(stream), "bmoe_plan_run")
+        _capi.check(plan.run(stream), "bmoe_plan_run")
         self.launches += 3  # worklist plan + expand, grouped GEMM
         return out
 
     def poll(self):
-        status, report = self._plan.poll()
-        if status not in (_capi.OK, _capi.INVALID_ARGUMENT):  # INVALID = never initialised
-            raise _capi.EngineError(status, f"grouped GEMM (site {report.code}, cta {report.cta})")
+        for plan in self._plans:
+            status, report = plan.poll()
+            if status not in (_capi.OK, _capi.INVALID_ARGUMENT):  # INVALID = never initialised
+                raise _capi.EngineError(
+                    status, f"grouped GEMM (site {report.code}, cta {report.cta})")
 
 
 class ExpertParallelLayer:
     """One expert-parallel grouped GEMM (e.g. an MoE up-projection)."""
 
     def __init__(self, owner: Sequence[int], n: int, k: int, *, rank: int, world: int,
-                 group=None, ops=None):
+                 group=None, ops=None, pipeline_groups: int = 1):
+        """``pipeline_groups`` > 1 splits every rank's experts into that many
+        groups and overlaps the exchange of one group with the GEMM of another."""
+        self.pipeline_groups = max(1, int(pipeline_groups))
         self.owner = [int(o) for o in owner]
         self.experts = len(self.owner)
         self.n, self.k = n, k
@@ -155,6 +167,9 @@ class ExpertParallelLayer:
         Returns y [T_local * top_k, n]: row j is token j // top_k routed to
         expert_ids.flatten()[j]."""
         import torch
+
+        if self.world > 1 and self.pipeline_groups > 1:
+            return self._forward_pipelined(x, expert_ids, w_local, record_events)
 
         dev = x.device
         top_k = int(expert_ids.shape[1])
@@ -237,6 +252,125 @@ class ExpertParallelLayer:
         mark("finish")
         self._marks = marks
         self.last_local_m = local_m
+        return y
+
+    # ------------------------------------------------------------ pipelined --
+    def _group_tables(self):
+        """Expert -> pipeline group, and the send order (group, owner, expert)."""
+        import torch
+
+        if not hasattr(self, "_gtables"):
+            groups = self.pipeline_groups
+            group_of = [0] * self.experts
+            local_bounds = None
+            for r in range(self.world):
+                mine = [e for e in range(self.experts) if self.owner[e] == r]
+                for i, e in enumerate(mine):
+                    group_of[e] = i * groups // max(1, len(mine))
+                if r == self.rank:
+                    cuts = [0] * (groups + 1)
+                    for i in range(len(mine)):
+                        cuts[i * groups // max(1, len(mine)) + 1] = i + 1
+                    for g in range(1, groups + 1):
+                        cuts[g] = max(cuts[g], cuts[g - 1])
+                    local_bounds = cuts
+            order = sorted(range(self.experts), key=lambda e: (group_of[e], self.owner[e], e))
+            position = torch.empty(self.experts, dtype=torch.int64)
+            position[torch.tensor(order, dtype=torch.int64)] = torch.arange(self.experts)
+            self._gtables = (torch.tensor(group_of, dtype=torch.int64), position, local_bounds)
+        return self._gtables
+
+    def _forward_pipelined(self, x, expert_ids, w_local, record_events=False):
+        """Same result as forward(); the experts of every rank are split into
+        ``pipeline_groups`` groups whose dispatch / GEMM / combine overlap: all
+        dispatches are queued on the communication stream up front, each group's
+        GEMM starts when its rows have arrived, and its combine is queued behind."""
+        import torch
+        import torch.distributed as dist
+
+        dev = x.device
+        groups = self.pipeline_groups
+        top_k = int(expert_ids.shape[1])
+        flat_ids = expert_ids.reshape(-1)
+        assignments = int(flat_ids.numel())
+        marks = []
+
+        def mark(name):
+            if record_events and x.is_cuda:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record(torch.cuda.current_stream())
+                marks.append((name, ev))
+
+        mark("start")
+        local_counts = torch.zeros(self.experts, dtype=torch.int64, device=dev)
+        local_counts.scatter_add_(0, flat_ids, torch.ones_like(flat_ids))
+        counts_all = self._all_gather_counts(local_counts).cpu()
+        owner_t, local_t, _ = self._host_tables()
+        group_t, position, bounds = self._group_tables()
+        send_matrix = torch.zeros(groups * self.world, dtype=torch.int64).scatter_add_(
+            0, group_t * self.world + owner_t, counts_all[self.rank]).reshape(groups, self.world)
+        send_rows = send_matrix.sum(dim=1).tolist()
+        send_off = [0]
+        for r in send_rows:
+            send_off.append(send_off[-1] + r)
+        mark("counts")
+
+        if getattr(self, "_gposition_dev", None) is None or self._gposition_dev.device != dev:
+            self._gposition_dev = position.to(dev)
+        keys = self._gposition_dev[flat_ids]
+        perm = torch.sort(keys, stable=True).indices
+        token_of = torch.div(perm, top_k, rounding_mode="floor")
+        d_recv = torch.empty(assignments, self.n, dtype=x.dtype, device=dev)
+
+        # queue every group's pack + dispatch
+        staged = []
+        for g in range(groups):
+            lo, hi = bounds[g], bounds[g + 1]
+            recv_matrix = counts_all[:, local_t[lo:hi]]                 # [world, E_g]
+            recv_splits = recv_matrix.sum(dim=1).tolist()
+            send_splits = send_matrix[g].tolist()
+            send = self.ops.gather_rows(x, token_of[send_off[g]:send_off[g + 1]])
+            recv = torch.empty(sum(recv_splits), self.k, dtype=x.dtype, device=dev)
+            work = dist.all_to_all_single(recv, send, recv_splits, send_splits,
+                                          group=self.group, async_op=True)
+            staged.append((lo, hi, recv_matrix, recv_splits, send_splits, send, recv, work))
+        mark("pack+dispatch issue")
+
+        combines = []
+        local_m_all = []
+        for g, (lo, hi, recv_matrix, recv_splits, send_splits, send, recv, work) in enumerate(staged):
+            work.wait()
+            local_m = recv_matrix.sum(dim=0).tolist()
+            local_m_all.extend(local_m)
+            total_local = int(sum(local_m))
+            seg_len = recv_matrix.t().contiguous().reshape(-1)
+            src_base = torch.cumsum(torch.tensor([0] + recv_splits[:-1], dtype=torch.int64), 0)
+            within = torch.cumsum(recv_matrix, dim=1) - recv_matrix
+            seg_start = (src_base[:, None] + within).t().contiguous().reshape(-1)
+            seg_len_d, seg_start_d = seg_len.to(dev), seg_start.to(dev)
+            out_start = torch.cumsum(seg_len_d, 0) - seg_len_d
+            index = (torch.repeat_interleave(seg_start_d - out_start, seg_len_d,
+                                             output_size=total_local)
+                     + torch.arange(total_local, device=dev, dtype=torch.int64))
+            a_packed = self.ops.gather_rows(recv, index)
+            d_packed = self.ops.grouped_gemm(a_packed, w_local[lo:hi], local_m, slot=g)
+            inverse = torch.empty(total_local, dtype=torch.int64, device=dev)
+            inverse[index] = torch.arange(total_local, device=dev, dtype=torch.int64)
+            d_send = self.ops.gather_rows(d_packed, inverse)
+            back = d_recv[send_off[g]:send_off[g + 1]]
+            cwork = dist.all_to_all_single(back, d_send, send_splits, recv_splits,
+                                           group=self.group, async_op=True)
+            combines.append((cwork, d_send, a_packed, d_packed))
+        mark("gemm groups issue")
+        for cwork, *_ in combines:
+            cwork.wait()
+        mark("combine")
+        inv_perm = torch.empty(assignments, dtype=torch.int64, device=dev)
+        inv_perm[perm] = torch.arange(assignments, device=dev, dtype=torch.int64)
+        y = self.ops.gather_rows(d_recv, inv_perm)
+        mark("finish")
+        self._marks = marks
+        self.last_local_m = local_m_all
         return y
 
     def phase_times_ms(self):

@@ -32,7 +32,7 @@ class OracleOps:
     def gather_rows(self, src, index, out=None):
         return src.index_select(0, index)
 
-    def grouped_gemm(self, a, w, counts, out=None):
+    def grouped_gemm(self, a, w, counts, out=None, slot=0):
         import torch
 
         n, k = int(w.shape[1]), int(w.shape[2])
@@ -44,7 +44,7 @@ class OracleOps:
         return torch.from_numpy(bits.view(np.int16).copy()).view(torch.bfloat16)
 
 
-def worker(rank, world, port, tmpdir):
+def worker(rank, world, port, tmpdir, groups=1):
     for p in (ROOT, ROOT / "tests", ROOT / "oracle"):
         sys.path.insert(0, str(p))
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
@@ -73,7 +73,8 @@ def worker(rank, world, port, tmpdir):
         bounds = [0] + [tokens * (r + 1) // world + (3 if r == 0 else 0) for r in range(world)]
         bounds[-1] = tokens
         lo, hi = bounds[rank], bounds[rank + 1]
-        layer = ep.ExpertParallelLayer(owner, n, k, rank=rank, world=world, ops=OracleOps())
+        layer = ep.ExpertParallelLayer(owner, n, k, rank=rank, world=world, ops=OracleOps(),
+                                       pipeline_groups=groups)
         w_local = w_all[layer.local_experts]
         y = layer.forward(x_all[lo:hi], ids_all[lo:hi], w_local)
 
@@ -91,11 +92,11 @@ def worker(rank, world, port, tmpdir):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 3])
-def test_ep_round_trip_equals_single_process(world, tmp_path, engine):
+@pytest.mark.parametrize("world,groups", [(2, 1), (3, 1), (2, 3), (3, 2)])
+def test_ep_round_trip_equals_single_process(world, groups, tmp_path, engine):
     import torch.multiprocessing as mp
 
-    mp.spawn(worker, args=(world, free_port(), str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(worker, args=(world, free_port(), str(tmp_path), groups), nprocs=world, join=True)
     rows = 0
     for r in range(world):
         same, count, local = Path(tmp_path, f"rank{r}.txt").read_text().split()

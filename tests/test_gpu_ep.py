@@ -95,12 +95,17 @@ def _ep_worker(rank, world, port, tmpdir):
         owner, _ = ep.place_experts(torch.bincount(ids.reshape(-1), minlength=40).tolist(),
                                     world, 512)
         lo, hi = tokens * rank // world, tokens * (rank + 1) // world
-        layer = ep.ExpertParallelLayer(owner, 512, 320, rank=rank, world=world,
-                                       ops=ep.CudaOps(scheduler="auto"))
-        y = layer.forward(x[lo:hi].cuda(), ids[lo:hi].cuda(), w[layer.local_experts].cuda())
-        layer.ops.poll()
         want = reference_output(engine, x, ids, w, 4)[lo * 4:hi * 4]
-        same = torch.equal(y.view(torch.int16), want.view(torch.int16))
+        same = True
+        for groups, opts in ((1, {}), (3, {"cta_group": 2, "cta_count": 60})):
+            layer = ep.ExpertParallelLayer(owner, 512, 320, rank=rank, world=world,
+                                           ops=ep.CudaOps(scheduler="dynamic_queue", **opts),
+                                           pipeline_groups=groups)
+            for _ in range(2):
+                y = layer.forward(x[lo:hi].cuda(), ids[lo:hi].cuda(),
+                                  w[layer.local_experts].cuda())
+            layer.ops.poll()
+            same = same and torch.equal(y.view(torch.int16), want.view(torch.int16))
         Path(tmpdir, f"rank{rank}.txt").write_text(str(int(same)))
         dist.barrier()
     finally:
