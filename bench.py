@@ -525,7 +525,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-single-gpu-ref", action="store_true")
-    ap.add_argument("--ep-groups", type=int, default=4,
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="multi-GPU token exchange: routing kernels over peer memory, or "
+                         "NCCL all-to-all with local re-packing")
+    ap.add_argument("--ep-groups", type=int, default=1,
                     help="expert groups pipelined through exchange and GEMM (multi-GPU)")
     ap.add_argument("--comm-sms", type=int, default=8,
                     help="SMs the pipelined GEMM leaves to the exchange kernels")

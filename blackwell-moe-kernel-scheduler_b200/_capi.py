@@ -299,6 +299,15 @@ SIGNATURES = {
         C.c_int,
         [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint32, C.c_void_p],
     ),
+    "bmoe_route_rows": (
+        C.c_int,
+        [C.c_void_p, C.c_uint32, C.c_uint64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32,
+         C.c_uint64, C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint32, C.c_uint32, C.c_void_p],
+    ),
+    "bmoe_peer_alloc": (C.c_int, [C.c_uint64, _P(C.c_void_p), C.c_void_p]),
+    "bmoe_peer_open": (C.c_int, [C.c_void_p, _P(C.c_void_p)]),
+    "bmoe_peer_close": (C.c_int, [C.c_void_p]),
+    "bmoe_peer_free": (C.c_int, [C.c_void_p]),
     "bmoe_build_info": (C.c_char_p, []),
 }
 

@@ -340,6 +340,7 @@ class ExpertParallelLayer:
         local_m_all = []
         for g, (lo, hi, recv_matrix, recv_splits, send_splits, send, recv, work) in enumerate(staged):
             work.wait()
+            mark(f"dispatch {g} arrived")
             local_m = recv_matrix.sum(dim=0).tolist()
             local_m_all.extend(local_m)
             total_local = int(sum(local_m))
@@ -361,7 +362,7 @@ class ExpertParallelLayer:
             cwork = dist.all_to_all_single(back, d_send, send_splits, recv_splits,
                                            group=self.group, async_op=True)
             combines.append((cwork, d_send, a_packed, d_packed))
-        mark("gemm groups issue")
+            mark(f"gemm {g}")
         for cwork, *_ in combines:
             cwork.wait()
         mark("combine")

@@ -87,13 +87,24 @@ def run(args, spec, workload):
         pair = args.cta_group != 1
         plan_options = {"cta_group": 2 if pair else 1,
                         "cta_count": max(1, (sms - args.comm_sms) // (2 if pair else 1))}
-    ops = ep.CudaOps(scheduler=args.policy, **plan_options)
-    layer = ep.ExpertParallelLayer(owner, n, k, rank=rank, world=world, ops=ops,
-                                   pipeline_groups=groups)
-    # un-pipelined twin for the per-phase split
-    plain = layer if groups == 1 else ep.ExpertParallelLayer(
-        owner, n, k, rank=rank, world=world,
-        ops=ep.CudaOps(scheduler=args.policy, cta_group=args.cta_group))
+    if args.exchange == "peer":
+        from bmoe_b200 import ep_peer
+
+        # Row capacity: every assignment of the batch could land on one rank.
+        layer = ep_peer.PeerExpertParallelLayer(
+            owner, n, k, rank=rank, world=world, rows_cap=tokens * top_k,
+            scheduler=args.policy, cta_group=args.cta_group)
+        ops = layer          # launches / poll live on the layer
+        plain = layer
+        groups = 1
+    else:
+        ops = ep.CudaOps(scheduler=args.policy, **plan_options)
+        layer = ep.ExpertParallelLayer(owner, n, k, rank=rank, world=world, ops=ops,
+                                       pipeline_groups=groups)
+        # un-pipelined twin for the per-phase split
+        plain = layer if groups == 1 else ep.ExpertParallelLayer(
+            owner, n, k, rank=rank, world=world,
+            ops=ep.CudaOps(scheduler=args.policy, cta_group=args.cta_group))
     w_local = _expert_weights(torch, layer.local_experts, n, k, dev)
     total_flops = 2.0 * tokens * top_k * n * k
     stream = torch.cuda.current_stream()
@@ -164,6 +175,8 @@ def run(args, spec, workload):
     single_gpu = None
     if world > 1 and not args.no_single_gpu_ref:
         if rank == 0:
+            if args.exchange == "peer":
+                pass  # peer buffers stay mapped by the other ranks until they exit
             del w_local, layer, ops, plain
             torch.cuda.empty_cache()
             solo_owner = [0] * spec["experts"]
@@ -209,6 +222,7 @@ def run(args, spec, workload):
         "config": {"workload": workload, "experts": spec["experts"], "top_k": top_k,
                    "tokens": tokens, "k": k, "n": n, "policy": args.policy,
                    "parallelism": f"ep{world}", "placement": "tile-count LPT",
+                   "exchange": args.exchange,
                    "pipeline_groups": groups, "comm_sms": args.comm_sms if groups > 1 else 0,
                    "rank_tiles": rank_tiles, "rank0_rows": local_rows,
                    "max_rank_rows": rows_max, "mean_rank_rows": tokens * top_k / world,
@@ -216,8 +230,11 @@ def run(args, spec, workload):
                    "note": "with more than one GPU the benchmark runs the expert-parallel "
                            "configuration; the one-GPU line of bench.py runs the "
                            "Mixtral-shaped grouped GEMM, see single_gpu_same_workload",
-                   "step": "count all-gather + pack + all-to-all dispatch + unpack + "
-                           "grouped GEMM + repack + all-to-all combine + un-permute"},
+                   "step": ("count all-gather + push rows into the owners' packed A over "
+                            "NVLink + grouped GEMM + pull result rows back"
+                            if args.exchange == "peer" else
+                            "count all-gather + pack + all-to-all dispatch + unpack + "
+                            "grouped GEMM + repack + all-to-all combine + un-permute")},
         "p50_us": bench.percentile(step_samples, 0.5) * 1e3,
         "p99_us": bench.percentile(step_samples, 0.99) * 1e3,
         "phases_ms_max_over_ranks": phases_ms,

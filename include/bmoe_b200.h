@@ -430,6 +430,35 @@ int bmoe_gather_rows(const void* src_dev, void* dst_dev, const int64_t* index_de
                      uint64_t rows, uint64_t src_rows, uint32_t row_bytes,
                      void* stream);
 
+/* Row routing over peer memory (NVLink): for i in [0, rows)
+ *   dst_bases[dst_rank[i]] + dst_row[i] * row_bytes  <-
+ *   src_bases[src_rank[i]] + src_row[i] * row_bytes
+ * src_bases_dev / dst_bases_dev: DEVICE arrays of n_src / n_dst base pointers
+ * (own buffers or buffers of other GPUs opened with bmoe_peer_open). A NULL rank
+ * array means entry 0 for every row, a NULL row array means row i. Rows whose
+ * rank or row index is out of range (>= n_*, >= *_rows_cap) are skipped. One
+ * kernel of plain loads and stores; max_ctas bounds its grid (0 = default) so it
+ * can run beside another kernel. The expert-parallel dispatch (push token rows
+ * into the owner's expert-major A) and combine (pull result rows back) are each
+ * one call. row_bytes must be a multiple of 16. */
+int bmoe_route_rows(const void* const* src_bases_dev, uint32_t n_src,
+                    uint64_t src_rows_cap, const int32_t* src_rank_dev,
+                    const int64_t* src_row_dev, void* const* dst_bases_dev,
+                    uint32_t n_dst, uint64_t dst_rows_cap,
+                    const int32_t* dst_rank_dev, const int64_t* dst_row_dev,
+                    uint64_t rows, uint32_t row_bytes, uint32_t max_ctas,
+                    void* stream);
+
+/* Device buffers that other processes on the node can map (CUDA IPC):
+ * bmoe_peer_alloc allocates `bytes` and writes a 64-byte handle; another process
+ * passes that handle to bmoe_peer_open and gets a pointer valid on ITS device
+ * (peer access over NVLink). bmoe_peer_close unmaps, bmoe_peer_free releases the
+ * owner's allocation. */
+int bmoe_peer_alloc(uint64_t bytes, void** ptr_out, uint8_t* handle_out);
+int bmoe_peer_open(const uint8_t* handle, void** ptr_out);
+int bmoe_peer_close(void* ptr);
+int bmoe_peer_free(void* ptr);
+
 /* Library build information ("sm_100a", CUDA runtime version, ...). */
 const char* bmoe_build_info(void);
 

@@ -118,3 +118,41 @@ def test_placement_is_deterministic_lpt(engine):
     assert all(capped.count(r) == 2 for r in range(4))
     with pytest.raises(Exception):
         ep.place_experts(counts, 3, 256, max_experts_per_rank=2)  # 6 slots for 8 experts
+
+
+def test_peer_route_plan_builds_the_single_gpu_packing(engine):
+    """plan_routes() (index arithmetic of the peer-memory exchange) on simulated
+    ranks: every owner's buffer is written exactly once per row, expert-major, and
+    inside an expert in global assignment order - the single-GPU packing."""
+    import torch
+
+    from bmoe_b200 import ep, ep_peer
+
+    gen = torch.Generator().manual_seed(9)
+    world, experts, top_k, tokens = 3, 10, 2, 50
+    probs = torch.rand(experts, generator=gen) + 0.05
+    probs[4] = 0.0
+    ids_all = torch.multinomial(probs.expand(tokens, -1), top_k, replacement=False, generator=gen)
+    counts = torch.bincount(ids_all.reshape(-1), minlength=experts).tolist()
+    owner, _ = ep.place_experts(counts, world, 256, tile_m=128, tile_n=128)
+    bounds = [0, 13, 31, tokens]
+    counts_all = torch.stack([
+        torch.bincount(ids_all[bounds[r]:bounds[r + 1]].reshape(-1), minlength=experts)
+        for r in range(world)]).to(torch.int64)
+    # global assignment id written into the owner's buffer slot
+    buffers = [dict() for _ in range(world)]
+    for r in range(world):
+        flat = ids_all[bounds[r]:bounds[r + 1]].reshape(-1)
+        perm, src_token, dst_rank, dst_row = ep_peer.plan_routes(counts_all, owner, r, flat, top_k)
+        assert torch.equal(src_token, perm // top_k)
+        for i in range(perm.numel()):
+            slot = buffers[int(dst_rank[i])]
+            assert int(dst_row[i]) not in slot, "two assignments routed to one row"
+            slot[int(dst_row[i])] = bounds[r] * top_k + int(perm[i])
+    flat_all = ids_all.reshape(-1)
+    for r in range(world):
+        mine = [e for e in range(experts) if owner[e] == r]
+        want = [j for e in mine for j in range(flat_all.numel()) if int(flat_all[j]) == e]
+        got = [buffers[r][row] for row in range(len(buffers[r]))]
+        assert sorted(buffers[r]) == list(range(len(want)))
+        assert got == want

@@ -76,6 +76,47 @@ def test_single_rank_layer_equals_plain_engine(engine):
     assert torch.equal(y.view(torch.int16), want.view(torch.int16))
 
 
+def test_route_rows_and_single_rank_peer_layer(engine):
+    """bmoe_route_rows against index_select / index_copy, and the peer-memory layer
+    on one rank (its own buffers only) against the plain engine."""
+    import ctypes as C
+
+    import torch
+
+    from bmoe_b200 import ep, ep_peer
+
+    lib = engine._capi.load()
+    gen = torch.Generator().manual_seed(5)
+    src = torch.randn(300, 512, generator=gen).to(torch.bfloat16).cuda()
+    dst = torch.zeros(400, 512, dtype=torch.bfloat16, device="cuda")
+    src_row = torch.randint(0, 300, (350,), generator=gen).cuda()
+    dst_row = torch.randperm(400, generator=gen)[:350].cuda()
+    dst_row[7] = 4000  # out of range: skipped
+    bases_s = torch.tensor([src.data_ptr()], dtype=torch.int64, device="cuda")
+    bases_d = torch.tensor([dst.data_ptr()], dtype=torch.int64, device="cuda")
+    rc = lib.bmoe_route_rows(bases_s.data_ptr(), 1, 300, None, src_row.data_ptr(),
+                             bases_d.data_ptr(), 1, 400, None, dst_row.data_ptr(), 350, 1024, 0,
+                             None)
+    assert rc == 0
+    want = torch.zeros_like(dst)
+    keep = torch.ones(350, dtype=torch.bool)
+    keep[7] = False
+    want[dst_row[keep.cuda()]] = src[src_row[keep.cuda()]]
+    assert torch.equal(dst.view(torch.int16), want.view(torch.int16))
+
+    ids, x, w = make_problem()
+    owner = [0] * 40
+    layer = ep_peer.PeerExpertParallelLayer(owner, 512, 320, rank=0, world=1, rows_cap=2400)
+    try:
+        for _ in range(2):
+            y = layer.forward(x.cuda(), ids.cuda(), w.cuda())
+        layer.poll()
+        want = reference_output(engine, x, ids, w, 4)
+        assert torch.equal(y.view(torch.int16), want.view(torch.int16))
+    finally:
+        layer.close()
+
+
 def _ep_worker(rank, world, port, tmpdir):
     for p in (ROOT, ROOT / "tests", ROOT / "oracle"):
         sys.path.insert(0, str(p))
@@ -106,6 +147,16 @@ def _ep_worker(rank, world, port, tmpdir):
                                   w[layer.local_experts].cuda())
             layer.ops.poll()
             same = same and torch.equal(y.view(torch.int16), want.view(torch.int16))
+        from bmoe_b200 import ep_peer
+
+        peer = ep_peer.PeerExpertParallelLayer(owner, 512, 320, rank=rank, world=world,
+                                               rows_cap=2400, scheduler="clc")
+        for _ in range(3):
+            y = peer.forward(x[lo:hi].cuda(), ids[lo:hi].cuda(), w[peer.local_experts].cuda())
+        peer.poll()
+        same = same and torch.equal(y.view(torch.int16), want.view(torch.int16))
+        dist.barrier()
+        peer.close()
         Path(tmpdir, f"rank{rank}.txt").write_text(str(int(same)))
         dist.barrier()
     finally:
