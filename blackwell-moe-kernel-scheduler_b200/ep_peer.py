@@ -35,38 +35,82 @@ class _RawCudaBuffer:
         }
 
 
-def plan_routes(counts_all, owner: Sequence[int], rank: int, flat_ids, top_k: int):
+class RoutePlanner:
     """Destination of every local assignment in its owner's expert-major buffer.
 
-    counts_all: host int64 [world, experts]; flat_ids: device int64 [assignments].
-    Returns (perm, src_token, dst_rank, dst_row): ``perm[i]`` is the assignment that
-    is i-th when this rank's assignments are sorted by expert (stable); it goes to
-    row ``dst_row[i]`` of rank ``dst_rank[i]``. Rows of one expert are laid out by
-    source rank, then by assignment order - the order of a single-GPU run.
+    Static per (owner map, rank): the tables below. Per step, ``plan`` needs the
+    host count matrix [world, experts] and the device expert ids.
+
+    Rows of one expert are laid out by source rank, then by assignment order -
+    the order of a single-GPU run. The traversal order of the returned arrays is
+    staggered by rank (rank r starts with the rows bound for rank r+1, then r+2,
+    ...), so that at any moment the ranks push to, or pull from, different GPUs
+    instead of all converging on the owner of the busiest expert.
     """
-    import torch
 
-    dev = flat_ids.device
-    experts = counts_all.shape[1]
-    owner_t = torch.tensor(list(owner), dtype=torch.int64)
-    totals = counts_all.sum(dim=0)                                   # rows per expert
-    # offset of every expert inside its owner's packed buffer (ascending expert id)
-    owner_off = torch.zeros(experts, dtype=torch.int64)
-    for r in torch.unique(owner_t).tolist():
-        mask = owner_t == r
-        t = totals[mask]
-        owner_off[mask] = torch.cumsum(t, 0) - t
-    dst_base = owner_off + counts_all[:rank].sum(dim=0)               # + rows of earlier sources
-    local_counts = counts_all[rank]
-    start = torch.cumsum(local_counts, 0) - local_counts
+    def __init__(self, owner: Sequence[int], rank: int, world: int):
+        import torch
 
-    perm = torch.sort(flat_ids, stable=True).indices
-    sorted_e = flat_ids[perm]
-    within = torch.arange(perm.numel(), device=dev, dtype=torch.int64) - start.to(dev)[sorted_e]
-    dst_row = dst_base.to(dev)[sorted_e] + within
-    dst_rank = owner_t.to(dev)[sorted_e].to(torch.int32)
-    src_token = torch.div(perm, top_k, rounding_mode="floor")
-    return perm, src_token, dst_rank, dst_row
+        self.rank, self.world = rank, world
+        self.experts = len(owner)
+        self.owner_t = torch.tensor(list(owner), dtype=torch.int64)
+        # experts ordered by (owner, id): packed order inside every owner's buffer
+        self.by_owner = torch.tensor(
+            sorted(range(self.experts), key=lambda e: (owner[e], e)), dtype=torch.int64)
+        self.owner_in_order = self.owner_t[self.by_owner]
+        # traversal order of this rank: staggered destination, then expert id
+        stagger = (self.owner_t - rank - 1) % world
+        self.key_of_expert = stagger * self.experts + torch.arange(self.experts)
+        self.by_key = torch.argsort(self.key_of_expert)
+        self._dev = None
+
+    def _device_tables(self, dev):
+        if self._dev is None or self._dev[0].device != dev:
+            self._dev = (self.key_of_expert.to(dev), self.owner_t.to(dev).to(self._i32()))
+        return self._dev
+
+    @staticmethod
+    def _i32():
+        import torch
+
+        return torch.int32
+
+    def plan(self, counts_all, flat_ids, top_k: int):
+        """Returns (perm, src_token, dst_rank, dst_row); ``perm[i]`` is the local
+        assignment handled i-th, bound for row ``dst_row[i]`` of rank ``dst_rank[i]``."""
+        import torch
+
+        dev = flat_ids.device
+        totals = counts_all.sum(dim=0)
+        # offset of each expert inside its owner's buffer
+        t_order = totals[self.by_owner]
+        excl = torch.cumsum(t_order, 0) - t_order
+        per_owner = torch.zeros(self.world, dtype=torch.int64).scatter_add_(
+            0, self.owner_in_order, t_order)
+        seg_base = torch.cumsum(per_owner, 0) - per_owner
+        owner_off = torch.empty(self.experts, dtype=torch.int64)
+        owner_off[self.by_owner] = excl - seg_base[self.owner_in_order]
+        dst_base = owner_off + counts_all[:self.rank].sum(dim=0)
+        # first position of each expert in this rank's traversal order
+        local = counts_all[self.rank]
+        l_order = local[self.by_key]
+        start = torch.empty(self.experts, dtype=torch.int64)
+        start[self.by_key] = torch.cumsum(l_order, 0) - l_order
+        tables = torch.stack([dst_base, start]).to(dev)               # one small H2D copy
+
+        key_dev, owner_dev = self._device_tables(dev)
+        perm = torch.sort(key_dev[flat_ids], stable=True).indices
+        sorted_e = flat_ids[perm]
+        within = torch.arange(perm.numel(), device=dev, dtype=torch.int64) - tables[1][sorted_e]
+        dst_row = tables[0][sorted_e] + within
+        dst_rank = owner_dev[sorted_e]
+        src_token = torch.div(perm, top_k, rounding_mode="floor")
+        return perm, src_token, dst_rank, dst_row
+
+
+def plan_routes(counts_all, owner: Sequence[int], rank: int, flat_ids, top_k: int):
+    """One-shot form of ``RoutePlanner(...).plan(...)``."""
+    return RoutePlanner(owner, rank, counts_all.shape[0]).plan(counts_all, flat_ids, top_k)
 
 
 class PeerBuffers:
@@ -151,10 +195,23 @@ class PeerExpertParallelLayer:
         dev = torch.device("cuda", torch.cuda.current_device())
         self._token = torch.zeros(1, dtype=torch.int32, device=dev)
         self._local_t = torch.tensor(self.local_experts, dtype=torch.int64)
+        self._planner = RoutePlanner(self.owner, rank, world)
+        self._base_cache = {}
 
     def close(self):
         self.plan.close()
         self.buffers.close()
+
+    def _base_of(self, tensor):
+        """One-entry device pointer table for a local tensor (cached by address)."""
+        import torch
+
+        key = tensor.data_ptr()
+        if key not in self._base_cache:
+            if len(self._base_cache) > 64:
+                self._base_cache.clear()
+            self._base_cache[key] = torch.tensor([key], dtype=torch.int64, device=tensor.device)
+        return self._base_cache[key]
 
     def _barrier(self):
         """Stream-ordered cross-rank barrier (no host synchronisation)."""
@@ -208,12 +265,11 @@ class PeerExpertParallelLayer:
         total_local = int(sum(local_m))
         if total_local > self.buffers.rows_cap:
             raise RuntimeError("routed rows exceed the peer buffer capacity")
-        perm, src_token, dst_rank, dst_row = plan_routes(counts_all, self.owner, self.rank,
-                                                         flat_ids, top_k)
+        perm, src_token, dst_rank, dst_row = self._planner.plan(counts_all, flat_ids, top_k)
         mark("counts")
 
         # dispatch: push token rows into the owners' expert-major A
-        x_base = torch.tensor([x.data_ptr()], dtype=torch.int64, device=dev)
+        x_base = self._base_of(x)
         self._route(x_base, 1, int(x.shape[0]), None, src_token,
                     self.buffers.a_bases, self.world, self.buffers.rows_cap, dst_rank, dst_row,
                     assignments, self.k * 2)
@@ -233,7 +289,7 @@ class PeerExpertParallelLayer:
 
         # combine: pull result rows back into assignment order
         y = torch.empty(assignments, self.n, dtype=x.dtype, device=dev)
-        y_base = torch.tensor([y.data_ptr()], dtype=torch.int64, device=dev)
+        y_base = self._base_of(y)
         self._route(self.buffers.d_bases, self.world, self.buffers.rows_cap, dst_rank, dst_row,
                     y_base, 1, assignments, None, perm, assignments, self.n * 2)
         mark("combine")
