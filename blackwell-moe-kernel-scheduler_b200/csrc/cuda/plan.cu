@@ -1,9 +1,12 @@
 // C interface, device half: the grouped-GEMM plan (section 3 of bmoe_b200.h).
 //
 // initialize() does everything that can be prepared ahead of a launch: argument
-// checks, policy resolution, H2D copy of the counts, the on-device worklist
-// build, host encoding of one TMA descriptor triple per active expert, queue
-// and status words. run() is a single kernel launch. Behavioural contract
+// checks, policy resolution, host encoding of one TMA descriptor triple per
+// active expert, ONE asynchronous copy (from pinned staging memory) of counts,
+// descriptors, queue and status words, and the on-device worklist build. It
+// enqueues on the plan's stream and does not wait for the device; a plan must
+// not be re-initialised while launches of it are still in flight on ANOTHER
+// stream. run() is a single kernel launch. Behavioural contract
 // (status codes, null / zero handling, stream override) follows
 // baselines/cutlass/cutlass_baseline.cu:195-377 of the reference.
 #include <cuda.h>
@@ -83,6 +86,27 @@ struct DeviceBlock {
   }
 };
 
+// Grow-only pinned host staging area (asynchronous H2D copies need it).
+struct PinnedBlock {
+  void* ptr = nullptr;
+  size_t bytes = 0;
+  bool reserve(size_t want) {
+    if (want <= bytes) return true;
+    release();
+    if (cudaHostAlloc(&ptr, want, cudaHostAllocDefault) != cudaSuccess) {
+      ptr = nullptr;
+      return false;
+    }
+    bytes = want;
+    return true;
+  }
+  void release() {
+    if (ptr != nullptr) cudaFreeHost(ptr);
+    ptr = nullptr;
+    bytes = 0;
+  }
+};
+
 bool misaligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; }
 
 }  // namespace
@@ -96,14 +120,13 @@ struct bmoe_plan {
   cudaEvent_t setup_done = nullptr;
   int device = -1;
 
-  DeviceBlock counts;     // uint32 [experts]
-  DeviceBlock tmaps;      // CUtensorMap [3][experts]
+  // One metadata block, filled by a single copy from pinned staging memory:
+  //   [0, 256) queue words   [256, 512) DeviceStatus
+  //   [512, ...) counts uint32 [experts]   then CUtensorMap [3][experts] (128-aligned)
+  DeviceBlock meta;
+  PinnedBlock staging;
   DeviceBlock worklist;   // bmoe_tile [capacity]
   DeviceBlock workspace;  // worklist builder arrays
-  DeviceBlock control;    // queue words (256 B) + DeviceStatus (256 B)
-
-  std::vector<CUtensorMap> host_maps;
-  std::vector<uint32_t> host_counts;
 
   bmoe::GemmParams params{};
   uint32_t units = 0;      // persistent CTAs or CTA pairs (tile count for CLC)
@@ -112,11 +135,10 @@ struct bmoe_plan {
   bool out_f32 = false;
 
   void release_all() {
-    counts.release();
-    tmaps.release();
+    meta.release();
+    staging.release();
     worklist.release();
     workspace.release();
-    control.release();
     if (setup_done != nullptr) cudaEventDestroy(setup_done);
     setup_done = nullptr;
     ready = false;
@@ -299,25 +321,54 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
     return BMOE_INVALID_ARGUMENT;
   }
   const size_t map_bytes = sizeof(CUtensorMap) * 3 * static_cast<size_t>(a.experts);
-  if (!plan->counts.reserve(sizeof(uint32_t) * a.experts) ||
-      !plan->tmaps.reserve(map_bytes) ||
+  const size_t off_counts = 512;
+  const size_t off_maps = (off_counts + sizeof(uint32_t) * a.experts + 127) / 128 * 128;
+  const size_t meta_bytes = off_maps + map_bytes;
+  if (!plan->meta.reserve(meta_bytes) || !plan->staging.reserve(meta_bytes) ||
       !plan->worklist.reserve(sizeof(bmoe_tile) * static_cast<size_t>(tiles)) ||
-      !plan->workspace.reserve(layout.bytes) || !plan->control.reserve(512)) {
+      !plan->workspace.reserve(layout.bytes)) {
     return BMOE_CUDA_ERROR;
   }
-  if (plan->setup_done == nullptr &&
-      cudaEventCreateWithFlags(&plan->setup_done, cudaEventDisableTiming) != cudaSuccess) {
+  if (plan->setup_done == nullptr) {
+    if (cudaEventCreateWithFlags(&plan->setup_done, cudaEventDisableTiming) != cudaSuccess) {
+      return BMOE_CUDA_ERROR;
+    }
+  } else if (cudaEventSynchronize(plan->setup_done) != cudaSuccess) {
+    // the previous set-up copy still reads the staging area
     return BMOE_CUDA_ERROR;
   }
   cudaStream_t stream = plan->setup_stream;
+  uint8_t* const stage = static_cast<uint8_t*>(plan->staging.ptr);
+  uint8_t* const meta = static_cast<uint8_t*>(plan->meta.ptr);
 
-  // ---- counts -> device, worklist built on the device ----
-  plan->host_counts.assign(a.tokens_per_expert, a.tokens_per_expert + a.experts);
-  if (cudaMemcpyAsync(plan->counts.ptr, plan->host_counts.data(),
-                      sizeof(uint32_t) * a.experts, cudaMemcpyHostToDevice,
-                      stream) != cudaSuccess) {
+  // ---- queue and status words, counts, one TMA descriptor triple per active expert ----
+  const uint32_t tail = policy.tail_tiles < tiles ? policy.tail_tiles : tiles;
+  const uint32_t main_end = tiles - tail;
+  std::memset(stage, 0, off_counts);
+  reinterpret_cast<uint32_t*>(stage)[1] = main_end;  // tail counter starts after the main part
+  std::memcpy(stage + off_counts, a.tokens_per_expert, sizeof(uint32_t) * a.experts);
+  CUtensorMap* const maps_a = reinterpret_cast<CUtensorMap*>(stage + off_maps);
+  CUtensorMap* const maps_b = maps_a + a.experts;
+  CUtensorMap* const maps_d = maps_b + a.experts;
+  for (uint32_t e = 0; e < a.experts; ++e) {
+    const uint64_t rows = a.tokens_per_expert[e];
+    if (rows == 0) {
+      std::memset(&maps_a[e], 0, sizeof(CUtensorMap));
+      std::memset(&maps_b[e], 0, sizeof(CUtensorMap));
+      std::memset(&maps_d[e], 0, sizeof(CUtensorMap));
+      continue;
+    }
+    if (!encode_matrix(&maps_a[e], a.a[e], rows, a.k, 128, false) ||
+        !encode_matrix(&maps_b[e], a.b[e], a.n, a.k, tile_n / cta_group, false) ||
+        !encode_matrix(&maps_d[e], a.d[e], rows, a.n, 32, out_f32)) {
+      return BMOE_CUDA_ERROR;
+    }
+  }
+  if (cudaMemcpyAsync(meta, stage, meta_bytes, cudaMemcpyHostToDevice, stream) != cudaSuccess) {
     return BMOE_CUDA_ERROR;
   }
+
+  // ---- worklist built on the device from the device copy of the counts ----
   bmoe_worklist_request request;
   request.experts = a.experts;
   request.n = a.n;
@@ -325,44 +376,14 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
   request.tile_n = tile_n;
   request.order = policy.order;
   request.raster = raster;
-  int rc = bmoe_worklist_build(static_cast<const uint32_t*>(plan->counts.ptr), &request,
+  int rc = bmoe_worklist_build(reinterpret_cast<const uint32_t*>(meta + off_counts), &request,
                                static_cast<bmoe_tile*>(plan->worklist.ptr), tiles,
                                plan->workspace.ptr, stream);
   if (rc != BMOE_OK) return rc;
-
-  // ---- one TMA descriptor triple per active expert ----
-  plan->host_maps.assign(3 * static_cast<size_t>(a.experts), CUtensorMap{});
-  CUtensorMap* const maps_a = plan->host_maps.data();
-  CUtensorMap* const maps_b = maps_a + a.experts;
-  CUtensorMap* const maps_d = maps_b + a.experts;
-  for (uint32_t e = 0; e < a.experts; ++e) {
-    const uint64_t rows = a.tokens_per_expert[e];
-    if (rows == 0) continue;
-    if (!encode_matrix(&maps_a[e], a.a[e], rows, a.k, 128, false) ||
-        !encode_matrix(&maps_b[e], a.b[e], a.n, a.k, tile_n / cta_group, false) ||
-        !encode_matrix(&maps_d[e], a.d[e], rows, a.n, 32, out_f32)) {
-      return BMOE_CUDA_ERROR;
-    }
-  }
-  if (cudaMemcpyAsync(plan->tmaps.ptr, plan->host_maps.data(), map_bytes,
-                      cudaMemcpyHostToDevice, stream) != cudaSuccess) {
-    return BMOE_CUDA_ERROR;
-  }
-
-  // ---- queue and status words ----
-  const uint32_t tail = policy.tail_tiles < tiles ? policy.tail_tiles : tiles;
-  const uint32_t main_end = tiles - tail;
-  uint32_t control_init[128];
-  std::memset(control_init, 0, sizeof(control_init));
-  control_init[1] = main_end;  // tail counter starts where the main part ends
-  if (cudaMemcpyAsync(plan->control.ptr, control_init, sizeof(control_init),
-                      cudaMemcpyHostToDevice, stream) != cudaSuccess) {
-    return BMOE_CUDA_ERROR;
-  }
   if (cudaEventRecord(plan->setup_done, stream) != cudaSuccess) return BMOE_CUDA_ERROR;
 
   // ---- launch parameters ----
-  const CUtensorMap* const dev_maps = static_cast<const CUtensorMap*>(plan->tmaps.ptr);
+  const CUtensorMap* const dev_maps = reinterpret_cast<const CUtensorMap*>(meta + off_maps);
   bmoe::GemmParams& p = plan->params;
   p = bmoe::GemmParams{};
   p.tmap_a = dev_maps;
@@ -375,9 +396,9 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
   p.claim_size = policy.claim_size;
   p.main_end = main_end;
   p.lookahead = policy.sched_mode == bmoe::kSchedStatic ? 0u : 1u;
-  p.queue = static_cast<uint32_t*>(plan->control.ptr);
+  p.queue = reinterpret_cast<uint32_t*>(meta);
   p.status = reinterpret_cast<bmoe::DeviceStatus*>(
-      static_cast<uint8_t*>(plan->control.ptr) + 256);
+      meta + 256);
   p.tile_visits = nullptr;
   p.cta_tiles = nullptr;
   p.wait_budget_ns = 1000000000ull;  // 1 s per wait, then the kernel gives up
@@ -388,9 +409,8 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
   plan->units = policy.one_cta_per_tile ? tiles : (tiles < unit_budget ? tiles : unit_budget);
 
   plan->stats.threadblock_count = plan->units * cta_group;
-  plan->stats.workspace_bytes = plan->counts.bytes + plan->tmaps.bytes +
-                                plan->worklist.bytes + plan->workspace.bytes +
-                                plan->control.bytes;
+  plan->stats.workspace_bytes =
+      plan->meta.bytes + plan->worklist.bytes + plan->workspace.bytes;
   plan->stats.total_tiles = tiles;
   plan->stats.tile_m = tile_m;
   plan->stats.tile_n = tile_n;
@@ -454,7 +474,7 @@ int bmoe_plan_poll(bmoe_plan* plan, bmoe_device_report* report) {
   uint32_t control_init[128];
   std::memset(control_init, 0, sizeof(control_init));
   control_init[1] = plan->params.main_end;
-  cudaMemcpy(plan->control.ptr, control_init, sizeof(control_init), cudaMemcpyHostToDevice);
+  cudaMemcpy(plan->meta.ptr, control_init, sizeof(control_init), cudaMemcpyHostToDevice);
   return BMOE_DEVICE_TIMEOUT;
 }
 
