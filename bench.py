@@ -41,6 +41,9 @@ WORKLOADS = {
     # half-size Mixtral-shaped case for profiler captures (weights 470 MB > L2)
     "profile_e8_t2048_k4096_n7168_zipf1.0": dict(
         experts=8, top_k=2, tokens=2048, k=4096, n=7168, distribution=3, zipf_alpha=1.0),
+    # small expert-parallel case for profiler captures of the routing kernels
+    "profile_ep_e32_t4096_k7168_n2048_zipf1.0": dict(
+        experts=32, top_k=4, tokens=4096, k=7168, n=2048, distribution=3, zipf_alpha=1.0),
     "ep_deepseek_e256_t32768_k7168_n2048_zipf1.0": dict(
         experts=256, top_k=8, tokens=32768, k=7168, n=2048, distribution=3, zipf_alpha=1.0),
 }
@@ -531,6 +534,91 @@ def run_single_gpu(args, spec, workload):
     print(json.dumps(line), flush=True)
 
 
+def run_skew_sweep(args):
+    """Qwen3-MoE-shaped skew sweep (E=128, top-8, T=16384, K=2048, N=768): per routing
+    point the reference's workload / schedule-model metrics, the variant its threshold
+    rule picks, and the engine's p50 / p99 per policy. One JSON line with a "sweep" list."""
+    import ctypes as C
+
+    import torch
+
+    import bmoe_b200 as engine
+
+    cap = engine._capi
+    lib = cap.load()
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda:0")
+    stream = torch.cuda.current_stream()
+    base = dict(experts=128, top_k=8, tokens=16384, k=2048, n=768)
+    points = [("uniform", 0, 1.2), ("zipf0.5", 3, 0.5), ("zipf1.0", 3, 1.0), ("zipf1.5", 3, 1.5)]
+    out = []
+    for label, dist_id, alpha in points:
+        spec = dict(base, distribution=dist_id, zipf_alpha=alpha)
+        counts = workload_counts(engine, spec)
+        n, k = spec["n"], spec["k"]
+        arr = (C.c_uint32 * len(counts))(*counts)
+        wm = cap.WorkloadMetrics()
+        lib.bmoe_workload_metrics_compute(arr, len(counts), n, 128, 128, C.byref(wm))
+        model = {}
+        for name, sched in (("expert_order", 0), ("static_persistent", 1), ("dynamic_queue", 2)):
+            sm = cap.ScheduleMetrics()
+            lib.bmoe_host_simulate(sched, arr, len(counts), n, 128, 128, 148, None, 0, None,
+                                   C.byref(sm))
+            model[name] = {"tail_ratio": sm.tail_ratio, "cta_work_cv": sm.cta_work_cv,
+                           "useful_work_ratio": sm.useful_work_ratio}
+        feats = cap.RoutingFeatures()
+        lib.bmoe_routing_features_compute(arr, len(counts), n, 128, 128, 148, C.byref(feats))
+        variant = C.c_uint32(0)
+        lib.bmoe_select_variant(C.byref(feats), None, C.byref(variant))
+        a, w = synth_inputs(torch, counts, n, k, dev)
+        d = torch.zeros(sum(counts), n, dtype=torch.bfloat16, device=dev)
+        flops = 2.0 * sum(counts) * n * k
+        plans = []
+        for policy, opts in (("expert_order", {}), ("static_persistent", {}),
+                             ("dynamic_queue", {}), ("clc", {}), ("auto", {})):
+            plan = engine.GroupedGemmPlan()
+            cap.check(plan.initialize_packed(a, w, d, counts, scheduler=policy, stream=stream,
+                                             cta_group=args.cta_group, **opts), policy)
+            plans.append((policy, plan))
+        for _ in range(max(3, args.warmup)):
+            for _, plan in plans:
+                plan.run(stream)
+        iters = args.policy_iters
+        ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+               for _ in plans] for _ in range(iters)]
+        torch.cuda.synchronize()
+        for i in range(iters):
+            for j, (_, plan) in enumerate(plans):
+                ev[i][j][0].record(stream)
+                plan.run(stream)
+                ev[i][j][1].record(stream)
+        torch.cuda.synchronize()
+        timing = {}
+        for j, (policy, plan) in enumerate(plans):
+            status, _ = plan.poll()
+            if status != 0:
+                raise RuntimeError(f"{policy}: {cap.status_string(status)}")
+            ms = [ev[i][j][0].elapsed_time(ev[i][j][1]) for i in range(iters)]
+            p50 = percentile(ms, 0.5)
+            timing[policy] = {"p50_us": p50 * 1e3, "p99_us": percentile(ms, 0.99) * 1e3,
+                              "useful_tflops_p50": flops / (p50 * 1e-3) / 1e12,
+                              "cta_group": plan.stats().cta_group}
+            plan.close()
+        for row in timing.values():
+            row["p99_speedup_vs_expert_order"] = timing["expert_order"]["p99_us"] / row["p99_us"]
+        out.append({"routing": label, "cv_m": wm.coefficient_of_variation,
+                    "max_over_mean_m": wm.max_over_mean, "tile_count_cv": wm.tile_count_cv,
+                    "small_m_expert_ratio": wm.small_m_expert_ratio,
+                    "total_tiles_128x128": wm.total_tiles, "schedule_model_148_ctas": model,
+                    "reference_rule_picks": cap.VARIANT_NAMES[variant.value],
+                    "engine": timing})
+        del a, w, d
+    print(json.dumps({"metric": "p50/p99 us per grouped GEMM vs routing skew", "unit": "us",
+                      "n_gpus": 1, "dtype": "bf16", "data": "synthetic",
+                      "config": {"workload": "qwen3_skew_sweep_e128_t16384_k2048_n768", **base},
+                      "iters": args.policy_iters, "sweep": out}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -556,16 +644,21 @@ def main():
     ap.add_argument("--comm-sms", type=int, default=8,
                     help="SMs the pipelined GEMM leaves to the exchange kernels")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--sweep", action="store_true",
+                    help="run the Qwen3-shaped routing-skew sweep instead of the headline")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
+    if args.sweep:
+        run_skew_sweep(args)
+        return
     workload = args.workload or (DEFAULT_WORKLOAD if args.gpus == 1 else EP_WORKLOAD)
     spec = WORKLOADS[workload]
     if args.impl == "reference":
         run_reference_arm(args, spec, workload)
         return
     single = args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1
-    if single and workload != EP_WORKLOAD:
+    if single and not workload.startswith(("ep_", "profile_ep_")):
         run_single_gpu(args, spec, workload)
     else:
         from bmoe_b200 import ep_bench  # noqa: F401  (multi-GPU arm)

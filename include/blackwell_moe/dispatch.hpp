@@ -41,6 +41,17 @@ struct DispatchThresholds {
   double sparse_expert_ratio = 0.5;
 };
 
+// Thresholds fitted on B200 measurements of this engine (Qwen3-shaped skew sweep
+// and the Mixtral- / DeepSeek-shaped workloads): chunked and hybrid claims never
+// paid (they cost 5-15 % through lost L2 locality of the tile_m-fastest
+// traversal), so the deep-queue branch is disabled; the other bootstrap values
+// were not contradicted by the data and are kept. Used by the plan's kAuto.
+inline DispatchThresholds fitted_b200_thresholds() {
+  DispatchThresholds t;
+  t.chunked_min_tiles_per_cta = 1.0e30;
+  return t;
+}
+
 // The launch variants the rule can choose (reference kernel names in
 // python/blackwell_moe_tirx/kernels/registry.py:45-106).
 enum class LaunchVariant {
