@@ -636,13 +636,18 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-single-gpu-ref", action="store_true")
-    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+    ap.add_argument("--exchange", default="peer", choices=["fused", "peer", "nccl"],
                     help="multi-GPU token exchange: routing kernels over peer memory, or "
                          "NCCL all-to-all with local re-packing")
-    ap.add_argument("--ep-groups", type=int, default=1,
-                    help="expert groups pipelined through exchange and GEMM (multi-GPU)")
+    ap.add_argument("--ep-groups", type=int, default=0,
+                    help="expert groups overlapped between exchange and GEMM (multi-GPU); "
+                         "0 = 4 for the fused exchange, 1 otherwise")
     ap.add_argument("--comm-sms", type=int, default=8,
                     help="SMs the pipelined GEMM leaves to the exchange kernels")
+    ap.add_argument("--dispatch-ctas", type=int, default=0,
+                    help="fused exchange: CTAs of the remote-row kernel (0 = one per SM)")
+    ap.add_argument("--topk-weights", action="store_true",
+                    help="expert-parallel arm: finish with the weighted top-k sum (y is [tokens, n])")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--sweep", action="store_true",
                     help="run the Qwen3-shaped routing-skew sweep instead of the headline")

@@ -131,6 +131,37 @@ class RoutingFeatures(C.Structure):
     ]
 
 
+class EpDispatchArgs(C.Structure):
+    _fields_ = [
+        ("x_dev", C.c_void_p), ("expert_ids_dev", C.c_void_p), ("row_base_dev", C.c_void_p),
+        ("owner_dev", C.c_void_p), ("group_of_dev", C.c_void_p), ("cursor_dev", C.c_void_p),
+        ("a_bases_dev", C.c_void_p), ("origin_bases_dev", C.c_void_p),
+        ("flag_bases_dev", C.c_void_p), ("group_done_dev", C.c_void_p),
+        ("chunk_next_dev", C.c_void_p),
+        ("dst_rank_out_dev", C.c_void_p), ("dst_row_out_dev", C.c_void_p),
+        ("assignments", C.c_uint64), ("rows_cap", C.c_uint64),
+        ("top_k", C.c_uint32), ("row_bytes", C.c_uint32), ("experts", C.c_uint32),
+        ("ranks", C.c_uint32), ("self", C.c_uint32), ("groups", C.c_uint32),
+        ("mode", C.c_uint32), ("epoch", C.c_uint32), ("max_ctas", C.c_uint32),
+        ("stream", C.c_void_p),
+    ]
+
+
+class EpReturnArgs(C.Structure):
+    _fields_ = [
+        ("d_dev", C.c_void_p), ("origin_dev", C.c_void_p), ("y_bases_dev", C.c_void_p),
+        ("flag_bases_dev", C.c_void_p), ("done_counter_dev", C.c_void_p),
+        ("rows", C.c_uint64), ("y_rows_cap", C.c_uint64),
+        ("row_bytes", C.c_uint32), ("ranks", C.c_uint32), ("self", C.c_uint32),
+        ("flag_slot", C.c_uint32), ("epoch", C.c_uint32), ("max_ctas", C.c_uint32),
+        ("stream", C.c_void_p),
+    ]
+
+
+EP_MAX_GROUPS = 16
+EP_LOCAL, EP_REMOTE, EP_ALL = 0, 1, 2
+
+
 class WorklistTotals(C.Structure):
     _fields_ = [
         ("total_tiles", C.c_uint32),
@@ -304,6 +335,20 @@ SIGNATURES = {
         [C.c_void_p, C.c_uint32, C.c_uint64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32,
          C.c_uint64, C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint32, C.c_uint32, C.c_void_p],
     ),
+    "bmoe_combine_topk": (
+        C.c_int,
+        [C.c_void_p, C.c_uint32, C.c_uint64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64,
+         C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p],
+    ),
+    "bmoe_ep_dispatch": (C.c_int, [C.c_void_p]),
+    "bmoe_ep_return": (C.c_int, [C.c_void_p]),
+    "bmoe_ep_wait_flags": (
+        C.c_int,
+        [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint64, C.c_void_p,
+         C.c_void_p],
+    ),
+    "bmoe_plan_set_gate": (
+        C.c_int, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p]),
     "bmoe_peer_alloc": (C.c_int, [C.c_uint64, _P(C.c_void_p), C.c_void_p]),
     "bmoe_peer_open": (C.c_int, [C.c_void_p, _P(C.c_void_p)]),
     "bmoe_peer_close": (C.c_int, [C.c_void_p]),

@@ -223,9 +223,44 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       const uint32_t peer_slots = PAIR ? ptx::map_to_cta(base + Cfg::kOffSlots, 1) : 0u;
       // Publishes one decoded record (or the sentinel) to the next ring slot
       // (of both CTAs in pair mode).
+      // Groups whose rows are known to have arrived from every other rank.
+      uint32_t groups_ready = 0;
+      auto gate = [&](uint32_t expert) -> bool {
+        const uint32_t g = p.gate_group_of[expert];
+        if (g >= 32 || ((groups_ready >> g) & 1u) != 0) return true;
+        uint64_t start = 0;
+        for (uint32_t r = 0; r < p.gate_ranks; ++r) {
+          if (r == p.gate_self) continue;
+          const uint32_t* flag = p.gate_flags + g * p.gate_ranks + r;
+          for (uint32_t spin = 1;; ++spin) {
+            if (static_cast<int32_t>(ptx::ld_acquire_sys_u32(flag) - p.gate_epoch) >= 0) break;
+            if ((spin & 0xf) == 0) {
+              if (*abort_word != 0) return false;
+              const uint64_t now = ptx::global_timer_ns();
+              if (start == 0) {
+                start = now;
+              } else if (now - start > budget) {
+                *abort_word = 1;
+                report(p, kSiteSchedGate, 0, expert, g, r);
+                return false;
+              }
+            }
+            __nanosleep(200);
+          }
+        }
+        // The rows were written by other GPUs' ordinary stores; the TMA loads that
+        // follow (async proxy) must observe them.
+        ptx::fence_proxy_async_all();
+        groups_ready |= 1u << g;
+        return true;
+      };
       auto publish = [&](int32_t tile_index) -> bool {
         const uint32_t slot = published % kSchedSlots;
         const uint32_t round = (published / kSchedSlots) & 1u;
+        if (p.gate_flags != nullptr && tile_index != kSentinel &&
+            !gate(p.tiles[tile_index].expert_id)) {
+          return false;
+        }
         if (!wait(bar_sched_empty(slot), round ^ 1u)) {
           report(p, kSiteSchedSlot, 0, static_cast<uint32_t>(tile_index), slot, published);
           return false;
@@ -362,6 +397,9 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
 
       const CUtensorMap* const map_a = p.tmap_a + expert;
       const CUtensorMap* const map_b = p.tmap_b + expert;
+      // Gated launch: the rows of this tile were stored by other GPUs; order this
+      // warp's TMA loads after the scheduler's observation of their flags.
+      if (p.gate_flags != nullptr) ptx::fence_proxy_async_all();
       if (expert != last_expert) {
         if (ptx::elect_one()) {
           ptx::tensormap_acquire(map_a);

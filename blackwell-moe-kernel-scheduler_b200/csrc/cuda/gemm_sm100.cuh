@@ -29,6 +29,7 @@ enum DeviceSite : uint32_t {
   kSiteMmaStage = 8,      // MMA waiting for operand bytes
   kSiteEpiInfo = 9,
   kSiteEpiAccum = 10,     // epilogue waiting for a finished accumulator
+  kSiteSchedGate = 11,    // scheduler waiting for another rank's rows (stage = group, aux = rank)
 };
 
 // Device-side error record; zero-initialised by the host.
@@ -60,6 +61,14 @@ struct GemmParams {
   uint32_t* cta_tiles;        // optional [gridDim.x]
   uint64_t* trace;            // optional [gridDim.x][kTraceWords] wait accounting
   uint64_t wait_budget_ns;
+  // Optional gate (expert-parallel exchange): a tile of expert e is published only
+  // after flag slots gate_group_of[e] * gate_ranks + r (r != gate_self) reached
+  // gate_epoch. The flags are raised by OTHER GPUs when their rows have landed.
+  const uint32_t* gate_flags;   // nullptr = no gate
+  const uint8_t* gate_group_of; // [experts]
+  uint32_t gate_epoch;
+  uint32_t gate_ranks;
+  uint32_t gate_self;
 };
 
 // Words per CTA of GemmParams::trace (SM cycles):

@@ -429,6 +429,24 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
   return BMOE_OK;
 }
 
+int bmoe_plan_set_gate(bmoe_plan* plan, const uint32_t* flags_dev, uint32_t epoch,
+                       uint32_t ranks, uint32_t self, const uint8_t* group_of_expert_dev) {
+  if (plan == nullptr || !plan->ready) return BMOE_INVALID_ARGUMENT;
+  bmoe::GemmParams& p = plan->params;
+  if (flags_dev == nullptr || ranks <= 1) {
+    p.gate_flags = nullptr;
+    p.gate_group_of = nullptr;
+    return BMOE_OK;
+  }
+  if (self >= ranks || ranks > 32 || group_of_expert_dev == nullptr) return BMOE_INVALID_ARGUMENT;
+  p.gate_flags = flags_dev;
+  p.gate_group_of = group_of_expert_dev;
+  p.gate_epoch = epoch;
+  p.gate_ranks = ranks;
+  p.gate_self = self;
+  return BMOE_OK;
+}
+
 int bmoe_plan_run(bmoe_plan* plan, void* stream) {
   if (plan == nullptr || !plan->ready) return BMOE_INVALID_ARGUMENT;
   if (plan->stats.active_experts == 0) return BMOE_OK;

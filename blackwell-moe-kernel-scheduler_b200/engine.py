@@ -145,6 +145,12 @@ class GroupedGemmPlan:
     def run(self, stream=None) -> int:
         return int(self._lib.bmoe_plan_run(self._handle, _stream_ptr(stream)))
 
+    def set_gate(self, flags_ptr, epoch: int, ranks: int, self_rank: int, group_of_ptr) -> int:
+        """Hold back the tiles of an expert group until the other ranks' rows of that
+        group have arrived (see ``bmoe_plan_set_gate``); ``flags_ptr`` None removes it."""
+        return int(self._lib.bmoe_plan_set_gate(self._handle, flags_ptr, epoch, ranks, self_rank,
+                                                group_of_ptr))
+
     def poll(self) -> tuple[int, _capi.DeviceReport]:
         report = _capi.DeviceReport()
         status = int(self._lib.bmoe_plan_poll(self._handle, C.byref(report)))

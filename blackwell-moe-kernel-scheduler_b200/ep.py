@@ -72,6 +72,32 @@ class CudaOps:
             self.launches += 1
         return out
 
+    def combine_topk(self, src, rows, weights=None, out=None):
+        """out[t] = bf16(sum_j weights[t, j] * src[rows[t, j]]) in FP32, j ascending;
+        ``rows`` [tokens, top_k] int64 (negative = dropped), ``weights`` float32 or None."""
+        import torch
+
+        if not src.is_cuda:
+            raise RuntimeError("the engine has no CPU path: combine_topk needs CUDA tensors")
+        tokens, top_k = int(rows.shape[0]), int(rows.shape[1])
+        n = int(src.shape[1])
+        if out is None:
+            out = torch.empty(tokens, n, dtype=src.dtype, device=src.device)
+        rows = rows.contiguous()
+        if weights is not None:
+            weights = weights.to(torch.float32).contiguous()
+        base = torch.tensor([src.data_ptr()], dtype=torch.int64, device=src.device)
+        _capi.check(
+            self._lib.bmoe_combine_topk(base.data_ptr(), 1, int(src.shape[0]), None,
+                                        rows.data_ptr(),
+                                        weights.data_ptr() if weights is not None else None,
+                                        tokens, top_k, n, out.data_ptr(), 0,
+                                        torch.cuda.current_stream().cuda_stream or None),
+            "bmoe_combine_topk")
+        if tokens:
+            self.launches += 1
+        return out
+
     def grouped_gemm(self, a, w, counts, out=None, slot=0):
         """``slot`` selects the plan object; launches that may be in flight at the
         same time (pipelined expert groups) must use different slots."""
@@ -161,14 +187,17 @@ class ExpertParallelLayer:
         dist.all_to_all_single(recv, send, recv_splits, send_splits, group=self.group)
         return recv
 
-    def forward(self, x, expert_ids, w_local, record_events=False):
+    def forward(self, x, expert_ids, w_local, record_events=False, topk_weights=None):
         """x [T_local, k]; expert_ids [T_local, top_k] int64 (device of x);
         w_local [len(local_experts), n, k] in ascending expert id.
         Returns y [T_local * top_k, n]: row j is token j // top_k routed to
-        expert_ids.flatten()[j]."""
+        expert_ids.flatten()[j]. With ``topk_weights`` [T_local, top_k] (float32) the
+        last step is the weighted top-k sum instead and y is [T_local, n]."""
         import torch
 
         if self.world > 1 and self.pipeline_groups > 1:
+            if topk_weights is not None:
+                raise ValueError("topk_weights is not supported with pipeline_groups > 1")
             return self._forward_pipelined(x, expert_ids, w_local, record_events)
 
         dev = x.device
@@ -215,7 +244,7 @@ class ExpertParallelLayer:
             mark("gemm")
             inv_perm = torch.empty(assignments, dtype=torch.int64, device=dev)
             inv_perm[perm] = torch.arange(assignments, device=dev, dtype=torch.int64)
-            y = self.ops.gather_rows(d_packed, inv_perm)
+            y = self._finish(d_packed, inv_perm, top_k, topk_weights)
             mark("finish")
             self._marks = marks
             self.last_local_m = local_m
@@ -248,11 +277,19 @@ class ExpertParallelLayer:
         mark("combine")
         inv_perm = torch.empty(assignments, dtype=torch.int64, device=dev)
         inv_perm[perm] = torch.arange(assignments, device=dev, dtype=torch.int64)
-        y = self.ops.gather_rows(d_recv, inv_perm)
+        y = self._finish(d_recv, inv_perm, top_k, topk_weights)
         mark("finish")
         self._marks = marks
         self.last_local_m = local_m
         return y
+
+    def _finish(self, rows_in_send_order, inv_perm, top_k, topk_weights):
+        """Assignment order (plain gather) or, with weights, the weighted top-k sum:
+        one kernel either way."""
+        if topk_weights is None:
+            return self.ops.gather_rows(rows_in_send_order, inv_perm)
+        return self.ops.combine_topk(rows_in_send_order, inv_perm.reshape(-1, top_k),
+                                     topk_weights)
 
     # ------------------------------------------------------------ pipelined --
     def _group_tables(self):

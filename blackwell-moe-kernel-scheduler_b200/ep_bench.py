@@ -79,7 +79,14 @@ def run(args, spec, workload):
     gen = torch.Generator(device=dev).manual_seed(4000 + rank)
     x_local = torch.randn(hi - lo, k, generator=gen, device=dev,
                           dtype=torch.float32).to(torch.bfloat16)
-    groups = args.ep_groups if world > 1 else 1
+    ep_groups = args.ep_groups or (4 if args.exchange == "fused" else 1)
+    groups = ep_groups if world > 1 else 1
+    gates = None
+    if args.topk_weights:
+        # router gates: the last step becomes the weighted top-k sum, y is [tokens, n]
+        gates = torch.softmax(torch.randn(hi - lo, top_k, generator=gen, device=dev), dim=1)
+        groups = 1
+    extra = {"topk_weights": gates} if gates is not None else {}
     plan_options = {"cta_group": args.cta_group}
     if groups > 1 and args.comm_sms > 0:
         # Leave a few SMs to the exchange kernels that run beside the GEMM.
@@ -87,7 +94,18 @@ def run(args, spec, workload):
         pair = args.cta_group != 1
         plan_options = {"cta_group": 2 if pair else 1,
                         "cta_count": max(1, (sms - args.comm_sms) // (2 if pair else 1))}
-    if args.exchange == "peer":
+    if args.exchange == "fused":
+        from bmoe_b200 import ep_fused
+
+        layer = ep_fused.FusedExpertParallelLayer(
+            owner, n, k, rank=rank, world=world, rows_cap=tokens * top_k,
+            assignments_cap=(hi - lo) * top_k, scheduler=args.policy,
+            exchange_groups=ep_groups, cta_group=args.cta_group,
+            dispatch_ctas=args.dispatch_ctas)
+        ops = layer
+        plain = layer
+        groups = layer.groups
+    elif args.exchange == "peer":
         from bmoe_b200 import ep_peer
 
         # Row capacity: every assignment of the batch could land on one rank.
@@ -110,7 +128,7 @@ def run(args, spec, workload):
     stream = torch.cuda.current_stream()
 
     for _ in range(args.warmup):
-        layer.forward(x_local, ids_local, w_local)
+        layer.forward(x_local, ids_local, w_local, **extra)
     ops.poll()
     barrier()
 
@@ -123,7 +141,7 @@ def run(args, spec, workload):
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0.record(stream)
     for _ in range(args.steps):
-        layer.forward(x_local, ids_local, w_local)
+        layer.forward(x_local, ids_local, w_local, **extra)
     t1.record(stream)
     barrier()
     ms_per_step = max_over_ranks(t0.elapsed_time(t1) / args.steps)
@@ -136,9 +154,10 @@ def run(args, spec, workload):
     phase_iters = max(3, min(args.steps, 20))
     for _ in range(phase_iters):
         barrier()
-        plain.forward(x_local, ids_local, w_local, record_events=True)
+        plain.forward(x_local, ids_local, w_local, record_events=True, **extra)
         phases = plain.phase_times_ms()
-        step_samples.append(max_over_ranks(sum(phases.values())))
+        step_samples.append(max_over_ranks(sum(v for key, v in phases.items()
+                                                if not key.endswith("_overlapped"))))
         for name, ms in phases.items():
             phase_sum[name] = phase_sum.get(name, 0.0) + ms
     phases_ms = {name: max_over_ranks(v / phase_iters) for name, v in phase_sum.items()}
@@ -150,12 +169,13 @@ def run(args, spec, workload):
     # end to end: activations from pinned host memory, result back to the host
     x_host = torch.empty(x_local.shape, dtype=torch.bfloat16).pin_memory()
     x_host.copy_(x_local)
-    y_host = torch.empty((hi - lo) * top_k, n, dtype=torch.bfloat16).pin_memory()
+    y_host = torch.empty((hi - lo) * (1 if gates is not None else top_k), n,
+                         dtype=torch.bfloat16).pin_memory()
     e2e_steps = max(3, min(args.steps, 10))
 
     def e2e_step():
         x_local.copy_(x_host, non_blocking=True)
-        y = layer.forward(x_local, ids_local, w_local)
+        y = layer.forward(x_local, ids_local, w_local, **extra)
         y_host.copy_(y, non_blocking=True)
 
     for _ in range(2):
@@ -175,7 +195,7 @@ def run(args, spec, workload):
     single_gpu = None
     if world > 1 and not args.no_single_gpu_ref:
         if rank == 0:
-            if args.exchange == "peer":
+            if args.exchange != "nccl":
                 pass  # peer buffers stay mapped by the other ranks until they exit
             del w_local, layer, ops, plain
             torch.cuda.empty_cache()
@@ -223,6 +243,7 @@ def run(args, spec, workload):
                    "tokens": tokens, "k": k, "n": n, "policy": args.policy,
                    "parallelism": f"ep{world}", "placement": "tile-count LPT",
                    "exchange": args.exchange,
+                   "last_step": "weighted top-k sum" if gates is not None else "rows in assignment order",
                    "pipeline_groups": groups, "comm_sms": args.comm_sms if groups > 1 else 0,
                    "rank_tiles": rank_tiles, "rank0_rows": local_rows,
                    "max_rank_rows": rows_max, "mean_rank_rows": tokens * top_k / world,
@@ -231,6 +252,10 @@ def run(args, spec, workload):
                            "configuration; the one-GPU line of bench.py runs the "
                            "Mixtral-shaped grouped GEMM, see single_gpu_same_workload",
                    "step": ("count all-gather + push rows into the owners' packed A over "
+                            "NVLink while the grouped GEMM, gated per expert group, already "
+                            "computes + push result rows back"
+                            if args.exchange == "fused" else
+                            "count all-gather + push rows into the owners' packed A over "
                             "NVLink + grouped GEMM + pull result rows back"
                             if args.exchange == "peer" else
                             "count all-gather + pack + all-to-all dispatch + unpack + "

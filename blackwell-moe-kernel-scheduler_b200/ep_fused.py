@@ -1,0 +1,369 @@
+"""Expert-parallel layer whose exchange overlaps the grouped GEMM.
+
+Same interface and result as ``ep.ExpertParallelLayer`` (NCCL all-to-all) and
+``ep_peer.PeerExpertParallelLayer`` (two routing kernels with barriers). Here the
+transfer and the math run at the same time:
+
+* a dispatch kernel on a side stream pushes the rows bound for other GPUs into the
+  owners' packed ``A`` group by group (experts are split into a few groups in
+  packed order) and raises a flag per (group, source) on every peer;
+* the grouped GEMM starts at once: its tile scheduler publishes the tiles of a
+  group only when the flags of all other sources for that group are in, so early
+  groups compute while late groups are still in flight;
+* a return kernel pushes every result row back to the rank it came from (the
+  dispatcher leaves an origin record beside each row), then raises a "done" flag;
+  the step ends when the other ranks' "done" flags are in.
+
+The only NCCL call per step is the all-gather of the per-expert counts. Kernels
+of one GPU never wait on each other: rows that stay on the rank are copied by a
+launch that precedes the GEMM in the same stream, and the gate looks at the flags
+of other ranks only. Every device-side wait is bounded; ``poll()`` reports a wait
+that ran out.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import Sequence
+
+import numpy as np
+
+from . import _capi
+
+
+def plan_step(counts_all, owner: Sequence[int], rank: int, groups: int, tile_m: int = 256):
+    """Host tables of one step from the count matrix ``counts_all`` [world, experts]
+    (numpy int64, identical on every rank).
+
+    Packed order on an owner: its experts in ascending id, and inside an expert the
+    sources in ascending rank. Groups are contiguous runs of an owner's experts with
+    about equal numbers of ``tile_m``-row tiles.
+
+    Returns a dict with ``local_experts``, ``local_m`` (rows per local expert),
+    ``row_base`` (int64 [experts]: first row of (expert, this rank) in the owner's A),
+    ``group_of`` (uint8 [experts]), ``group_local`` (uint8 per local expert) and
+    ``total_local``.
+    """
+    counts_all = np.asarray(counts_all, dtype=np.int64)
+    world, experts = counts_all.shape
+    owner_a = np.asarray(list(owner), dtype=np.int64)
+    totals = counts_all.sum(axis=0)
+    before_me = counts_all[:rank].sum(axis=0)
+    row_base = np.zeros(experts, dtype=np.int64)
+    group_of = np.zeros(experts, dtype=np.uint8)
+    for q in range(world):
+        mine = np.nonzero(owner_a == q)[0]                 # ascending expert id
+        m = totals[mine]
+        start = np.cumsum(m) - m
+        row_base[mine] = start + before_me[mine]
+        tiles = (m + tile_m - 1) // tile_m
+        total_tiles = int(tiles.sum())
+        if total_tiles > 0 and groups > 1:
+            tiles_before = np.cumsum(tiles) - tiles
+            group_of[mine] = np.minimum(groups - 1, tiles_before * groups // total_tiles)
+    local = np.nonzero(owner_a == rank)[0]
+    return {
+        "local_experts": local.tolist(),
+        "local_m": totals[local].tolist(),
+        "row_base": row_base,
+        "group_of": group_of,
+        "group_local": group_of[local].copy(),
+        "total_local": int(totals[local].sum()),
+    }
+
+
+class _RawCudaBuffer:
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {
+            "shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2,
+        }
+
+
+class SharedBuffers:
+    """Named device buffers on every rank, each mapped by all ranks of the node."""
+
+    def __init__(self, sizes: dict, *, rank: int, world: int, group=None):
+        import torch
+        import torch.distributed as dist
+
+        self._lib = _capi.load()
+        self.rank, self.world = rank, world
+        dev = torch.device("cuda", torch.cuda.current_device())
+        names = list(sizes)
+        self._own, self._opened = [], []
+        self.local = {}       # name -> uint8 tensor over the own buffer
+        self.bases = {}       # name -> int64 device tensor [world] of base pointers
+        handles = torch.zeros(len(names), 64, dtype=torch.uint8)
+        own_ptr = {}
+        for i, name in enumerate(names):
+            nbytes = max(256, int(sizes[name]))
+            ptr, buf = C.c_void_p(), (C.c_uint8 * 64)()
+            _capi.check(self._lib.bmoe_peer_alloc(nbytes, C.byref(ptr), buf), "bmoe_peer_alloc")
+            self._own.append(ptr.value)
+            own_ptr[name] = ptr.value
+            handles[i] = torch.tensor(list(buf), dtype=torch.uint8)
+            self.local[name] = torch.as_tensor(_RawCudaBuffer(ptr.value, nbytes), device=dev)
+            self.local[name].zero_()
+        table = {name: [0] * world for name in names}
+        for name in names:
+            table[name][rank] = own_ptr[name]
+        if world > 1:
+            gathered = torch.zeros(world, len(names), 64, dtype=torch.uint8, device=dev)
+            dist.all_gather_into_tensor(gathered.view(-1), handles.to(dev).view(-1), group=group)
+            gathered = gathered.cpu()
+            for r in range(world):
+                if r == rank:
+                    continue
+                for i, name in enumerate(names):
+                    raw = (C.c_uint8 * 64)(*gathered[r, i].tolist())
+                    ptr = C.c_void_p()
+                    _capi.check(self._lib.bmoe_peer_open(raw, C.byref(ptr)), "bmoe_peer_open")
+                    self._opened.append(ptr.value)
+                    table[name][r] = ptr.value
+        for name in names:
+            self.bases[name] = torch.tensor(table[name], dtype=torch.int64, device=dev)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier(group=group)   # every buffer is zeroed before anyone writes flags
+
+    def close(self):
+        import torch
+
+        torch.cuda.synchronize()
+        for p in self._opened:
+            self._lib.bmoe_peer_close(p)
+        self._opened = []
+        self.local = {}
+        for p in self._own:
+            self._lib.bmoe_peer_free(p)
+        self._own = []
+
+
+class FusedExpertParallelLayer:
+    def __init__(self, owner: Sequence[int], n: int, k: int, *, rank: int, world: int,
+                 rows_cap: int, assignments_cap: int, group=None, scheduler="dynamic_queue",
+                 exchange_groups: int = 4, dispatch_ctas: int = 0, wait_budget_ns: int = 0,
+                 **plan_options):
+        """``rows_cap``: packed rows this rank can own; ``assignments_cap``: local
+        assignments (tokens x top_k) per step; ``exchange_groups``: groups the
+        experts of a rank are split into for the overlap (1 = no overlap)."""
+        import torch
+
+        from .engine import GroupedGemmPlan
+
+        if world > 32:
+            raise ValueError("at most 32 ranks")
+        self._lib = _capi.load()
+        self.owner = [int(o) for o in owner]
+        self.experts = len(self.owner)
+        self.n, self.k, self.rank, self.world, self.group = n, k, rank, world, group
+        self.rows_cap, self.assignments_cap = int(rows_cap), int(assignments_cap)
+        self.groups = max(1, min(int(exchange_groups), _capi.EP_MAX_GROUPS)) if world > 1 else 1
+        self.local_experts = [e for e in range(self.experts) if self.owner[e] == rank]
+        self.scheduler, self.plan_options = scheduler, plan_options
+        self.dispatch_ctas, self.wait_budget_ns = int(dispatch_ctas), int(wait_budget_ns)
+        self.tile_m = 128 if plan_options.get("cta_group") == 1 else 256
+        self.plan = GroupedGemmPlan()
+        self.launches = 0
+        self.epoch = 0
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.dev = dev
+        flag_slots = (_capi.EP_MAX_GROUPS + 1) * world
+        self.shared = SharedBuffers(
+            {"a": self.rows_cap * k * 2, "d": self.rows_cap * n * 2, "origin": self.rows_cap * 8,
+             "y": self.assignments_cap * n * 2, "flags": flag_slots * 4},
+            rank=rank, world=world, group=group)
+        loc = self.shared.local
+        self.a = loc["a"].view(torch.bfloat16)[:self.rows_cap * k].view(self.rows_cap, k)
+        self.d = loc["d"].view(torch.bfloat16)[:self.rows_cap * n].view(self.rows_cap, n)
+        self.y = loc["y"].view(torch.bfloat16)[:self.assignments_cap * n] \
+            .view(self.assignments_cap, n)
+        # per-step tables: int64 row_base[E] | uint8 group_of[E] | uint8 group_local[E]
+        self._table_bytes = 8 * self.experts + 2 * self.experts
+        self._stage = torch.empty(self._table_bytes, dtype=torch.uint8).pin_memory()
+        self._tables = torch.empty(self._table_bytes, dtype=torch.uint8, device=dev)
+        self._owner_dev = torch.tensor(self.owner, dtype=torch.int32, device=dev)
+        # uint32 scratch zeroed every step: cursor[E] | group_done[MAX_GROUPS] | return
+        # counter | chunk counters of the remote and the local dispatch launch
+        self._scratch = torch.zeros(self.experts + 3 * _capi.EP_MAX_GROUPS + 1,
+                                    dtype=torch.int32, device=dev)
+        self._wait_status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._comm = torch.cuda.Stream(device=dev)
+        self._ev_start = torch.cuda.Event()
+        self._ev_comm = torch.cuda.Event()
+        self.routes = None
+
+    def close(self):
+        self.plan.close()
+        self.shared.close()
+
+    # ------------------------------------------------------------- launches --
+    def _dispatch(self, x, flat_ids, top_k, mode, stream, routes):
+        b = self.shared.bases
+        t = self._tables.data_ptr()
+        args = _capi.EpDispatchArgs(
+            x_dev=x.data_ptr(), expert_ids_dev=flat_ids.data_ptr(), row_base_dev=t,
+            owner_dev=self._owner_dev.data_ptr(), group_of_dev=t + 8 * self.experts,
+            cursor_dev=self._scratch.data_ptr(), a_bases_dev=b["a"].data_ptr(),
+            origin_bases_dev=b["origin"].data_ptr(), flag_bases_dev=b["flags"].data_ptr(),
+            group_done_dev=self._scratch.data_ptr() + 4 * self.experts,
+            chunk_next_dev=self._scratch.data_ptr() + 4 * (
+                self.experts + _capi.EP_MAX_GROUPS * (1 if mode == _capi.EP_REMOTE else 2) + 1),
+            dst_rank_out_dev=routes[0].data_ptr() if routes else None,
+            dst_row_out_dev=routes[1].data_ptr() if routes else None,
+            assignments=int(flat_ids.numel()), rows_cap=self.rows_cap, top_k=top_k,
+            row_bytes=self.k * 2, experts=self.experts, ranks=self.world, self=self.rank,
+            groups=self.groups, mode=mode, epoch=self.epoch, max_ctas=self.dispatch_ctas,
+            stream=stream.cuda_stream or None)
+        _capi.check(self._lib.bmoe_ep_dispatch(C.byref(args)), "bmoe_ep_dispatch")
+        self.launches += 1
+
+    def _return(self, rows, stream):
+        b = self.shared.bases
+        args = _capi.EpReturnArgs(
+            d_dev=self.d.data_ptr(), origin_dev=self.shared.local["origin"].data_ptr(),
+            y_bases_dev=b["y"].data_ptr(), flag_bases_dev=b["flags"].data_ptr(),
+            done_counter_dev=self._scratch.data_ptr() + 4 * (self.experts + _capi.EP_MAX_GROUPS),
+            rows=rows, y_rows_cap=self.assignments_cap, row_bytes=self.n * 2, ranks=self.world,
+            self=self.rank, flag_slot=_capi.EP_MAX_GROUPS * self.world + self.rank,
+            epoch=self.epoch, max_ctas=0, stream=stream.cuda_stream or None)
+        _capi.check(self._lib.bmoe_ep_return(C.byref(args)), "bmoe_ep_return")
+        self.launches += 1
+
+    # -------------------------------------------------------------- forward --
+    def forward(self, x, expert_ids, w_local, record_events=False, topk_weights=None,
+                record_routes=False):
+        """x [T_local, k]; expert_ids [T_local, top_k] int64; w_local [local experts, n, k].
+        Returns y [T_local * top_k, n] in assignment order - a view of the layer's result
+        buffer, valid until the next ``forward`` - or, with ``topk_weights``, the weighted
+        top-k sum [T_local, n]."""
+        import torch
+        import torch.distributed as dist
+
+        dev = x.device
+        main = torch.cuda.current_stream()
+        top_k = int(expert_ids.shape[1])
+        flat_ids = expert_ids.reshape(-1).contiguous()
+        assignments = int(flat_ids.numel())
+        if assignments > self.assignments_cap:
+            raise RuntimeError("more assignments than the result buffer holds")
+        marks = []
+
+        def mark(name):
+            if record_events:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record(main)
+                marks.append((name, ev))
+
+        mark("start")
+        local_counts = torch.zeros(self.experts, dtype=torch.int64, device=dev)
+        local_counts.scatter_add_(0, flat_ids.clamp(0, self.experts - 1),
+                                  ((flat_ids >= 0) & (flat_ids < self.experts)).to(torch.int64))
+        if self.world > 1:
+            flat = torch.empty(self.world * self.experts, dtype=torch.int64, device=dev)
+            dist.all_gather_into_tensor(flat, local_counts, group=self.group)
+            counts_all = flat.reshape(self.world, self.experts).cpu().numpy()
+        else:
+            counts_all = local_counts.reshape(1, -1).cpu().numpy()
+        step = plan_step(counts_all, self.owner, self.rank, self.groups, self.tile_m)
+        if step["total_local"] > self.rows_cap:
+            raise RuntimeError("routed rows exceed the packed buffer capacity")
+        stage = self._stage.numpy()
+        e = self.experts
+        stage[:8 * e].view(np.int64)[:] = step["row_base"]
+        stage[8 * e:9 * e] = step["group_of"]
+        stage[9 * e:9 * e + len(step["group_local"])] = step["group_local"]
+        self._tables.copy_(self._stage, non_blocking=True)
+        self._scratch.zero_()
+        self.epoch += 1
+        routes = None
+        if record_routes:
+            routes = (torch.full((assignments,), -1, dtype=torch.int32, device=dev),
+                      torch.full((assignments,), -1, dtype=torch.int64, device=dev))
+        self.routes = routes
+        mark("counts")
+
+        # rows bound for other GPUs: side stream, overlapped with everything below
+        if self.world > 1:
+            self._ev_start.record(main)
+            self._comm.wait_event(self._ev_start)
+            if record_events:
+                self._remote_marks = (torch.cuda.Event(enable_timing=True),
+                                      torch.cuda.Event(enable_timing=True))
+                self._remote_marks[0].record(self._comm)
+            self._dispatch(x, flat_ids, top_k, _capi.EP_REMOTE, self._comm, routes)
+            if record_events:
+                self._remote_marks[1].record(self._comm)
+            self._ev_comm.record(self._comm)
+        # rows that stay here: same stream as the GEMM
+        self._dispatch(x, flat_ids, top_k, _capi.EP_LOCAL, main, routes)
+        mark("local_rows")
+
+        total_local = step["total_local"]
+        if total_local:
+            _capi.check(self.plan.initialize_packed(self.a, w_local, self.d, step["local_m"],
+                                                    scheduler=self.scheduler, stream=main,
+                                                    **self.plan_options),
+                        "bmoe_plan_initialize")
+            if self.world > 1:
+                _capi.check(self.plan.set_gate(self.shared.local["flags"].data_ptr(), self.epoch,
+                                               self.world, self.rank,
+                                               self._tables.data_ptr() + 9 * e),
+                            "bmoe_plan_set_gate")
+            _capi.check(self.plan.run(main), "bmoe_plan_run")
+            self.launches += 3
+        mark("gemm")
+
+        self._return(total_local, main)
+        if self.world > 1:
+            _capi.check(
+                self._lib.bmoe_ep_wait_flags(self.shared.local["flags"].data_ptr(),
+                                             _capi.EP_MAX_GROUPS * self.world, self.world,
+                                             self.rank, self.epoch, self.wait_budget_ns,
+                                             self._wait_status.data_ptr(),
+                                             main.cuda_stream or None),
+                "bmoe_ep_wait_flags")
+            self.launches += 1
+            main.wait_event(self._ev_comm)
+        mark("return")
+        y = self.y[:assignments]
+        if topk_weights is not None:
+            rows = torch.arange(assignments, device=dev, dtype=torch.int64).reshape(-1, top_k)
+            out = torch.empty(assignments // top_k, self.n, dtype=x.dtype, device=dev)
+            weights = topk_weights.to(torch.float32).contiguous()
+            _capi.check(
+                self._lib.bmoe_combine_topk(self.shared.bases["y"].data_ptr()
+                                            + 8 * self.rank, 1, self.assignments_cap, None,
+                                            rows.data_ptr(), weights.data_ptr(),
+                                            assignments // top_k, top_k, self.n, out.data_ptr(),
+                                            0, main.cuda_stream or None),
+                "bmoe_combine_topk")
+            self.launches += 1
+            y = out
+            mark("weighted_sum")
+        self._marks = marks
+        self.last_local_m = step["local_m"]
+        return y
+
+    def poll(self):
+        status, report = self.plan.poll()
+        if status not in (_capi.OK, _capi.INVALID_ARGUMENT):
+            raise _capi.EngineError(
+                status, f"grouped GEMM (site {report.code}, cta {report.cta}, "
+                        f"group {report.stage}, rank {report.aux})")
+        word = int(self._wait_status.item()) & 0xffffffff
+        if word:
+            raise _capi.EngineError(
+                _capi.DEVICE_TIMEOUT,
+                f"results of rank {word & 0xff} did not arrive (flag slot {(word >> 8) & 0xffff})")
+
+    def phase_times_ms(self):
+        import torch
+
+        torch.cuda.synchronize()
+        out = {name: a.elapsed_time(b)
+               for (_, a), (name, b) in zip(self._marks[:-1], self._marks[1:])}
+        if self.world > 1 and getattr(self, "_remote_marks", None):
+            # side stream: runs beside local_rows / gemm, not part of their sum
+            out["remote_rows_overlapped"] = self._remote_marks[0].elapsed_time(self._remote_marks[1])
+        return out

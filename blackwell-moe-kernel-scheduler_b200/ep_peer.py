@@ -236,7 +236,10 @@ class PeerExpertParallelLayer:
         if rows:
             self.launches += 1
 
-    def forward(self, x, expert_ids, w_local, record_events=False):
+    def forward(self, x, expert_ids, w_local, record_events=False, topk_weights=None):
+        """As ``ep.ExpertParallelLayer.forward``. With ``topk_weights`` the combine
+        kernel reads every result row from its owner's memory and reduces the
+        top_k rows of a token on the fly (y is [T_local, n])."""
         import torch
         import torch.distributed as dist
 
@@ -286,6 +289,30 @@ class PeerExpertParallelLayer:
             self.launches += 3
         self._barrier()
         mark("gemm")
+
+        if topk_weights is not None:
+            # combine + weighted reduction in one pass over peer memory
+            by_rank = torch.empty(assignments, dtype=torch.int32, device=dev)
+            by_row = torch.empty(assignments, dtype=torch.int64, device=dev)
+            by_rank[perm] = dst_rank
+            by_row[perm] = dst_row
+            weights = topk_weights.to(torch.float32).contiguous()
+            y = torch.empty(assignments // top_k, self.n, dtype=x.dtype, device=dev)
+            _capi.check(
+                self._lib.bmoe_combine_topk(self.buffers.d_bases.data_ptr(), self.world,
+                                            self.buffers.rows_cap, by_rank.data_ptr(),
+                                            by_row.data_ptr(), weights.data_ptr(),
+                                            assignments // top_k, top_k, self.n, y.data_ptr(),
+                                            self.route_ctas,
+                                            torch.cuda.current_stream().cuda_stream or None),
+                "bmoe_combine_topk")
+            self.launches += 1
+            # No barrier here: an owner rewrites D only after the barrier that follows
+            # the NEXT dispatch, which every rank enters after this kernel.
+            mark("combine")
+            self._marks = marks
+            self.last_local_m = local_m
+            return y
 
         # combine: pull result rows back into assignment order
         y = torch.empty(assignments, self.n, dtype=x.dtype, device=dev)

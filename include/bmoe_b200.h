@@ -449,6 +449,113 @@ int bmoe_route_rows(const void* const* src_bases_dev, uint32_t n_src,
                     uint64_t rows, uint32_t row_bytes, uint32_t max_ctas,
                     void* stream);
 
+/* Weighted top-k combine, the un-permute after the expert GEMMs: for t in [0, tokens)
+ *   out[t, :] = bf16( sum_{j < top_k} w[t*top_k+j] *
+ *                     float(src_bases[rank[t*top_k+j]][row[t*top_k+j], :]) )
+ * FP32 accumulation, one fused multiply-add per term in ascending j, one BF16
+ * rounding (nearest even) at the end. A NULL weight array means 1.0 for every
+ * term, a NULL rank array means src_bases[0]. A negative row marks a dropped
+ * assignment; it and any out-of-range rank / row contribute nothing. The source
+ * buffers may belong to other GPUs (bmoe_peer_open), which makes this one kernel
+ * the expert-parallel combine exchange and the reduction together. n must be a
+ * multiple of 8. The reference leaves this step to its caller
+ * (agent/search_space.yaml:13 treats the permutation as engine input). */
+int bmoe_combine_topk(const void* const* src_bases_dev, uint32_t n_src,
+                      uint64_t src_rows_cap, const int32_t* src_rank_dev,
+                      const int64_t* src_row_dev, const float* weights_dev,
+                      uint64_t tokens, uint32_t top_k, uint32_t n, void* out_dev,
+                      uint32_t max_ctas, void* stream);
+
+/* ---- Expert-parallel exchange overlapped with the grouped GEMM (peer memory) ----
+ * No counterpart in the reference, which has no multi-GPU path; these are the data
+ * movers either side of its grouped-GEMM interface for the expert-parallel
+ * configuration. One rank per GPU; every pointer table below is a DEVICE array of
+ * `ranks` base pointers (own buffer or bmoe_peer_open mappings).
+ *
+ * Flag arrays: every rank owns a zero-initialised uint32 array of
+ * (BMOE_EP_MAX_GROUPS + 1) * ranks slots that all ranks map. Slot g*ranks + s holds
+ * the last step ("epoch", increasing by one per step) for which source rank s has
+ * delivered all of its rows of expert group g; slot BMOE_EP_MAX_GROUPS*ranks + s
+ * the last step whose results rank s has returned. A rank never raises flags in
+ * its own array. */
+#define BMOE_EP_MAX_GROUPS 16u
+#define BMOE_EP_LOCAL 0u   /* only rows whose owner is this rank; raises no flag */
+#define BMOE_EP_REMOTE 1u  /* only rows owned by other ranks; raises the group flags */
+#define BMOE_EP_ALL 2u
+
+typedef struct bmoe_ep_dispatch_args {
+  const void* x_dev;               /* [tokens, row_bytes] token rows of this rank */
+  const int64_t* expert_ids_dev;   /* [assignments] expert of assignment i (token i / top_k);
+                                      ids outside [0, experts) are dropped */
+  const int64_t* row_base_dev;     /* [experts] first row of (expert, this rank) in the owner's A */
+  const int32_t* owner_dev;        /* [experts] owning rank */
+  const uint8_t* group_of_dev;     /* [experts] group of the expert, < groups */
+  uint32_t* cursor_dev;            /* [experts] zero at step start (shared by the LOCAL and
+                                      REMOTE launches of a step) */
+  void* const* a_bases_dev;        /* [ranks] packed A buffers, rows_cap rows each */
+  void* const* origin_bases_dev;   /* [ranks] int64 origin record per packed row */
+  void* const* flag_bases_dev;     /* [ranks] flag arrays (REMOTE / ALL with ranks > 1) */
+  uint32_t* group_done_dev;        /* [groups] zero at step start (REMOTE / ALL) */
+  uint32_t* chunk_next_dev;        /* [groups] zero at step start; one array per launch */
+  int32_t* dst_rank_out_dev;       /* [assignments] or NULL: destination of every assignment */
+  int64_t* dst_row_out_dev;        /* [assignments] or NULL */
+  uint64_t assignments;
+  uint64_t rows_cap;
+  uint32_t top_k;
+  uint32_t row_bytes;              /* k * 2, multiple of 16 */
+  uint32_t experts;
+  uint32_t ranks;
+  uint32_t self;
+  uint32_t groups;
+  uint32_t mode;                   /* BMOE_EP_LOCAL / REMOTE / ALL */
+  uint32_t epoch;
+  uint32_t max_ctas;               /* 0 = default: 4 per SM for LOCAL, 7/16 of the SMs otherwise */
+  void* stream;
+} bmoe_ep_dispatch_args;
+
+/* Pushes token rows into the owners' packed A, group by group; the row inside
+ * (expert, source) comes from an atomic cursor, so the order of rows inside an
+ * expert is arbitrary (no result row depends on it). Beside every row it leaves the
+ * origin record rank << 40 | assignment that bmoe_ep_return follows. */
+int bmoe_ep_dispatch(const bmoe_ep_dispatch_args* args);
+
+typedef struct bmoe_ep_return_args {
+  const void* d_dev;               /* [rows, row_bytes] packed results of this rank */
+  const void* origin_dev;          /* [rows] int64 origin records (this rank's own buffer) */
+  void* const* y_bases_dev;        /* [ranks] result buffers in assignment order */
+  void* const* flag_bases_dev;
+  uint32_t* done_counter_dev;      /* zero at step start */
+  uint64_t rows;
+  uint64_t y_rows_cap;
+  uint32_t row_bytes;              /* n * 2, multiple of 16 */
+  uint32_t ranks;
+  uint32_t self;
+  uint32_t flag_slot;              /* BMOE_EP_MAX_GROUPS * ranks + self */
+  uint32_t epoch;
+  uint32_t max_ctas;               /* 0 = default */
+  void* stream;
+} bmoe_ep_return_args;
+
+/* Writes every packed result row to row `assignment` of its origin rank's y and
+ * then raises this rank's "done" flag on every peer. */
+int bmoe_ep_return(const bmoe_ep_return_args* args);
+
+/* Stream-ordered wait until slots first_slot + r (r != self) of the local flag
+ * array have reached `epoch`. Bounded: after budget_ns (0 = 1 s) the kernel stores
+ * 0x80000000 | first_slot << 8 | r in *status_dev (if it was 0) and returns. */
+int bmoe_ep_wait_flags(const uint32_t* flags_dev, uint32_t first_slot, uint32_t ranks,
+                       uint32_t self, uint32_t epoch, uint64_t budget_ns,
+                       uint32_t* status_dev, void* stream);
+
+/* Gate for the next bmoe_plan_run calls: the tile scheduler publishes a tile of
+ * expert e only after slots group_of_expert[e]*ranks + r (all r != self) of the
+ * local flag array reached `epoch` (bounded by the plan's wait budget; running out
+ * reports BMOE_DEVICE_TIMEOUT through bmoe_plan_poll). flags_dev == NULL removes
+ * the gate, and so does every bmoe_plan_initialize.
+ * group_of_expert_dev: [experts of the plan] uint8, values < 32. */
+int bmoe_plan_set_gate(bmoe_plan* plan, const uint32_t* flags_dev, uint32_t epoch,
+                       uint32_t ranks, uint32_t self, const uint8_t* group_of_expert_dev);
+
 /* Device buffers that other processes on the node can map (CUDA IPC):
  * bmoe_peer_alloc allocates `bytes` and writes a 64-byte handle; another process
  * passes that handle to bmoe_peer_open and gets a pointer valid on ITS device

@@ -581,6 +581,31 @@ ORC_EXPORT uint64_t orc_grouped_gemm(const uint16_t* a, const uint16_t* b,
   return rows_done;
 }
 
+/* Weighted top-k combine: out[t,:] = bf16(sum_j w[t,j] * float(src[row[t,j],:])),
+ * FP32, one fmaf per term, j ascending, one rounding to BF16. The reference has
+ * no such function (its callers own the un-permute, agent/search_space.yaml:13);
+ * this states the engine's definition of the step on the CPU. Rows < 0 or
+ * >= src_rows are dropped assignments. weights may be NULL (all 1.0f). */
+ORC_EXPORT int orc_combine_topk(const uint16_t* src, uint64_t src_rows, const int64_t* row,
+                                const float* weights, uint64_t tokens, uint32_t top_k,
+                                uint32_t n, uint16_t* out) {
+  if (src == NULL || row == NULL || out == NULL || top_k == 0) return -1;
+#pragma omp parallel for schedule(static)
+  for (int64_t t = 0; t < (int64_t)tokens; ++t) {
+    for (uint32_t c = 0; c < n; ++c) {
+      float acc = 0.0f;
+      for (uint32_t j = 0; j < top_k; ++j) {
+        const int64_t r = row[(uint64_t)t * top_k + j];
+        if (r < 0 || (uint64_t)r >= src_rows) continue;
+        const float w = weights != NULL ? weights[(uint64_t)t * top_k + j] : 1.0f;
+        acc = fmaf(w, bf16_to_f32(src[(uint64_t)r * n + c]), acc);
+      }
+      out[(uint64_t)t * n + c] = f32_to_bf16(acc);
+    }
+  }
+  return 0;
+}
+
 ORC_EXPORT int orc_max_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

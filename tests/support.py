@@ -105,6 +105,22 @@ class Oracle:
         rec[0] = tuple(int(x) for x in tile_record)
         return int(self.lib.orc_probe_checksum(ptr(rec), u32(work_scale)))
 
+    def combine_topk(self, src_bits, rows, weights=None):
+        """src_bits [R, n] uint16, rows [T, top_k] int64, weights [T, top_k] f32 -> [T, n] uint16."""
+        src_bits = np.ascontiguousarray(src_bits, dtype=np.uint16)
+        rows = np.ascontiguousarray(rows, dtype=np.int64)
+        tokens, top_k = rows.shape
+        n = src_bits.shape[1]
+        if weights is not None:
+            weights = np.ascontiguousarray(weights, dtype=np.float32)
+            assert weights.shape == rows.shape
+        out = np.zeros((tokens, n), dtype=np.uint16)
+        rc = self.lib.orc_combine_topk(ptr(src_bits), C.c_uint64(src_bits.shape[0]), ptr(rows),
+                                       ptr(weights) if weights is not None else None,
+                                       C.c_uint64(tokens), u32(top_k), u32(n), ptr(out))
+        assert rc == 0
+        return out
+
     def grouped_gemm(self, a_bits, w_bits, counts, n, k, *, want_f32=False, want_f64=False,
                      row_stride=1, row_phase=0, threads=0):
         """a_bits [sum M, k], w_bits [E, n, k] uint16 -> dict of outputs."""

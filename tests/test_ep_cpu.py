@@ -32,6 +32,14 @@ class OracleOps:
     def gather_rows(self, src, index, out=None):
         return src.index_select(0, index)
 
+    def combine_topk(self, src, rows, weights=None, out=None):
+        import torch
+
+        bits = self.oracle.combine_topk(
+            src.contiguous().view(torch.int16).numpy().view(np.uint16), rows.numpy(),
+            None if weights is None else weights.numpy())
+        return torch.from_numpy(bits.view(np.int16).copy()).view(torch.bfloat16)
+
     def grouped_gemm(self, a, w, counts, out=None, slot=0):
         import torch
 
@@ -86,6 +94,14 @@ def worker(rank, world, port, tmpdir, groups=1):
         y_ref[order] = d_ref
         want = y_ref[lo * top_k:hi * top_k]
         same = torch.equal(y.view(torch.int16), want.view(torch.int16))
+        if groups == 1:
+            # weighted top-k combine as the last step: equals the combine of the rows
+            gates = torch.rand(tokens, top_k, generator=gen)
+            z = layer.forward(x_all[lo:hi], ids_all[lo:hi], w_local, topk_weights=gates[lo:hi])
+            rows = torch.arange((hi - lo) * top_k).reshape(-1, top_k)
+            z_ref = OracleOps().combine_topk(want, rows, gates[lo:hi])
+            same = same and z.shape == (hi - lo, n) and torch.equal(
+                z.view(torch.int16), z_ref.view(torch.int16))
         Path(tmpdir, f"rank{rank}.txt").write_text(
             f"{int(same)} {y.shape[0]} {sum(layer.last_local_m)}")
     finally:
@@ -156,3 +172,44 @@ def test_peer_route_plan_builds_the_single_gpu_packing(engine):
         got = [buffers[r][row] for row in range(len(buffers[r]))]
         assert sorted(buffers[r]) == list(range(len(want)))
         assert got == want
+
+
+def test_fused_exchange_step_tables_cover_every_owner_buffer_once(engine):
+    """plan_step() of the overlapped exchange: with the cursor of the dispatch kernel
+    emulated in assignment order, the rows of all sources fill every owner's packed
+    buffer exactly once, expert-major in ascending id, and the expert groups are
+    contiguous runs of an owner's experts in packed order."""
+    import torch
+
+    from bmoe_b200 import ep, ep_fused
+
+    gen = torch.Generator().manual_seed(21)
+    world, experts, top_k, tokens, groups = 3, 14, 2, 120, 4
+    probs = torch.rand(experts, generator=gen) + 0.05
+    probs[6] = 0.0
+    ids_all = torch.multinomial(probs.expand(tokens, -1), top_k, replacement=False, generator=gen)
+    global_counts = torch.bincount(ids_all.reshape(-1), minlength=experts)
+    owner, _ = ep.place_experts(global_counts.tolist(), world, 256)
+    bounds = [0, 37, 90, tokens]
+    counts_all = np.stack([
+        np.bincount(ids_all[bounds[r]:bounds[r + 1]].reshape(-1).numpy(), minlength=experts)
+        for r in range(world)]).astype(np.int64)
+    steps = [ep_fused.plan_step(counts_all, owner, r, groups, tile_m=16) for r in range(world)]
+    for r in range(world):
+        assert steps[r]["local_experts"] == [e for e in range(experts) if owner[e] == r]
+        assert steps[r]["local_m"] == [int(global_counts[e]) for e in steps[r]["local_experts"]]
+        assert np.array_equal(steps[r]["group_of"], steps[0]["group_of"])   # same on every rank
+        g_local = steps[r]["group_local"]
+        assert np.all(np.diff(g_local.astype(np.int64)) >= 0) and g_local.max(initial=0) < groups
+    filled = [np.full(steps[q]["total_local"], -1, dtype=np.int64) for q in range(world)]
+    for r in range(world):
+        cursor = np.zeros(experts, dtype=np.int64)
+        flat = ids_all[bounds[r]:bounds[r + 1]].reshape(-1).numpy()
+        for e in flat:
+            row = steps[r]["row_base"][e] + cursor[e]
+            cursor[e] += 1
+            assert filled[owner[e]][row] == -1, "two assignments share a row"
+            filled[owner[e]][row] = e
+    for q in range(world):
+        want = np.repeat(steps[q]["local_experts"], steps[q]["local_m"])
+        assert np.array_equal(filled[q], want)

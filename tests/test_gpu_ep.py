@@ -33,6 +33,48 @@ def test_gather_rows_matches_index_select(engine):
     assert out[0].eq(1).all() and out[1:].eq(0).all()
 
 
+def oracle_combine(y, gates, top_k):
+    """CPU oracle of the weighted top-k sum over rows in assignment order."""
+    import support
+    import torch
+
+    bits = y.cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
+    rows = np.arange(bits.shape[0], dtype=np.int64).reshape(-1, top_k)
+    out = support.Oracle().combine_topk(bits, rows, gates.cpu().numpy())
+    return torch.from_numpy(out.view(np.int16).copy()).view(torch.bfloat16)
+
+
+def test_combine_topk_is_bit_exact_against_the_oracle(engine):
+    import support
+    import torch
+
+    from bmoe_b200 import ep
+
+    ops = ep.CudaOps()
+    oracle = support.Oracle()
+    gen = torch.Generator().manual_seed(11)
+    for src_rows, n, tokens, top_k in [(5, 8, 1, 1), (300, 24, 77, 2), (4096, 2048, 700, 8),
+                                       (2000, 7168, 130, 4), (900, 264, 55, 9)]:
+        src = torch.randn(src_rows, n, generator=gen).to(torch.bfloat16)
+        rows = torch.randint(0, src_rows, (tokens, top_k), generator=gen)
+        rows[tokens // 2, 0] = -1                      # a dropped assignment
+        if tokens > 3:
+            rows[3, :] = -1                            # a token with nothing routed
+            rows[1, top_k - 1] = src_rows + 5          # out of range: skipped as well
+        gates = torch.rand(tokens, top_k, generator=gen)
+        src_bits = src.view(torch.int16).numpy().view(np.uint16)
+        for weights in (gates, None):
+            got = ops.combine_topk(src.cuda(), rows.cuda(),
+                                   None if weights is None else weights.cuda())
+            want = oracle.combine_topk(src_bits, rows.numpy(),
+                                       None if weights is None else weights.numpy())
+            got_bits = got.cpu().view(torch.int16).numpy().view(np.uint16)
+            assert np.array_equal(got_bits, want), (src_rows, n, tokens, top_k)
+    lib = engine._capi.load()
+    assert lib.bmoe_combine_topk(None, 1, 1, None, None, None, 4, 2, 8, None, 0, None) != 0
+    assert lib.bmoe_combine_topk(None, 1, 1, None, None, None, 0, 2, 8, None, 0, None) == 0
+
+
 def reference_output(engine, x_all, ids_all, w_all, top_k):
     """Single-GPU engine over all assignments, returned in assignment order."""
     import torch
@@ -74,6 +116,10 @@ def test_single_rank_layer_equals_plain_engine(engine):
     layer.ops.poll()
     want = reference_output(engine, x, ids, w, 4)
     assert torch.equal(y.view(torch.int16), want.view(torch.int16))
+    gates = torch.rand(ids.shape, generator=torch.Generator().manual_seed(1))
+    z = layer.forward(x.cuda(), ids.cuda(), w.cuda(), topk_weights=gates.cuda())
+    assert z.shape == (x.shape[0], 512)
+    assert torch.equal(z.cpu().view(torch.int16), oracle_combine(want, gates, 4).view(torch.int16))
 
 
 def test_route_rows_and_single_rank_peer_layer(engine):
@@ -113,8 +159,88 @@ def test_route_rows_and_single_rank_peer_layer(engine):
         layer.poll()
         want = reference_output(engine, x, ids, w, 4)
         assert torch.equal(y.view(torch.int16), want.view(torch.int16))
+        gates = torch.rand(ids.shape, generator=torch.Generator().manual_seed(1))
+        z = layer.forward(x.cuda(), ids.cuda(), w.cuda(), topk_weights=gates.cuda())
+        assert torch.equal(z.cpu().view(torch.int16),
+                           oracle_combine(want, gates, 4).view(torch.int16))
     finally:
         layer.close()
+
+
+def test_single_rank_fused_layer_and_gate(engine):
+    """The overlapped-exchange layer on one rank against the plain engine, the gate of
+    the grouped GEMM with flags that are already up, and the bounded waits: a flag
+    that nothing raises makes the wait kernel and the gated GEMM give up with a
+    status instead of hanging."""
+    import torch
+
+    from bmoe_b200 import ep_fused
+
+    ids, x, w = make_problem()
+    want = reference_output(engine, x, ids, w, 4)
+    layer = ep_fused.FusedExpertParallelLayer([0] * 40, 512, 320, rank=0, world=1,
+                                              rows_cap=2400, assignments_cap=2400)
+    try:
+        for _ in range(2):
+            y = layer.forward(x.cuda(), ids.cuda(), w.cuda(), record_routes=True)
+        layer.poll()
+        assert torch.equal(y.view(torch.int16), want.view(torch.int16))
+        dst_rank, dst_row = layer.routes
+        assert dst_rank.eq(0).all() and torch.equal(
+            torch.sort(dst_row).values.cpu(), torch.arange(2400))
+        gates = torch.rand(ids.shape, generator=torch.Generator().manual_seed(1))
+        z = layer.forward(x.cuda(), ids.cuda(), w.cuda(), topk_weights=gates.cuda())
+        assert torch.equal(z.cpu().view(torch.int16),
+                           oracle_combine(want, gates, 4).view(torch.int16))
+    finally:
+        layer.close()
+
+    lib = engine._capi.load()
+    # wait kernel: rank 1 of 2 never reports -> status word, no hang
+    flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert lib.bmoe_ep_wait_flags(flags.data_ptr(), 32, 2, 0, 1, 2_000_000, status.data_ptr(),
+                                  None) == 0
+    torch.cuda.synchronize()
+    assert (int(status.item()) & 0xffffffff) == (0x80000000 | (32 << 8) | 1)
+    flags[33] = 1
+    status.zero_()
+    assert lib.bmoe_ep_wait_flags(flags.data_ptr(), 32, 2, 0, 1, 2_000_000, status.data_ptr(),
+                                  None) == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+
+    # gated GEMM: two groups, "rank 1" delivered group 0 only
+    counts = [150, 0, 300, 90]
+    gen = torch.Generator().manual_seed(4)
+    a = torch.randn(sum(counts), 192, generator=gen).to(torch.bfloat16).cuda()
+    wt = (torch.randn(4, 256, 192, generator=gen) * 192 ** -0.5).to(torch.bfloat16).cuda()
+    d_plain = torch.zeros(sum(counts), 256, dtype=torch.bfloat16, device="cuda")
+    engine.grouped_gemm(a, wt, d_plain, counts, scheduler="dynamic_queue")
+    group_of = torch.tensor([0, 0, 1, 1], dtype=torch.uint8, device="cuda")
+    flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+    flags[0 * 2 + 1] = 5                                   # group 0 from rank 1, epoch 5
+    for cta_group in (1, 2):
+        d = torch.zeros_like(d_plain)
+        plan = engine.GroupedGemmPlan()
+        assert plan.initialize_packed(a, wt, d, counts, scheduler="dynamic_queue",
+                                      cta_group=cta_group) == 0
+        assert plan.set_gate(flags.data_ptr(), 5, 2, 0, group_of.data_ptr()) == 0
+        flags[1 * 2 + 1] = 0
+        assert plan.run() == 0
+        torch.cuda.synchronize()
+        status_code, report = plan.poll()
+        assert status_code == engine._capi.DEVICE_TIMEOUT and report.code == 11
+        assert report.stage == 1 and report.aux == 1       # group 1, rank 1
+        flags[1 * 2 + 1] = 5                               # now everything has "arrived"
+        assert plan.initialize_packed(a, wt, d, counts, scheduler="dynamic_queue",
+                                      cta_group=cta_group) == 0
+        assert plan.set_gate(flags.data_ptr(), 5, 2, 0, group_of.data_ptr()) == 0
+        assert plan.run() == 0
+        torch.cuda.synchronize()
+        assert plan.poll()[0] == 0
+        assert torch.equal(d.view(torch.int16), d_plain.view(torch.int16))
+        plan.close()
 
 
 def _ep_worker(rank, world, port, tmpdir):
@@ -137,6 +263,8 @@ def _ep_worker(rank, world, port, tmpdir):
                                     world, 512)
         lo, hi = tokens * rank // world, tokens * (rank + 1) // world
         want = reference_output(engine, x, ids, w, 4)[lo * 4:hi * 4]
+        gates = torch.rand(ids.shape, generator=torch.Generator().manual_seed(1))[lo:hi]
+        want_z = oracle_combine(want, gates, 4)
         same = True
         for groups, opts in ((1, {}), (3, {"cta_group": 2, "cta_count": 60})):
             layer = ep.ExpertParallelLayer(owner, 512, 320, rank=rank, world=world,
@@ -147,6 +275,10 @@ def _ep_worker(rank, world, port, tmpdir):
                                   w[layer.local_experts].cuda())
             layer.ops.poll()
             same = same and torch.equal(y.view(torch.int16), want.view(torch.int16))
+            if groups == 1:
+                z = layer.forward(x[lo:hi].cuda(), ids[lo:hi].cuda(),
+                                  w[layer.local_experts].cuda(), topk_weights=gates.cuda())
+                same = same and torch.equal(z.cpu().view(torch.int16), want_z.view(torch.int16))
         from bmoe_b200 import ep_peer
 
         peer = ep_peer.PeerExpertParallelLayer(owner, 512, 320, rank=rank, world=world,
@@ -155,7 +287,24 @@ def _ep_worker(rank, world, port, tmpdir):
             y = peer.forward(x[lo:hi].cuda(), ids[lo:hi].cuda(), w[peer.local_experts].cuda())
         peer.poll()
         same = same and torch.equal(y.view(torch.int16), want.view(torch.int16))
+        for _ in range(2):
+            z = peer.forward(x[lo:hi].cuda(), ids[lo:hi].cuda(), w[peer.local_experts].cuda(),
+                             topk_weights=gates.cuda())
+        same = same and torch.equal(z.cpu().view(torch.int16), want_z.view(torch.int16))
+        from bmoe_b200 import ep_fused
+
+        fused = ep_fused.FusedExpertParallelLayer(owner, 512, 320, rank=rank, world=world,
+                                                  rows_cap=2400, assignments_cap=(hi - lo) * 4,
+                                                  exchange_groups=3, scheduler="dynamic_queue")
+        for i in range(4):
+            y = fused.forward(x[lo:hi].cuda(), ids[lo:hi].cuda(), w[fused.local_experts].cuda(),
+                              topk_weights=gates.cuda() if i == 3 else None)
+            if i == 2:
+                same = same and torch.equal(y.view(torch.int16), want.view(torch.int16))
+        fused.poll()
+        same = same and torch.equal(y.cpu().view(torch.int16), want_z.view(torch.int16))
         dist.barrier()
+        fused.close()
         peer.close()
         Path(tmpdir, f"rank{rank}.txt").write_text(str(int(same)))
         dist.barrier()

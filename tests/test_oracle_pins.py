@@ -181,3 +181,27 @@ def test_oracle_equals_compiled_reference_scheduler(oracle, reflib):
         mo, mr = oracle.workload_metrics(counts, n, tm, tn), reflib.workload_metrics(counts, n, tm, tn)
         assert [float(x).hex() for x in mo[1]] == [float(x).hex() for x in mr[1]]
         assert np.array_equal(mo[2], mr[2])
+
+
+def test_combine_topk_definition(oracle):
+    """The weighted top-k combine has no reference counterpart; this pins the CPU
+    statement of the step itself: FP32, terms in ascending j, one BF16 rounding,
+    dropped (negative) rows skipped. Weights are multiples of 1/8 so that every
+    product is exact in FP32 and a plain float32 loop is the same arithmetic."""
+    rng = np.random.default_rng(7)
+    src = support.f32_to_bf16_bits(rng.standard_normal((40, 24)).astype(np.float32))
+    rows = rng.integers(0, 40, size=(9, 3)).astype(np.int64)
+    rows[2, 1] = -1
+    rows[5, :] = -1
+    weights = (rng.integers(-8, 9, size=(9, 3)) / 8.0).astype(np.float32)
+    got = oracle.combine_topk(src, rows, weights)
+    vals = support.bf16_bits_to_f32(src)
+    want = np.zeros((9, 24), dtype=np.float32)
+    for t in range(9):
+        for j in range(3):
+            if rows[t, j] >= 0:
+                want[t] = (want[t] + weights[t, j] * vals[rows[t, j]]).astype(np.float32)
+    assert np.array_equal(got, support.f32_to_bf16_bits(want))
+    assert not got[5].any()
+    ones = oracle.combine_topk(src, rows, None)
+    assert np.array_equal(ones, oracle.combine_topk(src, rows, np.ones_like(weights)))
