@@ -636,16 +636,23 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-single-gpu-ref", action="store_true")
-    ap.add_argument("--exchange", default="peer", choices=["fused", "peer", "nccl"],
-                    help="multi-GPU token exchange: routing kernels over peer memory, or "
-                         "NCCL all-to-all with local re-packing")
+    ap.add_argument("--exchange", default="fused", choices=["fused", "peer", "nccl"],
+                    help="multi-GPU token exchange: fused = peer-memory pushes overlapped with "
+                         "the gated grouped GEMM; peer = two routing kernels with barriers; "
+                         "nccl = all-to-all with local re-packing")
     ap.add_argument("--ep-groups", type=int, default=0,
                     help="expert groups overlapped between exchange and GEMM (multi-GPU); "
-                         "0 = 4 for the fused exchange, 1 otherwise")
+                         "0 = 8 for the fused exchange, 1 otherwise")
     ap.add_argument("--comm-sms", type=int, default=8,
                     help="SMs the pipelined GEMM leaves to the exchange kernels")
     ap.add_argument("--dispatch-ctas", type=int, default=0,
                     help="fused exchange: CTAs of the remote-row kernel (0 = one per SM)")
+    ap.add_argument("--exchange-sms", type=int, default=16,
+                    help="fused exchange: SMs the GEMM leaves to the remote-row kernel "
+                         "(0 = share SMs, see --dispatch-ctas)")
+    ap.add_argument("--no-push", action="store_true",
+                    help="fused exchange: return result rows with a kernel after the GEMM "
+                         "instead of from its epilogue")
     ap.add_argument("--topk-weights", action="store_true",
                     help="expert-parallel arm: finish with the weighted top-k sum (y is [tokens, n])")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)

@@ -143,6 +143,7 @@ class EpDispatchArgs(C.Structure):
         ("top_k", C.c_uint32), ("row_bytes", C.c_uint32), ("experts", C.c_uint32),
         ("ranks", C.c_uint32), ("self", C.c_uint32), ("groups", C.c_uint32),
         ("mode", C.c_uint32), ("epoch", C.c_uint32), ("max_ctas", C.c_uint32),
+        ("block_threads", C.c_uint32), ("cluster", C.c_uint32),
         ("stream", C.c_void_p),
     ]
 
@@ -349,6 +350,8 @@ SIGNATURES = {
     ),
     "bmoe_plan_set_gate": (
         C.c_int, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p]),
+    "bmoe_plan_set_push": (
+        C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint64]),
     "bmoe_peer_alloc": (C.c_int, [C.c_uint64, _P(C.c_void_p), C.c_void_p]),
     "bmoe_peer_open": (C.c_int, [C.c_void_p, _P(C.c_void_p)]),
     "bmoe_peer_close": (C.c_int, [C.c_void_p]),

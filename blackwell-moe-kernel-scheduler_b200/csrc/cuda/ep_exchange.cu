@@ -113,6 +113,7 @@ struct DispatchArgs {
   uint32_t groups;
   uint32_t mode;               // BMOE_EP_LOCAL / BMOE_EP_REMOTE / BMOE_EP_ALL
   uint32_t epoch;
+  uint32_t span;               // assignments per claim: 32, 16, 8 or 4
 };
 
 // Group by group, a warp claims 32 consecutive assignments at a time from a shared
@@ -124,21 +125,26 @@ struct DispatchArgs {
 // the other, 512 contiguous bytes per instruction. The row inside (expert, source)
 // comes from an atomic cursor: the order of rows inside an expert does not change
 // any result row, only where it sits.
-__global__ void __launch_bounds__(kExThreads) ep_dispatch_kernel(DispatchArgs a) {
+__global__ void __launch_bounds__(1024) ep_dispatch_kernel(DispatchArgs a) {
   const uint32_t lane = threadIdx.x & 31;
-  const uint32_t chunks = static_cast<uint32_t>((a.assignments + 31) / 32);
-  for (uint32_t g = 0; g < a.groups; ++g) {
+  // Small inputs claim fewer than 32 assignments at a time so that every SM gets work.
+  const uint32_t span = a.span;
+  const uint32_t chunks = static_cast<uint32_t>((a.assignments + span - 1) / span);
+  // Rows that stay on this rank raise no flags: one pass over all groups.
+  const bool by_group = a.mode != BMOE_EP_LOCAL;
+  const uint32_t passes = by_group ? a.groups : 1u;
+  for (uint32_t g = 0; g < passes; ++g) {
     while (true) {
       uint32_t c = 0;
       if (lane == 0) c = atomicAdd(&a.chunk_next[g], 1u);
       c = __shfl_sync(0xffffffffu, c, 0);
       if (c >= chunks) break;
-      const uint64_t i = static_cast<uint64_t>(c) * 32 + lane;
+      const uint64_t i = static_cast<uint64_t>(c) * span + lane;
       int32_t to = -1;
       int64_t row = -1;
-      if (i < a.assignments) {
+      if (lane < span && i < a.assignments) {
         const int64_t e = a.expert_ids[i];
-        if (e >= 0 && e < static_cast<int64_t>(a.experts) && a.group_of[e] == g) {
+        if (e >= 0 && e < static_cast<int64_t>(a.experts) && (!by_group || a.group_of[e] == g)) {
           const int32_t owner = a.owner[e];
           const bool local = static_cast<uint32_t>(owner) == a.self;
           const bool wanted = a.mode == BMOE_EP_ALL || (a.mode == BMOE_EP_LOCAL) == local;
@@ -161,12 +167,12 @@ __global__ void __launch_bounds__(kExThreads) ep_dispatch_kernel(DispatchArgs a)
         todo &= todo - 1;
         const int32_t to_b = __shfl_sync(0xffffffffu, to, b);
         const int64_t row_b = __shfl_sync(0xffffffffu, row, b);
-        copy_row(a.x + ((static_cast<uint64_t>(c) * 32 + b) / a.top_k) * a.vec_per_row,
+        copy_row(a.x + ((static_cast<uint64_t>(c) * span + b) / a.top_k) * a.vec_per_row,
                  a.a_bases[to_b] + static_cast<uint64_t>(row_b) * a.vec_per_row, a.vec_per_row,
                  lane);
       }
     }
-    if (a.mode != BMOE_EP_LOCAL && a.ranks > 1) {
+    if (by_group && a.ranks > 1) {
       signal_peers_when_grid_done(&a.group_done[g], a.flag_bases, a.ranks, a.self,
                                   g * a.ranks + a.self, a.epoch);
     }
@@ -251,7 +257,7 @@ extern "C" int bmoe_ep_dispatch(const bmoe_ep_dispatch_args* args) {
       c.mode > BMOE_EP_ALL || c.top_k == 0 || c.row_bytes == 0 || c.row_bytes % 16 != 0 ||
       c.a_bases_dev == nullptr || c.origin_bases_dev == nullptr || c.cursor_dev == nullptr ||
       c.row_base_dev == nullptr || c.owner_dev == nullptr || c.group_of_dev == nullptr ||
-      c.chunk_next_dev == nullptr || c.assignments > 0xffffffffull * 32 ||
+      c.chunk_next_dev == nullptr || c.assignments > 0xffffffffull * 4 ||
       (c.assignments != 0 && (c.x_dev == nullptr || c.expert_ids_dev == nullptr)) ||
       (c.ranks > 1 && c.mode != BMOE_EP_LOCAL &&
        (c.flag_bases_dev == nullptr || c.group_done_dev == nullptr))) {
@@ -281,18 +287,47 @@ extern "C" int bmoe_ep_dispatch(const bmoe_ep_dispatch_args* args) {
   a.groups = c.groups;
   a.mode = c.mode;
   a.epoch = c.epoch;
-  // Remote rows: CTAs on fewer than half of the SMs by default. Each fits beside a
-  // resident GEMM CTA, so the copy runs while the GEMM computes, but an SM whose
-  // stores wait for NVLink slows everything else on it (measured: 64 CTAs move the
-  // rows as fast as 148 and leave the local copy and the GEMM much less disturbed).
-  // Local rows precede the GEMM in its stream and take the whole device.
-  const uint64_t want = (c.assignments + 255) / 256;  // 8 warps x 32 assignments per CTA pass
+  // Remote rows, default shape: 256-thread CTAs on fewer than half of the SMs. Each
+  // fits beside a resident GEMM CTA, so the copy runs while the GEMM computes, but an
+  // SM whose stores wait for NVLink slows everything else on it (measured: 64 CTAs
+  // move the rows as fast as 148 and disturb the GEMM much less). Callers that keep
+  // some SMs free of GEMM CTAs ask for a few 1024-thread CTAs instead (block_threads,
+  // cluster = 2 so that the CTAs fill whole SM pairs). Local rows precede the GEMM in
+  // its stream and take the whole device.
+  const uint32_t threads = c.block_threads == 0 ? bmoe::kExThreads : c.block_threads;
+  if ((threads != 256 && threads != 512 && threads != 1024) || c.cluster > 2) {
+    return BMOE_INVALID_ARGUMENT;
+  }
   const uint64_t sms = bmoe::device_sms();
   const uint64_t cap = c.max_ctas != 0 ? c.max_ctas
                        : c.mode == BMOE_EP_LOCAL ? 4 * sms : (sms * 7 / 16 > 0 ? sms * 7 / 16 : 1);
+  // Assignments per claim: 32, or fewer when that would leave warps of the grid idle.
+  const uint64_t warps_cap = cap * (threads / 32);
+  uint32_t span = 32;
+  while (span > 4 && (c.assignments + span - 1) / span < 2 * warps_cap) span >>= 1;
+  a.span = span;
+  const uint64_t per_cta = static_cast<uint64_t>(threads / 32) * span;
+  const uint64_t want = (c.assignments + per_cta - 1) / per_cta;
   uint32_t grid = static_cast<uint32_t>(want < cap ? want : cap);
   if (grid == 0) grid = 1;  // the flags are raised even when there is nothing to send
-  bmoe::ep_dispatch_kernel<<<grid, bmoe::kExThreads, 0, static_cast<cudaStream_t>(c.stream)>>>(a);
+  cudaLaunchConfig_t config{};
+  config.blockDim = dim3(threads, 1, 1);
+  config.dynamicSmemBytes = 0;
+  config.stream = static_cast<cudaStream_t>(c.stream);
+  cudaLaunchAttribute attr[1];
+  if (c.cluster == 2) {
+    grid = (grid + 1) / 2 * 2;
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    config.attrs = attr;
+    config.numAttrs = 1;
+  }
+  config.gridDim = dim3(grid, 1, 1);
+  if (cudaLaunchKernelEx(&config, bmoe::ep_dispatch_kernel, a) != cudaSuccess) {
+    return BMOE_CUDA_ERROR;
+  }
   return cudaPeekAtLastError() == cudaSuccess ? BMOE_OK : BMOE_CUDA_ERROR;
 }
 

@@ -558,6 +558,21 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       ++reads;
       if (tile == kSentinel) break;
 
+      // Push mode: where this lane's row goes (looked up while the MMAs still run).
+      uint4* push_dst = nullptr;
+      if constexpr (!OUT_F32) {
+        if (p.push_origin != nullptr && row_in_tile + lane < valid_m) {
+          const uint64_t rec = static_cast<uint64_t>(
+              p.push_origin[p.push_expert_row[expert] + row0 + row_in_tile + lane]);
+          const uint64_t to = rec >> 40;
+          const uint64_t at = rec & ((1ull << 40) - 1);
+          // A bad record must never become a stray access to another GPU's memory.
+          if (to < p.push_ranks && at < p.push_rows_cap) {
+            push_dst = p.push_bases[to] + at * p.push_vec_per_row + (col0 >> 3);
+          }
+        }
+      }
+
       if (!timed_wait(bar_tmem_full(buf), buf_round, t_accum)) {
         if (lane == 0 && quad == 0) {
           report(p, kSiteEpiAccum, 3, static_cast<uint32_t>(tile), buf, 0);
@@ -619,6 +634,26 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                 ptx::pack_bf16x2(__uint_as_float(hi[8 * j + 6]), __uint_as_float(hi[8 * j + 7])));
           }
         }
+        if constexpr (!OUT_F32) {
+          if (p.push_origin != nullptr) {
+            // Rows leave from the staging tile: 8 lanes write the 128 bytes of one row.
+            __syncwarp();
+            const uint32_t tile_smem = staging + sbuf * kStoreBytes;
+#pragma unroll
+            for (uint32_t it = 0; it < 8; ++it) {
+              const uint32_t r = it * 4 + (lane >> 3);
+              const uint32_t j = lane & 7u;
+              const unsigned long long dst_r = __shfl_sync(
+                  0xffffffffu, reinterpret_cast<unsigned long long>(push_dst), r);
+              if (dst_r != 0 && c * kChunkCols + j * 8 < valid_n) {
+                const uint4 v = ptx::ld_shared_v4(tile_smem + r * 128u + ((j ^ (r & 7u)) << 4));
+                reinterpret_cast<uint4*>(dst_r)[c * (kChunkCols / 8) + j] = v;
+              }
+            }
+            sbuf ^= 1u;
+            continue;
+          }
+        }
         ptx::fence_async_shared();
         __syncwarp();
         if (lane == 0) {
@@ -643,6 +678,9 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       }
     }
     if (lane == 0) ptx::tma_store_wait_all();
+    // Pushed rows may sit in other GPUs' memory: make them visible system-wide
+    // before the kernel ends and the next launch in the stream raises the flags.
+    if (p.push_origin != nullptr) __threadfence_system();
     if (quad == 0 && lane == 0) misc->tiles_done = tiles_done;
     if (tracing && quad == 0 && lane == 0) {
       p.trace[blockIdx.x * kTraceWords + 5] = t_info;

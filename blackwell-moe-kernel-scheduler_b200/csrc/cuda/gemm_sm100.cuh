@@ -69,6 +69,16 @@ struct GemmParams {
   uint32_t gate_epoch;
   uint32_t gate_ranks;
   uint32_t gate_self;
+  // Optional result push (expert-parallel exchange, BF16 output): instead of the TMA
+  // store into D, the epilogue writes every valid tile row to row `assignment` of its
+  // origin rank's result buffer (plain 16-byte stores, 128 contiguous bytes per row
+  // and chunk; peer memory over NVLink or local memory).
+  const long long* push_origin;     // [packed rows] rank << 40 | assignment; nullptr = off
+  const uint32_t* push_expert_row;  // [experts] first packed row of each expert
+  uint4* const* push_bases;         // [push_ranks] result buffers
+  uint64_t push_rows_cap;           // rows each result buffer holds
+  uint32_t push_vec_per_row;        // n / 8
+  uint32_t push_ranks;
 };
 
 // Words per CTA of GemmParams::trace (SM cycles):

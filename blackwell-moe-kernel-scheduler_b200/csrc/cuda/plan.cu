@@ -131,6 +131,7 @@ struct bmoe_plan {
   bmoe::GemmParams params{};
   uint32_t units = 0;      // persistent CTAs or CTA pairs (tile count for CLC)
   uint32_t tile_n = 0;
+  uint32_t stats_n = 0;    // output columns of the current problem
   uint32_t cta_group = 1;
   bool out_f32 = false;
 
@@ -407,6 +408,7 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
   p.wait_budget_ns = 1000000000ull;  // 1 s per wait, then the kernel gives up
 
   plan->tile_n = tile_n;
+  plan->stats_n = a.n;
   plan->cta_group = cta_group;
   plan->out_f32 = out_f32;
   plan->units = policy.one_cta_per_tile ? tiles : (tiles < unit_budget ? tiles : unit_budget);
@@ -444,6 +446,28 @@ int bmoe_plan_set_gate(bmoe_plan* plan, const uint32_t* flags_dev, uint32_t epoc
   p.gate_epoch = epoch;
   p.gate_ranks = ranks;
   p.gate_self = self;
+  return BMOE_OK;
+}
+
+int bmoe_plan_set_push(bmoe_plan* plan, const void* origin_dev,
+                       const uint32_t* expert_row_dev, void* const* y_bases_dev,
+                       uint32_t ranks, uint64_t y_rows_cap) {
+  if (plan == nullptr || !plan->ready) return BMOE_INVALID_ARGUMENT;
+  bmoe::GemmParams& p = plan->params;
+  if (origin_dev == nullptr) {
+    p.push_origin = nullptr;
+    return BMOE_OK;
+  }
+  if (plan->out_f32 || expert_row_dev == nullptr || y_bases_dev == nullptr || ranks == 0 ||
+      y_rows_cap == 0) {
+    return BMOE_INVALID_ARGUMENT;
+  }
+  p.push_origin = static_cast<const long long*>(origin_dev);
+  p.push_expert_row = expert_row_dev;
+  p.push_bases = reinterpret_cast<uint4* const*>(y_bases_dev);
+  p.push_rows_cap = y_rows_cap;
+  p.push_vec_per_row = plan->stats_n / 8;
+  p.push_ranks = ranks;
   return BMOE_OK;
 }
 

@@ -88,15 +88,23 @@ class GroupedGemmPlan:
     ) -> int:
         """Pointer-array form of the reference arguments. Returns a status."""
         experts = len(tokens_per_expert)
-        arr_a = (C.c_void_p * max(1, experts))(*[p or None for p in a_ptrs])
-        arr_b = (C.c_void_p * max(1, experts))(*[p or None for p in b_ptrs])
-        arr_d = (C.c_void_p * max(1, experts))(*[p or None for p in d_ptrs])
-        counts = (C.c_uint32 * max(1, experts))(*[int(c) for c in tokens_per_expert])
+
+        def pointers(values):
+            if isinstance(values, np.ndarray):
+                arr = np.ascontiguousarray(values, dtype=np.uint64)
+            else:
+                arr = np.array([int(p or 0) for p in values], dtype=np.uint64)
+            return arr if arr.size else np.zeros(1, dtype=np.uint64)
+
+        arr_a, arr_b, arr_d = pointers(a_ptrs), pointers(b_ptrs), pointers(d_ptrs)
+        counts = np.ascontiguousarray(tokens_per_expert, dtype=np.uint32)
+        if counts.size == 0:
+            counts = np.zeros(1, dtype=np.uint32)
         args = _capi.GemmArgs(
-            a=C.cast(arr_a, C.POINTER(C.c_void_p)),
-            b=C.cast(arr_b, C.POINTER(C.c_void_p)),
-            d=C.cast(arr_d, C.POINTER(C.c_void_p)),
-            tokens_per_expert=C.cast(counts, C.POINTER(C.c_uint32)),
+            a=arr_a.ctypes.data_as(C.POINTER(C.c_void_p)),
+            b=arr_b.ctypes.data_as(C.POINTER(C.c_void_p)),
+            d=arr_d.ctypes.data_as(C.POINTER(C.c_void_p)),
+            tokens_per_expert=counts.ctypes.data_as(C.POINTER(C.c_uint32)),
             experts=experts,
             n=n,
             k=k,
@@ -127,19 +135,16 @@ class GroupedGemmPlan:
             return _capi.INVALID_ARGUMENT
         if not (a.is_contiguous() and w.is_contiguous() and d.is_contiguous()):
             return _capi.INVALID_ARGUMENT
-        total = int(sum(int(c) for c in tokens_per_expert))
+        counts = np.asarray(tokens_per_expert, dtype=np.int64)
+        total = int(counts.sum())
         if int(a.shape[0]) < total or int(d.shape[0]) < total:
             return _capi.INVALID_ARGUMENT
-        a_base, w_base, d_base = a.data_ptr(), w.data_ptr(), d.data_ptr()
-        a_ptrs, b_ptrs, d_ptrs = [], [], []
-        row = 0
-        for e, c in enumerate(tokens_per_expert):
-            a_ptrs.append(a_base + row * k * 2)
-            b_ptrs.append(w_base + e * n * k * 2)
-            d_ptrs.append(d_base + row * n * d_elem)
-            row += int(c)
+        first_row = (np.cumsum(counts) - counts).astype(np.uint64)
+        a_ptrs = np.uint64(a.data_ptr()) + first_row * np.uint64(k * 2)
+        b_ptrs = np.uint64(w.data_ptr()) + np.arange(experts, dtype=np.uint64) * np.uint64(n * k * 2)
+        d_ptrs = np.uint64(d.data_ptr()) + first_row * np.uint64(n * d_elem)
         self._keep = (a, w, d)
-        return self.initialize(a_ptrs, b_ptrs, d_ptrs, tokens_per_expert, n, k, **options)
+        return self.initialize(a_ptrs, b_ptrs, d_ptrs, counts, n, k, **options)
 
     # --------------------------------------------------------------- run --
     def run(self, stream=None) -> int:
@@ -150,6 +155,12 @@ class GroupedGemmPlan:
         group have arrived (see ``bmoe_plan_set_gate``); ``flags_ptr`` None removes it."""
         return int(self._lib.bmoe_plan_set_gate(self._handle, flags_ptr, epoch, ranks, self_rank,
                                                 group_of_ptr))
+
+    def set_push(self, origin_ptr, expert_row_ptr, y_bases_ptr, ranks: int, y_rows_cap: int) -> int:
+        """Send result rows straight to their origin ranks' buffers instead of D (see
+        ``bmoe_plan_set_push``); ``origin_ptr`` None switches back."""
+        return int(self._lib.bmoe_plan_set_push(self._handle, origin_ptr, expert_row_ptr,
+                                                y_bases_ptr, ranks, y_rows_cap))
 
     def poll(self) -> tuple[int, _capi.DeviceReport]:
         report = _capi.DeviceReport()

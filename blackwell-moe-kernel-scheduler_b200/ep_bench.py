@@ -79,7 +79,7 @@ def run(args, spec, workload):
     gen = torch.Generator(device=dev).manual_seed(4000 + rank)
     x_local = torch.randn(hi - lo, k, generator=gen, device=dev,
                           dtype=torch.float32).to(torch.bfloat16)
-    ep_groups = args.ep_groups or (4 if args.exchange == "fused" else 1)
+    ep_groups = args.ep_groups or (8 if args.exchange == "fused" else 1)
     groups = ep_groups if world > 1 else 1
     gates = None
     if args.topk_weights:
@@ -101,7 +101,8 @@ def run(args, spec, workload):
             owner, n, k, rank=rank, world=world, rows_cap=tokens * top_k,
             assignments_cap=(hi - lo) * top_k, scheduler=args.policy,
             exchange_groups=ep_groups, cta_group=args.cta_group,
-            dispatch_ctas=args.dispatch_ctas)
+            dispatch_ctas=args.dispatch_ctas, push_results=not args.no_push,
+            exchange_sms=args.exchange_sms)
         ops = layer
         plain = layer
         groups = layer.groups

@@ -10,9 +10,12 @@ transfer and the math run at the same time:
 * the grouped GEMM starts at once: its tile scheduler publishes the tiles of a
   group only when the flags of all other sources for that group are in, so early
   groups compute while late groups are still in flight;
-* a return kernel pushes every result row back to the rank it came from (the
-  dispatcher leaves an origin record beside each row), then raises a "done" flag;
-  the step ends when the other ranks' "done" flags are in.
+* the epilogue of the GEMM writes every result row straight into the result buffer
+  of the rank the row came from (the dispatcher leaves an origin record beside each
+  row), so the way back is spread over the run time of the GEMM as well; a last
+  small launch raises a "done" flag on every peer and the step ends when the other
+  ranks' "done" flags are in. (``push_results=False`` keeps D local and sends the
+  rows back with a separate kernel after the GEMM.)
 
 The only NCCL call per step is the all-gather of the per-expert counts. Kernels
 of one GPU never wait on each other: rows that stay on the rank are copied by a
@@ -31,45 +34,64 @@ import numpy as np
 from . import _capi
 
 
-def plan_step(counts_all, owner: Sequence[int], rank: int, groups: int, tile_m: int = 256):
-    """Host tables of one step from the count matrix ``counts_all`` [world, experts]
-    (numpy int64, identical on every rank).
+class StepPlanner:
+    """Host tables of one step, vectorised; everything that depends only on the
+    expert -> rank map is prepared once.
 
     Packed order on an owner: its experts in ascending id, and inside an expert the
     sources in ascending rank. Groups are contiguous runs of an owner's experts with
     about equal numbers of ``tile_m``-row tiles.
-
-    Returns a dict with ``local_experts``, ``local_m`` (rows per local expert),
-    ``row_base`` (int64 [experts]: first row of (expert, this rank) in the owner's A),
-    ``group_of`` (uint8 [experts]), ``group_local`` (uint8 per local expert) and
-    ``total_local``.
     """
+
+    def __init__(self, owner: Sequence[int], rank: int, world: int, groups: int, tile_m: int = 256):
+        self.rank, self.world, self.groups, self.tile_m = rank, world, max(1, groups), tile_m
+        owner_a = np.asarray(list(owner), dtype=np.int64)
+        self.experts = owner_a.size
+        self.order = np.lexsort((np.arange(self.experts), owner_a))     # by (owner, id)
+        self.owner_sorted = owner_a[self.order]
+        # position in `order` where each expert's owner segment starts
+        first = np.searchsorted(self.owner_sorted, np.arange(world), side="left")
+        self.seg_start = first[self.owner_sorted]
+        self.local = np.nonzero(owner_a == rank)[0]
+        self.owner_a = owner_a
+
+    def step(self, counts_all):
+        """``counts_all`` [world, experts] (numpy int64, identical on every rank). Returns a
+        dict with ``local_experts``, ``local_m`` (rows per local expert), ``row_base``
+        (int64 [experts]: first row of (expert, this rank) in the owner's A), ``group_of``
+        (uint8 [experts]), ``group_local`` (uint8 per local expert) and ``total_local``."""
+        counts_all = np.asarray(counts_all, dtype=np.int64)
+        totals = counts_all.sum(axis=0)
+        before_me = counts_all[:self.rank].sum(axis=0)
+        t = totals[self.order]
+        excl = np.cumsum(t) - t
+        row_base = np.empty(self.experts, dtype=np.int64)
+        row_base[self.order] = excl - excl[self.seg_start] + before_me[self.order]
+        group_of = np.zeros(self.experts, dtype=np.uint8)
+        if self.groups > 1:
+            tiles = (t + self.tile_m - 1) // self.tile_m
+            tiles_excl = np.cumsum(tiles) - tiles
+            before = tiles_excl - tiles_excl[self.seg_start]
+            per_owner = np.bincount(self.owner_sorted, weights=tiles, minlength=self.world)
+            total = np.maximum(1, per_owner[self.owner_sorted].astype(np.int64))
+            group_of[self.order] = np.minimum(self.groups - 1, before * self.groups // total)
+        local_m = totals[self.local]
+        return {
+            "local_experts": self.local.tolist(),
+            "local_m": local_m,
+            "row_base": row_base,
+            "group_of": group_of,
+            "group_local": group_of[self.local],
+            "total_local": int(local_m.sum()),
+        }
+
+
+def plan_step(counts_all, owner: Sequence[int], rank: int, groups: int, tile_m: int = 256):
+    """One-shot form of ``StepPlanner(...).step(counts_all)`` with ``local_m`` as a list."""
     counts_all = np.asarray(counts_all, dtype=np.int64)
-    world, experts = counts_all.shape
-    owner_a = np.asarray(list(owner), dtype=np.int64)
-    totals = counts_all.sum(axis=0)
-    before_me = counts_all[:rank].sum(axis=0)
-    row_base = np.zeros(experts, dtype=np.int64)
-    group_of = np.zeros(experts, dtype=np.uint8)
-    for q in range(world):
-        mine = np.nonzero(owner_a == q)[0]                 # ascending expert id
-        m = totals[mine]
-        start = np.cumsum(m) - m
-        row_base[mine] = start + before_me[mine]
-        tiles = (m + tile_m - 1) // tile_m
-        total_tiles = int(tiles.sum())
-        if total_tiles > 0 and groups > 1:
-            tiles_before = np.cumsum(tiles) - tiles
-            group_of[mine] = np.minimum(groups - 1, tiles_before * groups // total_tiles)
-    local = np.nonzero(owner_a == rank)[0]
-    return {
-        "local_experts": local.tolist(),
-        "local_m": totals[local].tolist(),
-        "row_base": row_base,
-        "group_of": group_of,
-        "group_local": group_of[local].copy(),
-        "total_local": int(totals[local].sum()),
-    }
+    out = StepPlanner(owner, rank, counts_all.shape[0], groups, tile_m).step(counts_all)
+    out["local_m"] = out["local_m"].tolist()
+    return out
 
 
 class _RawCudaBuffer:
@@ -143,10 +165,18 @@ class FusedExpertParallelLayer:
     def __init__(self, owner: Sequence[int], n: int, k: int, *, rank: int, world: int,
                  rows_cap: int, assignments_cap: int, group=None, scheduler="dynamic_queue",
                  exchange_groups: int = 4, dispatch_ctas: int = 0, wait_budget_ns: int = 0,
-                 **plan_options):
+                 push_results: bool = True, exchange_sms: int = 16, **plan_options):
         """``rows_cap``: packed rows this rank can own; ``assignments_cap``: local
         assignments (tokens x top_k) per step; ``exchange_groups``: groups the
-        experts of a rank are split into for the overlap (1 = no overlap)."""
+        experts of a rank are split into for the overlap (1 = no overlap).
+
+        ``exchange_sms`` (even, multi-rank only): SMs the grouped GEMM leaves free for
+        the kernel that pushes rows to other GPUs, which then runs as that many
+        1024-thread CTAs. An SM whose stores wait for NVLink stalls whatever else runs
+        on it, so sharing SMs with GEMM CTAs costs more than giving a few away. The
+        GEMM must then be a persistent policy (its grid is what leaves the SMs free).
+        0 = share: ``dispatch_ctas`` 256-thread CTAs (default 7/16 of the SMs) that fit
+        beside resident GEMM CTAs; any policy."""
         import torch
 
         from .engine import GroupedGemmPlan
@@ -160,10 +190,23 @@ class FusedExpertParallelLayer:
         self.rows_cap, self.assignments_cap = int(rows_cap), int(assignments_cap)
         self.groups = max(1, min(int(exchange_groups), _capi.EP_MAX_GROUPS)) if world > 1 else 1
         self.local_experts = [e for e in range(self.experts) if self.owner[e] == rank]
-        self.scheduler, self.plan_options = scheduler, plan_options
+        self.scheduler, self.plan_options = scheduler, dict(plan_options)
         self.dispatch_ctas, self.wait_budget_ns = int(dispatch_ctas), int(wait_budget_ns)
+        self.exchange_sms = int(exchange_sms) // 2 * 2 if world > 1 else 0
+        if self.exchange_sms:
+            if str(scheduler) in ("clc", "auto", "5", "4"):
+                raise ValueError("exchange_sms > 0 needs a persistent policy (static or "
+                                 "dynamic_queue): one CTA per tile would fill the SMs meant "
+                                 "for the exchange kernel")
+            sms = torch.cuda.get_device_properties(torch.cuda.current_device()) \
+                .multi_processor_count
+            pair = self.plan_options.get("cta_group", 0) != 1 and n > 128
+            self.plan_options["cta_group"] = 2 if pair else 1
+            self.plan_options["cta_count"] = max(1, (sms - self.exchange_sms) // (2 if pair else 1))
+        self.push_results = bool(push_results)
         self.tile_m = 128 if plan_options.get("cta_group") == 1 else 256
         self.plan = GroupedGemmPlan()
+        self._planner = StepPlanner(self.owner, rank, world, self.groups, self.tile_m)
         self.launches = 0
         self.epoch = 0
         dev = torch.device("cuda", torch.cuda.current_device())
@@ -178,8 +221,10 @@ class FusedExpertParallelLayer:
         self.d = loc["d"].view(torch.bfloat16)[:self.rows_cap * n].view(self.rows_cap, n)
         self.y = loc["y"].view(torch.bfloat16)[:self.assignments_cap * n] \
             .view(self.assignments_cap, n)
-        # per-step tables: int64 row_base[E] | uint8 group_of[E] | uint8 group_local[E]
-        self._table_bytes = 8 * self.experts + 2 * self.experts
+        # per-step tables: int64 row_base[E] | uint8 group_of[E] | uint8 group_local[E] |
+        # (4-aligned) uint32 first packed row of every local expert [E]
+        self._off_expert_row = (10 * self.experts + 3) // 4 * 4
+        self._table_bytes = self._off_expert_row + 4 * self.experts
         self._stage = torch.empty(self._table_bytes, dtype=torch.uint8).pin_memory()
         self._tables = torch.empty(self._table_bytes, dtype=torch.uint8, device=dev)
         self._owner_dev = torch.tensor(self.owner, dtype=torch.int32, device=dev)
@@ -213,7 +258,10 @@ class FusedExpertParallelLayer:
             dst_row_out_dev=routes[1].data_ptr() if routes else None,
             assignments=int(flat_ids.numel()), rows_cap=self.rows_cap, top_k=top_k,
             row_bytes=self.k * 2, experts=self.experts, ranks=self.world, self=self.rank,
-            groups=self.groups, mode=mode, epoch=self.epoch, max_ctas=self.dispatch_ctas,
+            groups=self.groups, mode=mode, epoch=self.epoch,
+            max_ctas=0 if mode == _capi.EP_LOCAL else (self.exchange_sms or self.dispatch_ctas),
+            block_threads=1024 if (mode != _capi.EP_LOCAL and self.exchange_sms) else 256,
+            cluster=2 if (mode != _capi.EP_LOCAL and self.exchange_sms) else 0,
             stream=stream.cuda_stream or None)
         _capi.check(self._lib.bmoe_ep_dispatch(C.byref(args)), "bmoe_ep_dispatch")
         self.launches += 1
@@ -265,7 +313,7 @@ class FusedExpertParallelLayer:
             counts_all = flat.reshape(self.world, self.experts).cpu().numpy()
         else:
             counts_all = local_counts.reshape(1, -1).cpu().numpy()
-        step = plan_step(counts_all, self.owner, self.rank, self.groups, self.tile_m)
+        step = self._planner.step(counts_all)
         if step["total_local"] > self.rows_cap:
             raise RuntimeError("routed rows exceed the packed buffer capacity")
         stage = self._stage.numpy()
@@ -273,6 +321,9 @@ class FusedExpertParallelLayer:
         stage[:8 * e].view(np.int64)[:] = step["row_base"]
         stage[8 * e:9 * e] = step["group_of"]
         stage[9 * e:9 * e + len(step["group_local"])] = step["group_local"]
+        local_m = step["local_m"]
+        stage[self._off_expert_row:self._off_expert_row + 4 * len(local_m)].view(np.uint32)[:] = \
+            np.cumsum(local_m) - local_m
         self._tables.copy_(self._stage, non_blocking=True)
         self._scratch.zero_()
         self.epoch += 1
@@ -283,6 +334,9 @@ class FusedExpertParallelLayer:
         self.routes = routes
         mark("counts")
 
+        # rows that stay here: same stream as the GEMM, and before the remote pushes
+        # start (an SM whose stores wait for NVLink slows this short copy several times)
+        self._dispatch(x, flat_ids, top_k, _capi.EP_LOCAL, main, routes)
         # rows bound for other GPUs: side stream, overlapped with everything below
         if self.world > 1:
             self._ev_start.record(main)
@@ -295,8 +349,6 @@ class FusedExpertParallelLayer:
             if record_events:
                 self._remote_marks[1].record(self._comm)
             self._ev_comm.record(self._comm)
-        # rows that stay here: same stream as the GEMM
-        self._dispatch(x, flat_ids, top_k, _capi.EP_LOCAL, main, routes)
         mark("local_rows")
 
         total_local = step["total_local"]
@@ -310,11 +362,20 @@ class FusedExpertParallelLayer:
                                                self.world, self.rank,
                                                self._tables.data_ptr() + 9 * e),
                             "bmoe_plan_set_gate")
+            if self.push_results:
+                _capi.check(self.plan.set_push(self.shared.local["origin"].data_ptr(),
+                                               self._tables.data_ptr() + self._off_expert_row,
+                                               self.shared.bases["y"].data_ptr(), self.world,
+                                               self.assignments_cap),
+                            "bmoe_plan_set_push")
             _capi.check(self.plan.run(main), "bmoe_plan_run")
             self.launches += 3
         mark("gemm")
 
-        self._return(total_local, main)
+        if not self.push_results:
+            self._return(total_local, main)
+        elif self.world > 1:
+            self._return(0, main)        # rows already went out of the epilogue: flags only
         if self.world > 1:
             _capi.check(
                 self._lib.bmoe_ep_wait_flags(self.shared.local["flags"].data_ptr(),
@@ -342,7 +403,7 @@ class FusedExpertParallelLayer:
             y = out
             mark("weighted_sum")
         self._marks = marks
-        self.last_local_m = step["local_m"]
+        self.last_local_m = step["local_m"].tolist()
         return y
 
     def poll(self):

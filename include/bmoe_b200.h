@@ -510,6 +510,8 @@ typedef struct bmoe_ep_dispatch_args {
   uint32_t mode;                   /* BMOE_EP_LOCAL / REMOTE / ALL */
   uint32_t epoch;
   uint32_t max_ctas;               /* 0 = default: 4 per SM for LOCAL, 7/16 of the SMs otherwise */
+  uint32_t block_threads;          /* 0 = 256; 256, 512 or 1024 */
+  uint32_t cluster;                /* 2 = launch the CTAs as pairs that fill whole SM pairs */
   void* stream;
 } bmoe_ep_dispatch_args;
 
@@ -555,6 +557,18 @@ int bmoe_ep_wait_flags(const uint32_t* flags_dev, uint32_t first_slot, uint32_t 
  * group_of_expert_dev: [experts of the plan] uint8, values < 32. */
 int bmoe_plan_set_gate(bmoe_plan* plan, const uint32_t* flags_dev, uint32_t epoch,
                        uint32_t ranks, uint32_t self, const uint8_t* group_of_expert_dev);
+
+/* Result push for the next bmoe_plan_run calls (BF16 output only): the epilogue
+ * writes every valid result row to row `assignment` of y_bases_dev[rank], following
+ * the origin record rank << 40 | assignment of the row (origin_dev, indexed by packed
+ * row: expert_row_dev[e] + row inside expert e), instead of storing it to D. With
+ * peer buffers in y_bases_dev this is the expert-parallel combine exchange, spread
+ * over the run time of the GEMM. Records whose rank or assignment is out of range
+ * are skipped. origin_dev == NULL switches back to D; so does bmoe_plan_initialize.
+ * After the run, bmoe_ep_return with rows == 0 raises the "done" flags. */
+int bmoe_plan_set_push(bmoe_plan* plan, const void* origin_dev,
+                       const uint32_t* expert_row_dev, void* const* y_bases_dev,
+                       uint32_t ranks, uint64_t y_rows_cap);
 
 /* Device buffers that other processes on the node can map (CUDA IPC):
  * bmoe_peer_alloc allocates `bytes` and writes a 64-byte handle; another process

@@ -178,6 +178,16 @@ def test_single_rank_fused_layer_and_gate(engine):
 
     ids, x, w = make_problem()
     want = reference_output(engine, x, ids, w, 4)
+    for push, opts in ((False, {}), (True, {"cta_group": 1}), (True, {"scheduler": "clc"})):
+        plain = ep_fused.FusedExpertParallelLayer([0] * 40, 512, 320, rank=0, world=1,
+                                                  rows_cap=2400, assignments_cap=2400,
+                                                  push_results=push, **opts)
+        try:
+            y = plain.forward(x.cuda(), ids.cuda(), w.cuda())
+            plain.poll()
+            assert torch.equal(y.view(torch.int16), want.view(torch.int16)), (push, opts)
+        finally:
+            plain.close()
     layer = ep_fused.FusedExpertParallelLayer([0] * 40, 512, 320, rank=0, world=1,
                                               rows_cap=2400, assignments_cap=2400)
     try:
@@ -305,6 +315,16 @@ def _ep_worker(rank, world, port, tmpdir):
         same = same and torch.equal(y.cpu().view(torch.int16), want_z.view(torch.int16))
         dist.barrier()
         fused.close()
+        kept = ep_fused.FusedExpertParallelLayer(owner, 512, 320, rank=rank, world=world,
+                                                 rows_cap=2400, assignments_cap=(hi - lo) * 4,
+                                                 exchange_groups=2, push_results=False,
+                                                 cta_group=1)
+        for _ in range(2):
+            y = kept.forward(x[lo:hi].cuda(), ids[lo:hi].cuda(), w[kept.local_experts].cuda())
+        kept.poll()
+        same = same and torch.equal(y.view(torch.int16), want.view(torch.int16))
+        dist.barrier()
+        kept.close()
         peer.close()
         Path(tmpdir, f"rank{rank}.txt").write_text(str(int(same)))
         dist.barrier()
