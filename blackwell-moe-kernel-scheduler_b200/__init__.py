@@ -5,7 +5,10 @@ Sub-modules:
   _capi     ctypes binding of ``include/bmoe_b200.h``
   planner   host planning interface (spec, worklist plan, claims, dispatch)
   engine    grouped-GEMM plan, device worklist builder, scheduler probe
+  runner    correctness + CUDA-event benchmark harness (reference CSV schema), cli
   ep        expert-parallel layer (torch.distributed all-to-all)
+  ep_peer   expert-parallel layer over peer memory (two routing kernels)
+  ep_fused  expert-parallel layer whose exchange overlaps the grouped GEMM
 
 The directory name contains hyphens; import it through the ``bmoe_b200`` module
 at the repository root.
@@ -32,6 +35,7 @@ from .planner import (  # noqa: F401
     select_kernel,
     static_cta_assignments,
 )
+from .runner import BenchmarkResult, load_token_counts, run_benchmark  # noqa: F401
 from .engine import (  # noqa: F401
     GroupedGemmPlan,
     TILE_DTYPE,

@@ -334,11 +334,8 @@ class FusedExpertParallelLayer:
         self.routes = routes
         mark("counts")
 
-        # rows that stay here: same stream as the GEMM, and before the remote pushes
-        # start (an SM whose stores wait for NVLink slows this short copy several times)
-        self._dispatch(x, flat_ids, top_k, _capi.EP_LOCAL, main, routes)
-        # rows bound for other GPUs: side stream, overlapped with everything below
-        if self.world > 1:
+        def push_remote():
+            # rows bound for other GPUs: side stream, overlapped with everything below
             self._ev_start.record(main)
             self._comm.wait_event(self._ev_start)
             if record_events:
@@ -349,6 +346,16 @@ class FusedExpertParallelLayer:
             if record_events:
                 self._remote_marks[1].record(self._comm)
             self._ev_comm.record(self._comm)
+
+        # Rows that stay here go in the GEMM's stream. With SMs set aside for the remote
+        # pushes the two launches cannot share an SM (registers), so the pushes start
+        # first; when they share SMs the local copy goes first, because an SM whose
+        # stores wait for NVLink slows this short copy several times.
+        if self.world > 1 and self.exchange_sms:
+            push_remote()
+        self._dispatch(x, flat_ids, top_k, _capi.EP_LOCAL, main, routes)
+        if self.world > 1 and not self.exchange_sms:
+            push_remote()
         mark("local_rows")
 
         total_local = step["total_local"]

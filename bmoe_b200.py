@@ -16,3 +16,8 @@ _spec = importlib.util.spec_from_file_location(
 _module = importlib.util.module_from_spec(_spec)
 sys.modules["bmoe_b200"] = _module
 _spec.loader.exec_module(_module)
+
+if __name__ == "__main__":  # python bmoe_b200.py --kernel v2_dynamic --csv ...
+    from bmoe_b200.cli import main
+
+    main()

@@ -252,6 +252,31 @@ def main() -> None:
         lambda i, e: (i % 7 - 3).astype(np.float64),
         lambda i, e: ((5 * i) % 13 - 6).astype(np.float64), 16.0)
 
+    # ---- data formats of the reference's Python harness ----
+    # CSV schema of blackwell_moe_tirx/runner.py (header and the formatting of one
+    # row built from fixed field values), and one routing file written by
+    # python/generate_workloads.py (JSON and CSV form) for the ingestion test.
+    from blackwell_moe_tirx.runner import BenchmarkResult
+    sample = dict(
+        device="NVIDIA B200", implementation="impl_name", acquisition="global atomic queue; claim 1",
+        distribution="zipf", experts=64, active_experts=61, tokens=4096, n=7168, k=2048,
+        tiles=3584, ctas=148, pipe_depth=2, claim_size=4, hybrid_main_claim_size=8,
+        hybrid_tail_tiles=296, cv_m=1.23456789, max_over_mean_m=7.5, inactive_expert_ratio=0.046875,
+        small_m_expert_ratio=0.75, expert_tile_cv=1.1, max_expert_tiles_over_mean=6.25,
+        tiles_per_cta=24.2162162, useful_work_ratio=0.8765432, median_ms=0.32691, p95_ms=0.3400004,
+        effective_tflops=367.94449, max_abs_error=0.0078125, max_rel_error=1.25e-05)
+    out["runner"] = {"csv_header": BenchmarkResult.csv_header(),
+                     "sample_fields": sample,
+                     "sample_row": BenchmarkResult(**sample).csv_row()}
+    import subprocess
+    script = REFERENCE / "python" / "generate_workloads.py"
+    flags = ["--distribution", "zipf", "--experts", "16", "--tokens", "512", "--seed", "7",
+             "--zipf-alpha", "1.1"]
+    for fmt in ("json", "csv"):
+        text = subprocess.run([sys.executable, str(script), *flags, "--format", fmt],
+                              check=True, capture_output=True, text=True).stdout
+        (HERE / f"workload_zipf_e16_t512.{fmt}").write_text(text)
+
     path = HERE / "reference_vectors.json"
     path.write_text(json.dumps(out, indent=1, sort_keys=True) + "\n")
     print(f"wrote {path} ({path.stat().st_size} bytes)")

@@ -305,3 +305,32 @@ def test_fp32_output_epilogue(engine, oracle):
         plan.close()
     exact = oracle.grouped_gemm(a_bits, w_bits, c2, n2, k2, want_f32=True)["f32"]
     assert np.array_equal(d2.cpu().numpy(), exact)
+
+
+@pytest.mark.gpu
+def test_harness_runs_every_launch_variant(engine, tmp_path, capsys):
+    """run_benchmark (the reference harness's call) for every version name: correctness
+    with the reference's tolerances, a CSV row in its schema, and the command line with a
+    routing file of the reference's generator."""
+    from pathlib import Path
+
+    spec = engine.MoESpec(experts=6, tokens=700, n=384, k=256, cta_count=148, hybrid_tail_tiles=8)
+    plan = engine.build_workload_plan(spec, "zipf", seed=11)
+    header = engine.BenchmarkResult.csv_header().split(",")
+    for version in engine.list_versions():
+        result = engine.run_benchmark(spec, plan, version=version, warmup=2, iterations=5)
+        row = result.csv_row().split(",")
+        assert len(row) == len(header)
+        assert result.max_abs_error <= 5.0e-2 and result.median_ms > 0 and result.tiles == len(plan.tiles)
+        assert result.p95_ms >= result.median_ms and result.effective_tflops > 0
+    only = engine.run_benchmark(spec, plan, version="v2_dynamic", correctness_only=True)
+    assert only.median_ms != only.median_ms  # NaN: nothing was timed
+
+    from bmoe_b200 import cli
+    routing = Path(__file__).resolve().parent / "golden" / "workload_zipf_e16_t512.json"
+    cli.main(["--kernel", "auto", "--workload-file", str(routing), "--n", "256", "--k", "128",
+              "--warmup", "1", "--iterations", "3", "--csv"])
+    out = capsys.readouterr().out.strip().splitlines()
+    assert out[0] == engine.BenchmarkResult.csv_header() and out[1].split(",")[3] == "zipf"
+    with pytest.raises(ValueError):
+        engine.run_benchmark(spec, plan, dump_cuda=tmp_path / "k.cu")

@@ -235,3 +235,31 @@ def test_dispatch_equals_reference_python(engine, golden):
         assert plan.logical_flops == case["logical_flops"]
         assert plan.padded_flops == case["padded_flops"]
         assert support.sha(np.asarray(plan.device_worklist(), dtype=np.int32)) == case["worklist_sha256"]
+
+
+def test_harness_csv_schema_and_routing_files_match_the_reference(engine):
+    """BenchmarkResult writes the reference harness's CSV (header and number formats
+    pinned by a row the reference class formatted), and load_token_counts reads the
+    files of the reference's generate_workloads.py."""
+    import json
+    from pathlib import Path
+
+    golden_dir = Path(__file__).resolve().parent / "golden"
+    golden = json.loads((golden_dir / "reference_vectors.json").read_text())["runner"]
+    assert engine.BenchmarkResult.csv_header() == golden["csv_header"]
+    assert engine.BenchmarkResult(**golden["sample_fields"]).csv_row() == golden["sample_row"]
+
+    counts, name, seed = engine.load_token_counts(golden_dir / "workload_zipf_e16_t512.json")
+    assert (len(counts), sum(counts), name, seed) == (16, 512, "zipf", 7)
+    from_csv, csv_name, _ = engine.load_token_counts(golden_dir / "workload_zipf_e16_t512.csv")
+    assert from_csv == counts and csv_name == "trace"
+    spec = engine.MoESpec(experts=16, tokens=512, n=256, k=128)
+    plan = engine.build_workload_plan(spec, name, seed=seed, token_counts=counts)
+    assert plan.tokens_per_expert == counts and plan.distribution == "zipf"
+
+    from bmoe_b200 import cli
+    args = cli.build_parser().parse_args([])
+    assert (args.kernel, args.experts, args.tokens, args.n, args.k, args.ctas, args.warmup,
+            args.iterations) == ("v1_static_ws", 64, 4096, 7168, 2048, 148, 20, 200)
+    with pytest.raises(ValueError):
+        engine.run_benchmark(spec, plan, warmup=-1)
