@@ -44,6 +44,9 @@ WORKLOADS = {
     # small expert-parallel case for profiler captures of the routing kernels
     "profile_ep_e32_t4096_k7168_n2048_zipf1.0": dict(
         experts=32, top_k=4, tokens=4096, k=7168, n=2048, distribution=3, zipf_alpha=1.0),
+    # same, top-8 and 16384 tokens: the weighted top-k sum reads 537 MB (> L2)
+    "profile_ep_e32_t16384_top8_k7168_n2048_zipf1.0": dict(
+        experts=32, top_k=8, tokens=16384, k=7168, n=2048, distribution=3, zipf_alpha=1.0),
     "ep_deepseek_e256_t32768_k7168_n2048_zipf1.0": dict(
         experts=256, top_k=8, tokens=32768, k=7168, n=2048, distribution=3, zipf_alpha=1.0),
 }
@@ -354,12 +357,13 @@ def run_single_gpu(args, spec, workload):
     sampler = ClockSampler(0)
     sampler.start()
     time.sleep(0.25)
-    launches_before = plan.stats().launches
     torch.cuda.synchronize()
-    samples = time_policy(torch, plan, stream, args.steps)
-    # the K steps again as one region (event pair around all of them)
+    # per-launch samples for p50 / p99 (at least 1000 launches for the p99)
+    samples = time_policy(torch, plan, stream, max(args.steps, 1000))
+    # the timed region: exactly K steps inside one event pair
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
+    launches_before = plan.stats().launches
     t0.record(stream)
     for _ in range(args.steps):
         plan.run(stream)
@@ -373,6 +377,22 @@ def run_single_gpu(args, spec, workload):
     ms_per_step = region_ms / args.steps
     value = flops / (ms_per_step * 1e-3) / 1e12
     avg_launch_ms = sum(samples) / len(samples)
+
+    # The same launch with the per-step set-up inside the measurement: counts upload,
+    # worklist kernels and TMA descriptors rebuilt before every run (routing changes per step).
+    replan = []
+    for _ in range(60):
+        r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        r0.record(stream)
+        status = plan.initialize_packed(a, w, d, counts, scheduler=args.policy,
+                                        cta_group=args.cta_group, stream=stream) or plan.run(stream)
+        r1.record(stream)
+        if status != 0:
+            raise RuntimeError("re-plan step failed")
+        replan.append((r0, r1))
+    torch.cuda.synchronize()
+    replan_ms = [x.elapsed_time(y) for x, y in replan][10:]
+    check(plan, "re-plan steps")
 
     # ---------------- per-policy latency table (outside the headline region) --
     policies = {}
@@ -524,6 +544,9 @@ def run_single_gpu(args, spec, workload):
                    "l2": "weights (%.0f MB) exceed the 126 MB L2; no flush between steps"
                          % (active * n * k * 2 / 1e6)},
         "p50_us": percentile(samples, 0.5) * 1e3, "p99_us": percentile(samples, 0.99) * 1e3,
+        "latency_samples": len(samples),
+        "p50_us_with_replan": percentile(replan_ms, 0.5) * 1e3,
+        "p99_us_with_replan": percentile(replan_ms, 0.99) * 1e3,
         "policies": policies, "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
         "gpu_launches": launches, "clocks": clocks,
     }
@@ -574,12 +597,22 @@ def run_skew_sweep(args):
         d = torch.zeros(sum(counts), n, dtype=torch.bfloat16, device=dev)
         flops = 2.0 * sum(counts) * n * k
         plans = []
-        for policy, opts in (("expert_order", {}), ("static_persistent", {}),
-                             ("dynamic_queue", {}), ("clc", {}), ("auto", {})):
+        # "auto" = the plan's own rule (fitted thresholds); "reference_rule" = the variant
+        # the reference's bootstrap thresholds pick, launched as that variant.
+        picked = cap.VARIANT_NAMES[variant.value]
+        mspec = engine.MoESpec(experts=len(counts), tokens=sum(counts), n=n, k=k)
+        ref_opts = dict(engine.get_descriptor(picked).engine_options(mspec))
+        ref_policy = ref_opts.pop("scheduler")
+        ref_opts.pop("cta_count", None)
+        for label_, policy, opts in (("expert_order", "expert_order", {}),
+                                     ("static_persistent", "static_persistent", {}),
+                                     ("dynamic_queue", "dynamic_queue", {}), ("clc", "clc", {}),
+                                     ("auto", "auto", {}),
+                                     ("reference_rule", ref_policy, ref_opts)):
             plan = engine.GroupedGemmPlan()
             cap.check(plan.initialize_packed(a, w, d, counts, scheduler=policy, stream=stream,
-                                             cta_group=args.cta_group, **opts), policy)
-            plans.append((policy, plan))
+                                             cta_group=args.cta_group, **opts), label_)
+            plans.append((label_, plan))
         for _ in range(max(3, args.warmup)):
             for _, plan in plans:
                 plan.run(stream)
@@ -650,6 +683,9 @@ def main():
     ap.add_argument("--exchange-sms", type=int, default=16,
                     help="fused exchange: SMs the GEMM leaves to the remote-row kernel "
                          "(0 = share SMs, see --dispatch-ctas)")
+    ap.add_argument("--split-hot", action="store_true",
+                    help="fused exchange: cut experts above half a rank's fair share of the "
+                         "tiles into row shards placed on several ranks")
     ap.add_argument("--no-push", action="store_true",
                     help="fused exchange: return result rows with a kernel after the GEMM "
                          "instead of from its epilogue")
@@ -679,4 +715,11 @@ def main():
 
 
 if __name__ == "__main__":
+    # Standard output carries exactly one JSON line. Libraries that write to file
+    # descriptor 1 themselves (NCCL's version banner) are sent to stderr: Python's
+    # sys.stdout keeps the real stdout, descriptor 1 becomes a copy of stderr.
+    sys.stdout.flush()
+    sys.stdout = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     main()
+    sys.stdout.flush()

@@ -131,19 +131,29 @@ class RoutingFeatures(C.Structure):
     ]
 
 
-class EpDispatchArgs(C.Structure):
+class EpRouteArgs(C.Structure):
     _fields_ = [
-        ("x_dev", C.c_void_p), ("expert_ids_dev", C.c_void_p), ("row_base_dev", C.c_void_p),
-        ("owner_dev", C.c_void_p), ("group_of_dev", C.c_void_p), ("cursor_dev", C.c_void_p),
-        ("a_bases_dev", C.c_void_p), ("origin_bases_dev", C.c_void_p),
-        ("flag_bases_dev", C.c_void_p), ("group_done_dev", C.c_void_p),
-        ("chunk_next_dev", C.c_void_p),
+        ("expert_ids_dev", C.c_void_p), ("row_base_dev", C.c_void_p), ("owner_dev", C.c_void_p),
+        ("group_of_dev", C.c_void_p), ("cursor_dev", C.c_void_p),
+        ("origin_bases_dev", C.c_void_p), ("entries_dev", C.c_void_p),
+        ("bucket_offset_dev", C.c_void_p), ("bucket_fill_dev", C.c_void_p),
         ("dst_rank_out_dev", C.c_void_p), ("dst_row_out_dev", C.c_void_p),
         ("assignments", C.c_uint64), ("rows_cap", C.c_uint64),
-        ("top_k", C.c_uint32), ("row_bytes", C.c_uint32), ("experts", C.c_uint32),
-        ("ranks", C.c_uint32), ("self", C.c_uint32), ("groups", C.c_uint32),
-        ("mode", C.c_uint32), ("epoch", C.c_uint32), ("max_ctas", C.c_uint32),
-        ("block_threads", C.c_uint32), ("cluster", C.c_uint32),
+        ("top_k", C.c_uint32), ("experts", C.c_uint32), ("ranks", C.c_uint32),
+        ("self", C.c_uint32), ("groups", C.c_uint32),
+        ("stream", C.c_void_p),
+    ]
+
+
+class EpDispatchArgs(C.Structure):
+    _fields_ = [
+        ("x_dev", C.c_void_p), ("entries_dev", C.c_void_p), ("bucket_offset_dev", C.c_void_p),
+        ("a_bases_dev", C.c_void_p), ("flag_bases_dev", C.c_void_p),
+        ("group_done_dev", C.c_void_p), ("chunk_next_dev", C.c_void_p),
+        ("assignments", C.c_uint64), ("tokens", C.c_uint64), ("rows_cap", C.c_uint64),
+        ("row_bytes", C.c_uint32), ("ranks", C.c_uint32), ("self", C.c_uint32),
+        ("groups", C.c_uint32), ("mode", C.c_uint32), ("epoch", C.c_uint32),
+        ("max_ctas", C.c_uint32), ("block_threads", C.c_uint32), ("cluster", C.c_uint32),
         ("stream", C.c_void_p),
     ]
 
@@ -341,6 +351,7 @@ SIGNATURES = {
         [C.c_void_p, C.c_uint32, C.c_uint64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64,
          C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p],
     ),
+    "bmoe_ep_route": (C.c_int, [C.c_void_p]),
     "bmoe_ep_dispatch": (C.c_int, [C.c_void_p]),
     "bmoe_ep_return": (C.c_int, [C.c_void_p]),
     "bmoe_ep_wait_flags": (

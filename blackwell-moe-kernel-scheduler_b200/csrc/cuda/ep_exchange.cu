@@ -1,10 +1,12 @@
 // Expert-parallel exchange overlapped with the grouped GEMM, over peer memory.
 //
 // Per step every rank (one GPU each)
-//   1. pushes its token rows straight into the owners' expert-major packed A
-//      (ep_dispatch_kernel). Experts are split into a few GROUPS in packed order;
-//      the kernel works group by group and, when all of its rows of a group have
-//      been written, raises a per-(group, source) flag in every peer's flag array;
+//   1. plans its routes (ep_route_kernel: destination row of every assignment, origin
+//      record beside it, one entry per row bucketed by exchange group) and pushes its
+//      token rows straight into the owners' expert-major packed A (ep_dispatch_kernel).
+//      Experts are split into a few GROUPS in packed order; the kernel works group by
+//      group and, when all of its rows of a group have been written, raises a
+//      per-(group, source) flag in every peer's flag array;
 //   2. runs ONE grouped GEMM whose tile scheduler holds back the tiles of a group
 //      until the flags of all other sources for that group have arrived
 //      (GemmParams::gate_*), so the math on early groups overlaps the transfer of
@@ -89,92 +91,154 @@ __device__ __forceinline__ void signal_peers_when_grid_done(uint32_t* counter,
   }
 }
 
-struct DispatchArgs {
-  const uint4* x;              // [tokens, k] BF16 token rows of this rank
-  const int64_t* expert_ids;   // [tokens * top_k]
+// One routed row to copy: token row `token` of this rank's x -> row `row` of rank `to`.
+struct RouteEntry {
+  uint32_t token;
+  uint32_t to;
+  uint32_t row;
+  uint32_t pad;
+};
+static_assert(sizeof(RouteEntry) == 16, "one 16-byte load per entry");
+
+struct RouteArgs {
+  const int64_t* expert_ids;   // [assignments]
   const int64_t* row_base;     // [experts] first row of (expert, this source) in the owner's A
   const int32_t* owner;        // [experts]
   const uint8_t* group_of;     // [experts] group of the expert on its owner
   uint32_t* cursor;            // [experts] rows handed out so far (zero at step start)
-  uint4* const* a_bases;       // [ranks] packed A of every rank
   long long* const* origin_bases;  // [ranks] origin record per packed row
-  uint32_t* const* flag_bases; // [ranks] flag arrays
-  uint32_t* group_done;        // [groups] CTA arrival counters (zero at step start)
-  uint32_t* chunk_next;        // [groups] next unclaimed chunk of 32 assignments (zero at start)
+  RouteEntry* entries;         // [assignments] bucketed: groups 0..G-1 (remote), G (local)
+  const uint32_t* bucket_offset;   // [groups + 2] from the host's count matrix
+  uint32_t* bucket_fill;       // [groups + 1] zero at step start
   int32_t* dst_rank_out;       // [assignments] or nullptr: where each assignment went
   int64_t* dst_row_out;        // [assignments] or nullptr
   uint64_t assignments;
   uint64_t rows_cap;
   uint32_t top_k;
-  uint32_t vec_per_row;
   uint32_t experts;
+  uint32_t ranks;
+  uint32_t self;
+  uint32_t groups;
+};
+
+// Route planning, one thread per assignment: destination row from the expert's cursor
+// (the order of rows inside an expert changes no result row, only where it sits), the
+// origin record beside that row, and one entry in the bucket of the row's exchange
+// group (or the local bucket). Lanes that hit the same expert or bucket share one
+// atomic. The copy kernels then walk dense lists instead of filtering all assignments
+// once per group.
+__global__ void __launch_bounds__(256) ep_route_kernel(RouteArgs a) {
+  const uint32_t lane = threadIdx.x & 31;
+  const uint32_t lanes_below = (1u << lane) - 1u;
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+  const uint64_t rounds = (a.assignments + stride - 1) / stride;
+  for (uint64_t r = 0; r < rounds; ++r) {  // whole warps stay together for the votes
+    const uint64_t i = r * stride + static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    int64_t e = -1;
+    int32_t to = -1;
+    uint32_t bucket = 0xffffffffu;
+    if (i < a.assignments) {
+      e = a.expert_ids[i];
+      if (e >= 0 && e < static_cast<int64_t>(a.experts)) {
+        to = a.owner[e];
+        if (to >= 0 && static_cast<uint32_t>(to) < a.ranks) {
+          bucket = static_cast<uint32_t>(to) == a.self ? a.groups : a.group_of[e];
+          if (bucket > a.groups) bucket = 0xffffffffu;
+        }
+      }
+    }
+    const bool live = bucket != 0xffffffffu;
+    // one cursor atomic per distinct expert in the warp
+    const uint32_t key_e = live ? static_cast<uint32_t>(e) : 0xffffffffu;
+    const uint32_t same_e = __match_any_sync(0xffffffffu, key_e);
+    uint32_t first_pos = 0;
+    const uint32_t lead_e = __ffs(same_e) - 1;
+    if (live && lane == lead_e) first_pos = atomicAdd(&a.cursor[e], __popc(same_e));
+    first_pos = __shfl_sync(0xffffffffu, first_pos, lead_e);
+    // one bucket atomic per distinct bucket in the warp
+    const uint32_t same_b = __match_any_sync(0xffffffffu, bucket);
+    uint32_t first_slot = 0;
+    const uint32_t lead_b = __ffs(same_b) - 1;
+    if (live && lane == lead_b) first_slot = atomicAdd(&a.bucket_fill[bucket], __popc(same_b));
+    first_slot = __shfl_sync(0xffffffffu, first_slot, lead_b);
+    if (!live) continue;
+    const int64_t row = a.row_base[e] + first_pos + __popc(same_e & lanes_below);
+    // A bad table must never become a stray access to another GPU's memory.
+    if (row < 0 || static_cast<uint64_t>(row) >= a.rows_cap) continue;
+    const uint32_t slot = a.bucket_offset[bucket] + first_slot + __popc(same_b & lanes_below);
+    if (slot >= a.bucket_offset[bucket + 1] || slot >= a.assignments) continue;
+    a.origin_bases[to][row] =
+        static_cast<long long>((static_cast<uint64_t>(a.self) << kOriginRankShift) | i);
+    RouteEntry entry;
+    entry.token = static_cast<uint32_t>(i / a.top_k);
+    entry.to = static_cast<uint32_t>(to);
+    entry.row = static_cast<uint32_t>(row);
+    entry.pad = 0;
+    a.entries[slot] = entry;
+    if (a.dst_rank_out != nullptr) a.dst_rank_out[i] = to;
+    if (a.dst_row_out != nullptr) a.dst_row_out[i] = row;
+  }
+}
+
+struct DispatchArgs {
+  const uint4* x;              // [tokens, k] BF16 token rows of this rank
+  const RouteEntry* entries;   // bucketed route entries (ep_route_kernel)
+  const uint32_t* bucket_offset;   // [groups + 2]
+  uint4* const* a_bases;       // [ranks] packed A of every rank
+  uint32_t* const* flag_bases; // [ranks] flag arrays
+  uint32_t* group_done;        // [groups] CTA arrival counters (zero at step start)
+  uint32_t* chunk_next;        // [groups + 1] next unclaimed entry per bucket (zero at start)
+  uint64_t tokens;
+  uint64_t rows_cap;
+  uint32_t vec_per_row;
   uint32_t ranks;
   uint32_t self;
   uint32_t groups;
   uint32_t mode;               // BMOE_EP_LOCAL / BMOE_EP_REMOTE / BMOE_EP_ALL
   uint32_t epoch;
-  uint32_t span;               // assignments per claim: 32, 16, 8 or 4
+  uint32_t span;               // entries per claim: 1..32
 };
 
-// Group by group, a warp claims 32 consecutive assignments at a time from a shared
-// counter (SMs that also push rows over NVLink or run GEMM CTAs are slower, so a
-// static split would wait for them): every lane
-// looks up one of them (expert, group, owner: three dependent loads, paid once per
-// 32 assignments), the lanes whose assignment belongs to this pass take a row from
-// the expert's cursor, and the warp then copies the selected token rows one after
-// the other, 512 contiguous bytes per instruction. The row inside (expert, source)
-// comes from an atomic cursor: the order of rows inside an expert does not change
-// any result row, only where it sits.
+// Bucket by bucket (exchange groups in order, then - or only - the local bucket), a
+// warp claims `span` entries at a time from a shared counter (SMs that also push rows
+// over NVLink or run GEMM CTAs are slower, so a static split would wait for them) and
+// copies those token rows one after the other, 512 contiguous bytes per instruction.
+// When every CTA has finished a remote group, the last one raises the group's flag on
+// all peers.
 __global__ void __launch_bounds__(1024) ep_dispatch_kernel(DispatchArgs a) {
   const uint32_t lane = threadIdx.x & 31;
-  // Small inputs claim fewer than 32 assignments at a time so that every SM gets work.
   const uint32_t span = a.span;
-  const uint32_t chunks = static_cast<uint32_t>((a.assignments + span - 1) / span);
-  // Rows that stay on this rank raise no flags: one pass over all groups.
-  const bool by_group = a.mode != BMOE_EP_LOCAL;
-  const uint32_t passes = by_group ? a.groups : 1u;
-  for (uint32_t g = 0; g < passes; ++g) {
+  const uint32_t first_bucket = a.mode == BMOE_EP_LOCAL ? a.groups : 0u;
+  const uint32_t end_bucket = a.mode == BMOE_EP_REMOTE ? a.groups : a.groups + 1u;
+  for (uint32_t b = first_bucket; b < end_bucket; ++b) {
+    const uint32_t begin = a.bucket_offset[b];
+    const uint32_t count = a.bucket_offset[b + 1] - begin;
     while (true) {
-      uint32_t c = 0;
-      if (lane == 0) c = atomicAdd(&a.chunk_next[g], 1u);
-      c = __shfl_sync(0xffffffffu, c, 0);
-      if (c >= chunks) break;
-      const uint64_t i = static_cast<uint64_t>(c) * span + lane;
-      int32_t to = -1;
-      int64_t row = -1;
-      if (lane < span && i < a.assignments) {
-        const int64_t e = a.expert_ids[i];
-        if (e >= 0 && e < static_cast<int64_t>(a.experts) && (!by_group || a.group_of[e] == g)) {
-          const int32_t owner = a.owner[e];
-          const bool local = static_cast<uint32_t>(owner) == a.self;
-          const bool wanted = a.mode == BMOE_EP_ALL || (a.mode == BMOE_EP_LOCAL) == local;
-          if (wanted && owner >= 0 && static_cast<uint32_t>(owner) < a.ranks) {
-            row = a.row_base[e] + atomicAdd(&a.cursor[e], 1u);
-            // A bad table must never become a stray access to another GPU's memory.
-            if (row >= 0 && static_cast<uint64_t>(row) < a.rows_cap) {
-              to = owner;
-              a.origin_bases[to][row] =
-                  static_cast<long long>((static_cast<uint64_t>(a.self) << kOriginRankShift) | i);
-              if (a.dst_rank_out != nullptr) a.dst_rank_out[i] = to;
-              if (a.dst_row_out != nullptr) a.dst_row_out[i] = row;
-            }
-          }
-        }
+      uint32_t at = 0;
+      if (lane == 0) at = atomicAdd(&a.chunk_next[b], span);
+      at = __shfl_sync(0xffffffffu, at, 0);
+      if (at >= count) break;
+      RouteEntry entry{};
+      bool have = false;
+      if (lane < span && at + lane < count) {
+        entry = a.entries[begin + at + lane];
+        // entries come from this GPU's own route kernel; check them all the same
+        have = entry.to < a.ranks && entry.row < a.rows_cap && entry.token < a.tokens;
       }
-      uint32_t todo = __ballot_sync(0xffffffffu, to >= 0);
+      uint32_t todo = __ballot_sync(0xffffffffu, have);
       while (todo != 0) {
-        const uint32_t b = __ffs(todo) - 1;
+        const uint32_t l = __ffs(todo) - 1;
         todo &= todo - 1;
-        const int32_t to_b = __shfl_sync(0xffffffffu, to, b);
-        const int64_t row_b = __shfl_sync(0xffffffffu, row, b);
-        copy_row(a.x + ((static_cast<uint64_t>(c) * span + b) / a.top_k) * a.vec_per_row,
-                 a.a_bases[to_b] + static_cast<uint64_t>(row_b) * a.vec_per_row, a.vec_per_row,
-                 lane);
+        const uint32_t token = __shfl_sync(0xffffffffu, entry.token, l);
+        const uint32_t to = __shfl_sync(0xffffffffu, entry.to, l);
+        const uint32_t row = __shfl_sync(0xffffffffu, entry.row, l);
+        copy_row(a.x + static_cast<uint64_t>(token) * a.vec_per_row,
+                 a.a_bases[to] + static_cast<uint64_t>(row) * a.vec_per_row, a.vec_per_row, lane);
       }
     }
-    if (by_group && a.ranks > 1) {
-      signal_peers_when_grid_done(&a.group_done[g], a.flag_bases, a.ranks, a.self,
-                                  g * a.ranks + a.self, a.epoch);
+    if (b < a.groups && a.ranks > 1) {
+      signal_peers_when_grid_done(&a.group_done[b], a.flag_bases, a.ranks, a.self,
+                                  b * a.ranks + a.self, a.epoch);
     }
   }
 }
@@ -250,38 +314,66 @@ uint32_t device_sms() {
 }  // namespace
 }  // namespace bmoe
 
+extern "C" int bmoe_ep_route(const bmoe_ep_route_args* args) {
+  if (args == nullptr) return BMOE_INVALID_ARGUMENT;
+  const bmoe_ep_route_args& c = *args;
+  if (c.ranks == 0 || c.self >= c.ranks || c.groups == 0 || c.groups > BMOE_EP_MAX_GROUPS ||
+      c.top_k == 0 || c.assignments > 0xffffffffull || c.rows_cap > 0xffffffffull ||
+      c.row_base_dev == nullptr || c.owner_dev == nullptr || c.group_of_dev == nullptr ||
+      c.cursor_dev == nullptr || c.origin_bases_dev == nullptr || c.entries_dev == nullptr ||
+      c.bucket_offset_dev == nullptr || c.bucket_fill_dev == nullptr ||
+      (c.assignments != 0 && c.expert_ids_dev == nullptr)) {
+    return BMOE_INVALID_ARGUMENT;
+  }
+  if (c.assignments == 0) return BMOE_OK;
+  bmoe::RouteArgs a;
+  a.expert_ids = c.expert_ids_dev;
+  a.row_base = c.row_base_dev;
+  a.owner = c.owner_dev;
+  a.group_of = c.group_of_dev;
+  a.cursor = c.cursor_dev;
+  a.origin_bases = reinterpret_cast<long long* const*>(c.origin_bases_dev);
+  a.entries = static_cast<bmoe::RouteEntry*>(c.entries_dev);
+  a.bucket_offset = c.bucket_offset_dev;
+  a.bucket_fill = c.bucket_fill_dev;
+  a.dst_rank_out = c.dst_rank_out_dev;
+  a.dst_row_out = c.dst_row_out_dev;
+  a.assignments = c.assignments;
+  a.rows_cap = c.rows_cap;
+  a.top_k = c.top_k;
+  a.experts = c.experts;
+  a.ranks = c.ranks;
+  a.self = c.self;
+  a.groups = c.groups;
+  const uint64_t want = (c.assignments + 255) / 256;
+  const uint64_t cap = 4ull * bmoe::device_sms();
+  const uint32_t grid = static_cast<uint32_t>(want < cap ? want : cap);
+  bmoe::ep_route_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(c.stream)>>>(a);
+  return cudaPeekAtLastError() == cudaSuccess ? BMOE_OK : BMOE_CUDA_ERROR;
+}
+
 extern "C" int bmoe_ep_dispatch(const bmoe_ep_dispatch_args* args) {
   if (args == nullptr) return BMOE_INVALID_ARGUMENT;
   const bmoe_ep_dispatch_args& c = *args;
   if (c.ranks == 0 || c.self >= c.ranks || c.groups == 0 || c.groups > BMOE_EP_MAX_GROUPS ||
-      c.mode > BMOE_EP_ALL || c.top_k == 0 || c.row_bytes == 0 || c.row_bytes % 16 != 0 ||
-      c.a_bases_dev == nullptr || c.origin_bases_dev == nullptr || c.cursor_dev == nullptr ||
-      c.row_base_dev == nullptr || c.owner_dev == nullptr || c.group_of_dev == nullptr ||
-      c.chunk_next_dev == nullptr || c.assignments > 0xffffffffull * 4 ||
-      (c.assignments != 0 && (c.x_dev == nullptr || c.expert_ids_dev == nullptr)) ||
+      c.mode > BMOE_EP_ALL || c.row_bytes == 0 || c.row_bytes % 16 != 0 ||
+      c.a_bases_dev == nullptr || c.entries_dev == nullptr || c.bucket_offset_dev == nullptr ||
+      c.chunk_next_dev == nullptr || (c.assignments != 0 && c.x_dev == nullptr) ||
       (c.ranks > 1 && c.mode != BMOE_EP_LOCAL &&
        (c.flag_bases_dev == nullptr || c.group_done_dev == nullptr))) {
     return BMOE_INVALID_ARGUMENT;
   }
   bmoe::DispatchArgs a;
   a.x = static_cast<const uint4*>(c.x_dev);
-  a.expert_ids = c.expert_ids_dev;
-  a.row_base = c.row_base_dev;
-  a.owner = c.owner_dev;
-  a.group_of = c.group_of_dev;
-  a.cursor = c.cursor_dev;
+  a.entries = static_cast<const bmoe::RouteEntry*>(c.entries_dev);
+  a.bucket_offset = c.bucket_offset_dev;
   a.a_bases = reinterpret_cast<uint4* const*>(c.a_bases_dev);
-  a.origin_bases = reinterpret_cast<long long* const*>(c.origin_bases_dev);
   a.flag_bases = reinterpret_cast<uint32_t* const*>(c.flag_bases_dev);
   a.group_done = c.group_done_dev;
   a.chunk_next = c.chunk_next_dev;
-  a.dst_rank_out = c.dst_rank_out_dev;
-  a.dst_row_out = c.dst_row_out_dev;
-  a.assignments = c.assignments;
+  a.tokens = c.tokens;
   a.rows_cap = c.rows_cap;
-  a.top_k = c.top_k;
   a.vec_per_row = c.row_bytes / 16;
-  a.experts = c.experts;
   a.ranks = c.ranks;
   a.self = c.self;
   a.groups = c.groups;
@@ -301,13 +393,14 @@ extern "C" int bmoe_ep_dispatch(const bmoe_ep_dispatch_args* args) {
   const uint64_t sms = bmoe::device_sms();
   const uint64_t cap = c.max_ctas != 0 ? c.max_ctas
                        : c.mode == BMOE_EP_LOCAL ? 4 * sms : (sms * 7 / 16 > 0 ? sms * 7 / 16 : 1);
-  // Assignments per claim: 32, or fewer when that would leave warps of the grid idle.
+  // Entries per claim: few enough that every warp of the grid gets several claims per
+  // bucket (the buckets of a step hold about assignments / buckets entries each).
   const uint64_t warps_cap = cap * (threads / 32);
-  uint32_t span = 32;
-  while (span > 4 && (c.assignments + span - 1) / span < 2 * warps_cap) span >>= 1;
+  const uint64_t per_bucket = c.assignments / (c.mode == BMOE_EP_LOCAL ? 1 : c.groups) + 1;
+  uint32_t span = 8;
+  while (span > 1 && per_bucket / span < 4 * warps_cap) span >>= 1;
   a.span = span;
-  const uint64_t per_cta = static_cast<uint64_t>(threads / 32) * span;
-  const uint64_t want = (c.assignments + per_cta - 1) / per_cta;
+  const uint64_t want = (c.assignments + 7) / 8;   // one warp per routed row at most
   uint32_t grid = static_cast<uint32_t>(want < cap ? want : cap);
   if (grid == 0) grid = 1;  // the flags are raised even when there is nothing to send
   cudaLaunchConfig_t config{};

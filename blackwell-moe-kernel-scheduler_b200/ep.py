@@ -41,6 +41,33 @@ def place_experts(global_counts: Sequence[int], ranks: int, n: int, *, tile_m: i
     return [int(x) for x in owner][:experts], [int(x) for x in loads][:ranks]
 
 
+def split_and_place_experts(global_counts: Sequence[int], ranks: int, n: int, *,
+                            tile_m: int = 128, tile_n: int = 256, max_share: float = 0.5):
+    """Placement with ROW SHARDS for hot experts. An expert whose tile count exceeds
+    ``max_share`` of one rank's fair share (total tiles / ranks) is cut into that many
+    shards of about equal rows (at most one per rank); every shard is then placed like
+    an expert by ``place_experts``. The ranks that own shards of an expert each hold a
+    copy of its weights; which shard a routed row goes to is decided per assignment
+    (assignment index modulo the shard count), and no result row depends on it.
+
+    Returns (parts, shard_owner, loads): ``parts[e]`` shards of expert e (1 = whole),
+    shards numbered expert-major (shard id = sum(parts[:e]) + p), ``shard_owner[s]``
+    the owning rank, ``loads`` the tiles per rank."""
+    counts = [int(c) for c in global_counts]
+    col_tiles = -(-n // tile_n)
+    tiles = [-(-c // tile_m) * col_tiles for c in counts]
+    fair = sum(tiles) / max(1, ranks)
+    parts = []
+    for t in tiles:
+        want = 1 if ranks <= 1 or fair <= 0 else -(-t // max(1, int(max_share * fair)))
+        parts.append(max(1, min(ranks, want)))
+    shard_counts = []
+    for c, p in zip(counts, parts):
+        shard_counts.extend(c // p + (1 if q < c % p else 0) for q in range(p))
+    shard_owner, loads = place_experts(shard_counts, ranks, n, tile_m=tile_m, tile_n=tile_n)
+    return parts, shard_owner, loads
+
+
 class CudaOps:
     """Device operations of the layer, all through the engine's C interface."""
 

@@ -72,8 +72,15 @@ def run(args, spec, workload):
     n, k, top_k, tokens = spec["n"], spec["k"], spec["top_k"], spec["tokens"]
     ids_all = _routing(torch, spec)
     global_counts = torch.bincount(ids_all.reshape(-1), minlength=spec["experts"]).tolist()
-    owner, rank_tiles = ep.place_experts(global_counts, world, n, tile_m=256 if args.cta_group != 1 else 128,
-                                         tile_n=256)
+    place_tile_m = 256 if args.cta_group != 1 else 128
+    parts = None
+    if args.exchange == "fused" and world > 1 and args.split_hot:
+        # experts above half a rank's fair share of the tiles are cut into row shards
+        parts, owner, rank_tiles = ep.split_and_place_experts(global_counts, world, n,
+                                                              tile_m=place_tile_m, tile_n=256)
+    else:
+        owner, rank_tiles = ep.place_experts(global_counts, world, n, tile_m=place_tile_m,
+                                             tile_n=256)
     lo, hi = tokens * rank // world, tokens * (rank + 1) // world
     ids_local = ids_all[lo:hi].to(dev)
     gen = torch.Generator(device=dev).manual_seed(4000 + rank)
@@ -102,7 +109,7 @@ def run(args, spec, workload):
             assignments_cap=(hi - lo) * top_k, scheduler=args.policy,
             exchange_groups=ep_groups, cta_group=args.cta_group,
             dispatch_ctas=args.dispatch_ctas, push_results=not args.no_push,
-            exchange_sms=args.exchange_sms)
+            exchange_sms=args.exchange_sms, expert_parts=parts)
         ops = layer
         plain = layer
         groups = layer.groups
@@ -242,7 +249,10 @@ def run(args, spec, workload):
         "data": "synthetic",
         "config": {"workload": workload, "experts": spec["experts"], "top_k": top_k,
                    "tokens": tokens, "k": k, "n": n, "policy": args.policy,
-                   "parallelism": f"ep{world}", "placement": "tile-count LPT",
+                   "parallelism": f"ep{world}",
+                   "placement": ("tile-count LPT" if parts is None else
+                                 "tile-count LPT over row shards: %d of %d experts split, %d shards"
+                                 % (sum(p > 1 for p in parts), len(parts), sum(parts))),
                    "exchange": args.exchange,
                    "last_step": "weighted top-k sum" if gates is not None else "rows in assignment order",
                    "pipeline_groups": groups, "comm_sms": args.comm_sms if groups > 1 else 0,

@@ -59,7 +59,9 @@ class StepPlanner:
         """``counts_all`` [world, experts] (numpy int64, identical on every rank). Returns a
         dict with ``local_experts``, ``local_m`` (rows per local expert), ``row_base``
         (int64 [experts]: first row of (expert, this rank) in the owner's A), ``group_of``
-        (uint8 [experts]), ``group_local`` (uint8 per local expert) and ``total_local``."""
+        (uint8 [experts]), ``group_local`` (uint8 per local expert), ``bucket_offset``
+        (uint32 [groups + 2]: this rank's route entries per exchange group, then the rows
+        that stay) and ``total_local``."""
         counts_all = np.asarray(counts_all, dtype=np.int64)
         totals = counts_all.sum(axis=0)
         before_me = counts_all[:self.rank].sum(axis=0)
@@ -75,6 +77,16 @@ class StepPlanner:
             per_owner = np.bincount(self.owner_sorted, weights=tiles, minlength=self.world)
             total = np.maximum(1, per_owner[self.owner_sorted].astype(np.int64))
             group_of[self.order] = np.minimum(self.groups - 1, before * self.groups // total)
+        # entries this rank routes per bucket: exchange groups 0..G-1 (rows bound for other
+        # ranks), then the rows that stay
+        mine = counts_all[self.rank]
+        away = self.owner_a != self.rank
+        sizes = np.zeros(self.groups + 1, dtype=np.int64)
+        sizes[:self.groups] = np.bincount(group_of[away], weights=mine[away],
+                                          minlength=self.groups)[:self.groups]
+        sizes[self.groups] = mine[~away].sum()
+        bucket_offset = np.zeros(self.groups + 2, dtype=np.uint32)
+        bucket_offset[1:] = np.cumsum(sizes)
         local_m = totals[self.local]
         return {
             "local_experts": self.local.tolist(),
@@ -82,6 +94,7 @@ class StepPlanner:
             "row_base": row_base,
             "group_of": group_of,
             "group_local": group_of[self.local],
+            "bucket_offset": bucket_offset,
             "total_local": int(local_m.sum()),
         }
 
@@ -165,10 +178,16 @@ class FusedExpertParallelLayer:
     def __init__(self, owner: Sequence[int], n: int, k: int, *, rank: int, world: int,
                  rows_cap: int, assignments_cap: int, group=None, scheduler="dynamic_queue",
                  exchange_groups: int = 4, dispatch_ctas: int = 0, wait_budget_ns: int = 0,
-                 push_results: bool = True, exchange_sms: int = 16, **plan_options):
+                 push_results: bool = True, exchange_sms: int = 16,
+                 expert_parts: Sequence[int] | None = None, **plan_options):
         """``rows_cap``: packed rows this rank can own; ``assignments_cap``: local
         assignments (tokens x top_k) per step; ``exchange_groups``: groups the
         experts of a rank are split into for the overlap (1 = no overlap).
+
+        ``expert_parts``: row shards per expert from ``ep.split_and_place_experts``; ``owner``
+        then has one entry per SHARD (expert-major), ``local_experts`` lists the expert of
+        every local shard (a split expert's weights live on several ranks) and routed rows
+        of a split expert are dealt to its shards by assignment index.
 
         ``exchange_sms`` (even, multi-rank only): SMs the grouped GEMM leaves free for
         the kernel that pushes rows to other GPUs, which then runs as that many
@@ -189,7 +208,15 @@ class FusedExpertParallelLayer:
         self.n, self.k, self.rank, self.world, self.group = n, k, rank, world, group
         self.rows_cap, self.assignments_cap = int(rows_cap), int(assignments_cap)
         self.groups = max(1, min(int(exchange_groups), _capi.EP_MAX_GROUPS)) if world > 1 else 1
-        self.local_experts = [e for e in range(self.experts) if self.owner[e] == rank]
+        self.local_shards = [e for e in range(self.experts) if self.owner[e] == rank]
+        self.expert_parts = None if expert_parts is None else [int(p) for p in expert_parts]
+        if self.expert_parts is None:
+            self.local_experts = list(self.local_shards)
+        else:
+            if sum(self.expert_parts) != self.experts or min(self.expert_parts) < 1:
+                raise ValueError("owner needs one entry per shard: sum(expert_parts)")
+            expert_of_shard = [e for e, p in enumerate(self.expert_parts) for _ in range(p)]
+            self.local_experts = [expert_of_shard[s] for s in self.local_shards]
         self.scheduler, self.plan_options = scheduler, dict(plan_options)
         self.dispatch_ctas, self.wait_budget_ns = int(dispatch_ctas), int(wait_budget_ns)
         self.exchange_sms = int(exchange_sms) // 2 * 2 if world > 1 else 0
@@ -223,16 +250,26 @@ class FusedExpertParallelLayer:
             .view(self.assignments_cap, n)
         # per-step tables: int64 row_base[E] | uint8 group_of[E] | uint8 group_local[E] |
         # (4-aligned) uint32 first packed row of every local expert [E]
+        # | uint32 bucket offsets [MAX_GROUPS + 2]
         self._off_expert_row = (10 * self.experts + 3) // 4 * 4
-        self._table_bytes = self._off_expert_row + 4 * self.experts
+        self._off_buckets = self._off_expert_row + 4 * self.experts
+        self._table_bytes = self._off_buckets + 4 * (_capi.EP_MAX_GROUPS + 2)
         self._stage = torch.empty(self._table_bytes, dtype=torch.uint8).pin_memory()
         self._tables = torch.empty(self._table_bytes, dtype=torch.uint8, device=dev)
         self._owner_dev = torch.tensor(self.owner, dtype=torch.int32, device=dev)
         # uint32 scratch zeroed every step: cursor[E] | group_done[MAX_GROUPS] | return
-        # counter | chunk counters of the remote and the local dispatch launch
-        self._scratch = torch.zeros(self.experts + 3 * _capi.EP_MAX_GROUPS + 1,
+        # counter | claim counters of the remote and of the local copy launch
+        # [MAX_GROUPS + 1 each] | bucket fill [MAX_GROUPS + 1]
+        g1 = _capi.EP_MAX_GROUPS + 1
+        self._scratch = torch.zeros(self.experts + _capi.EP_MAX_GROUPS + 1 + 3 * g1,
                                     dtype=torch.int32, device=dev)
+        self._entries = torch.empty(max(1, self.assignments_cap) * 16, dtype=torch.uint8,
+                                    device=dev)
         self._wait_status = torch.zeros(1, dtype=torch.int32, device=dev)
+        if self.expert_parts is not None:
+            parts = torch.tensor(self.expert_parts, dtype=torch.int64)
+            self._parts_dev = parts.to(dev)
+            self._shard_base_dev = (torch.cumsum(parts, 0) - parts).to(dev)
         self._comm = torch.cuda.Stream(device=dev)
         self._ev_start = torch.cuda.Event()
         self._ev_comm = torch.cuda.Event()
@@ -243,25 +280,44 @@ class FusedExpertParallelLayer:
         self.shared.close()
 
     # ------------------------------------------------------------- launches --
-    def _dispatch(self, x, flat_ids, top_k, mode, stream, routes):
-        b = self.shared.bases
+    def _scratch_ptr(self, word: int) -> int:
+        return self._scratch.data_ptr() + 4 * word
+
+    def _route(self, flat_ids, top_k, stream, routes):
+        e, g1 = self.experts, _capi.EP_MAX_GROUPS + 1
         t = self._tables.data_ptr()
-        args = _capi.EpDispatchArgs(
-            x_dev=x.data_ptr(), expert_ids_dev=flat_ids.data_ptr(), row_base_dev=t,
-            owner_dev=self._owner_dev.data_ptr(), group_of_dev=t + 8 * self.experts,
-            cursor_dev=self._scratch.data_ptr(), a_bases_dev=b["a"].data_ptr(),
-            origin_bases_dev=b["origin"].data_ptr(), flag_bases_dev=b["flags"].data_ptr(),
-            group_done_dev=self._scratch.data_ptr() + 4 * self.experts,
-            chunk_next_dev=self._scratch.data_ptr() + 4 * (
-                self.experts + _capi.EP_MAX_GROUPS * (1 if mode == _capi.EP_REMOTE else 2) + 1),
+        args = _capi.EpRouteArgs(
+            expert_ids_dev=flat_ids.data_ptr(), row_base_dev=t,
+            owner_dev=self._owner_dev.data_ptr(), group_of_dev=t + 8 * e,
+            cursor_dev=self._scratch_ptr(0),
+            origin_bases_dev=self.shared.bases["origin"].data_ptr(),
+            entries_dev=self._entries.data_ptr(), bucket_offset_dev=t + self._off_buckets,
+            bucket_fill_dev=self._scratch_ptr(e + _capi.EP_MAX_GROUPS + 1 + 2 * g1),
             dst_rank_out_dev=routes[0].data_ptr() if routes else None,
             dst_row_out_dev=routes[1].data_ptr() if routes else None,
             assignments=int(flat_ids.numel()), rows_cap=self.rows_cap, top_k=top_k,
-            row_bytes=self.k * 2, experts=self.experts, ranks=self.world, self=self.rank,
-            groups=self.groups, mode=mode, epoch=self.epoch,
-            max_ctas=0 if mode == _capi.EP_LOCAL else (self.exchange_sms or self.dispatch_ctas),
-            block_threads=1024 if (mode != _capi.EP_LOCAL and self.exchange_sms) else 256,
-            cluster=2 if (mode != _capi.EP_LOCAL and self.exchange_sms) else 0,
+            experts=e, ranks=self.world, self=self.rank, groups=self.groups,
+            stream=stream.cuda_stream or None)
+        _capi.check(self._lib.bmoe_ep_route(C.byref(args)), "bmoe_ep_route")
+        if flat_ids.numel():
+            self.launches += 1
+
+    def _dispatch(self, x, assignments, mode, stream):
+        e, g1 = self.experts, _capi.EP_MAX_GROUPS + 1
+        remote = mode != _capi.EP_LOCAL
+        args = _capi.EpDispatchArgs(
+            x_dev=x.data_ptr(), entries_dev=self._entries.data_ptr(),
+            bucket_offset_dev=self._tables.data_ptr() + self._off_buckets,
+            a_bases_dev=self.shared.bases["a"].data_ptr(),
+            flag_bases_dev=self.shared.bases["flags"].data_ptr(),
+            group_done_dev=self._scratch_ptr(e),
+            chunk_next_dev=self._scratch_ptr(e + _capi.EP_MAX_GROUPS + 1 + (0 if remote else g1)),
+            assignments=assignments, tokens=int(x.shape[0]), rows_cap=self.rows_cap,
+            row_bytes=self.k * 2, ranks=self.world, self=self.rank, groups=self.groups,
+            mode=mode, epoch=self.epoch,
+            max_ctas=(self.exchange_sms or self.dispatch_ctas) if remote else 0,
+            block_threads=1024 if (remote and self.exchange_sms) else 256,
+            cluster=2 if (remote and self.exchange_sms) else 0,
             stream=stream.cuda_stream or None)
         _capi.check(self._lib.bmoe_ep_dispatch(C.byref(args)), "bmoe_ep_dispatch")
         self.launches += 1
@@ -271,7 +327,7 @@ class FusedExpertParallelLayer:
         args = _capi.EpReturnArgs(
             d_dev=self.d.data_ptr(), origin_dev=self.shared.local["origin"].data_ptr(),
             y_bases_dev=b["y"].data_ptr(), flag_bases_dev=b["flags"].data_ptr(),
-            done_counter_dev=self._scratch.data_ptr() + 4 * (self.experts + _capi.EP_MAX_GROUPS),
+            done_counter_dev=self._scratch_ptr(self.experts + _capi.EP_MAX_GROUPS),
             rows=rows, y_rows_cap=self.assignments_cap, row_bytes=self.n * 2, ranks=self.world,
             self=self.rank, flag_slot=_capi.EP_MAX_GROUPS * self.world + self.rank,
             epoch=self.epoch, max_ctas=0, stream=stream.cuda_stream or None)
@@ -293,6 +349,14 @@ class FusedExpertParallelLayer:
         top_k = int(expert_ids.shape[1])
         flat_ids = expert_ids.reshape(-1).contiguous()
         assignments = int(flat_ids.numel())
+        if self.expert_parts is not None:
+            # expert -> shard: rows of a split expert are dealt round-robin by assignment index
+            real = len(self.expert_parts)
+            valid = (flat_ids >= 0) & (flat_ids < real)
+            safe = flat_ids.clamp(0, real - 1)
+            deal = torch.arange(assignments, device=dev, dtype=torch.int64) % self._parts_dev[safe]
+            flat_ids = torch.where(valid, self._shard_base_dev[safe] + deal,
+                                   torch.full_like(flat_ids, -1))
         if assignments > self.assignments_cap:
             raise RuntimeError("more assignments than the result buffer holds")
         marks = []
@@ -324,6 +388,8 @@ class FusedExpertParallelLayer:
         local_m = step["local_m"]
         stage[self._off_expert_row:self._off_expert_row + 4 * len(local_m)].view(np.uint32)[:] = \
             np.cumsum(local_m) - local_m
+        buckets = step["bucket_offset"]
+        stage[self._off_buckets:self._off_buckets + 4 * len(buckets)].view(np.uint32)[:] = buckets
         self._tables.copy_(self._stage, non_blocking=True)
         self._scratch.zero_()
         self.epoch += 1
@@ -332,6 +398,7 @@ class FusedExpertParallelLayer:
             routes = (torch.full((assignments,), -1, dtype=torch.int32, device=dev),
                       torch.full((assignments,), -1, dtype=torch.int64, device=dev))
         self.routes = routes
+        self._route(flat_ids, top_k, main, routes)
         mark("counts")
 
         def push_remote():
@@ -342,7 +409,7 @@ class FusedExpertParallelLayer:
                 self._remote_marks = (torch.cuda.Event(enable_timing=True),
                                       torch.cuda.Event(enable_timing=True))
                 self._remote_marks[0].record(self._comm)
-            self._dispatch(x, flat_ids, top_k, _capi.EP_REMOTE, self._comm, routes)
+            self._dispatch(x, assignments, _capi.EP_REMOTE, self._comm)
             if record_events:
                 self._remote_marks[1].record(self._comm)
             self._ev_comm.record(self._comm)
@@ -353,7 +420,7 @@ class FusedExpertParallelLayer:
         # stores wait for NVLink slows this short copy several times.
         if self.world > 1 and self.exchange_sms:
             push_remote()
-        self._dispatch(x, flat_ids, top_k, _capi.EP_LOCAL, main, routes)
+        self._dispatch(x, assignments, _capi.EP_LOCAL, main)
         if self.world > 1 and not self.exchange_sms:
             push_remote()
         mark("local_rows")

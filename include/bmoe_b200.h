@@ -483,27 +483,51 @@ int bmoe_combine_topk(const void* const* src_bases_dev, uint32_t n_src,
 #define BMOE_EP_REMOTE 1u  /* only rows owned by other ranks; raises the group flags */
 #define BMOE_EP_ALL 2u
 
-typedef struct bmoe_ep_dispatch_args {
-  const void* x_dev;               /* [tokens, row_bytes] token rows of this rank */
+typedef struct bmoe_ep_route_args {
   const int64_t* expert_ids_dev;   /* [assignments] expert of assignment i (token i / top_k);
                                       ids outside [0, experts) are dropped */
   const int64_t* row_base_dev;     /* [experts] first row of (expert, this rank) in the owner's A */
   const int32_t* owner_dev;        /* [experts] owning rank */
-  const uint8_t* group_of_dev;     /* [experts] group of the expert, < groups */
-  uint32_t* cursor_dev;            /* [experts] zero at step start (shared by the LOCAL and
-                                      REMOTE launches of a step) */
-  void* const* a_bases_dev;        /* [ranks] packed A buffers, rows_cap rows each */
+  const uint8_t* group_of_dev;     /* [experts] exchange group of the expert, < groups */
+  uint32_t* cursor_dev;            /* [experts] zero at step start */
   void* const* origin_bases_dev;   /* [ranks] int64 origin record per packed row */
-  void* const* flag_bases_dev;     /* [ranks] flag arrays (REMOTE / ALL with ranks > 1) */
-  uint32_t* group_done_dev;        /* [groups] zero at step start (REMOTE / ALL) */
-  uint32_t* chunk_next_dev;        /* [groups] zero at step start; one array per launch */
+  void* entries_dev;               /* [assignments] 16-byte route entries, written here */
+  const uint32_t* bucket_offset_dev; /* [groups + 2] first entry of bucket b: groups 0..G-1 hold
+                                      the rows bound for other ranks, bucket G the rows that
+                                      stay; sizes follow from the count matrix */
+  uint32_t* bucket_fill_dev;       /* [groups + 1] zero at step start */
   int32_t* dst_rank_out_dev;       /* [assignments] or NULL: destination of every assignment */
   int64_t* dst_row_out_dev;        /* [assignments] or NULL */
-  uint64_t assignments;
-  uint64_t rows_cap;
+  uint64_t assignments;            /* < 2^32 */
+  uint64_t rows_cap;               /* rows every packed A holds, < 2^32 */
   uint32_t top_k;
-  uint32_t row_bytes;              /* k * 2, multiple of 16 */
   uint32_t experts;
+  uint32_t ranks;
+  uint32_t self;
+  uint32_t groups;
+  void* stream;
+} bmoe_ep_route_args;
+
+/* Route planning of one step: the destination row of every assignment (the row inside
+ * (expert, source) comes from an atomic cursor, so the order of rows inside an expert
+ * is arbitrary; no result row depends on it), the origin record
+ * rank << 40 | assignment beside that row in the owner's memory, and one entry per
+ * routed row in the bucket of its exchange group. Precedes bmoe_ep_dispatch in stream
+ * order. */
+int bmoe_ep_route(const bmoe_ep_route_args* args);
+
+typedef struct bmoe_ep_dispatch_args {
+  const void* x_dev;               /* [tokens, row_bytes] token rows of this rank */
+  const void* entries_dev;         /* route entries written by bmoe_ep_route */
+  const uint32_t* bucket_offset_dev; /* [groups + 2], as for bmoe_ep_route */
+  void* const* a_bases_dev;        /* [ranks] packed A buffers, rows_cap rows each */
+  void* const* flag_bases_dev;     /* [ranks] flag arrays (REMOTE / ALL with ranks > 1) */
+  uint32_t* group_done_dev;        /* [groups] zero at step start (REMOTE / ALL) */
+  uint32_t* chunk_next_dev;        /* [groups + 1] zero at step start */
+  uint64_t assignments;            /* entries in all buckets together (sizes the grid) */
+  uint64_t tokens;                 /* rows of x */
+  uint64_t rows_cap;
+  uint32_t row_bytes;              /* k * 2, multiple of 16 */
   uint32_t ranks;
   uint32_t self;
   uint32_t groups;
@@ -515,10 +539,10 @@ typedef struct bmoe_ep_dispatch_args {
   void* stream;
 } bmoe_ep_dispatch_args;
 
-/* Pushes token rows into the owners' packed A, group by group; the row inside
- * (expert, source) comes from an atomic cursor, so the order of rows inside an
- * expert is arbitrary (no result row depends on it). Beside every row it leaves the
- * origin record rank << 40 | assignment that bmoe_ep_return follows. */
+/* Copies the routed token rows into the owners' packed A, bucket by bucket: REMOTE
+ * walks the exchange groups in order and raises a group's flags on all peers when the
+ * last CTA has finished it; LOCAL copies the rows that stay on this rank; ALL does
+ * both (groups first). LOCAL and REMOTE launches of a step may overlap. */
 int bmoe_ep_dispatch(const bmoe_ep_dispatch_args* args);
 
 typedef struct bmoe_ep_return_args {

@@ -205,6 +205,12 @@ def test_fused_exchange_step_tables_cover_every_owner_buffer_once(engine):
     for r in range(world):
         cursor = np.zeros(experts, dtype=np.int64)
         flat = ids_all[bounds[r]:bounds[r + 1]].reshape(-1).numpy()
+        # route entries per bucket: exchange groups of rows that leave, then rows that stay
+        sizes = np.zeros(groups + 1, dtype=np.int64)
+        for e in flat:
+            sizes[groups if owner[e] == r else steps[r]["group_of"][e]] += 1
+        assert np.array_equal(np.diff(steps[r]["bucket_offset"].astype(np.int64)), sizes)
+        assert steps[r]["bucket_offset"][-1] == flat.size
         for e in flat:
             row = steps[r]["row_base"][e] + cursor[e]
             cursor[e] += 1
@@ -213,3 +219,16 @@ def test_fused_exchange_step_tables_cover_every_owner_buffer_once(engine):
     for q in range(world):
         want = np.repeat(steps[q]["local_experts"], steps[q]["local_m"])
         assert np.array_equal(filled[q], want)
+
+
+def test_hot_experts_are_split_into_row_shards(engine):
+    from bmoe_b200 import ep
+
+    counts = [4000, 300, 300, 200, 100, 100, 0, 50]
+    parts, shard_owner, loads = ep.split_and_place_experts(counts, 4, 256, tile_m=128, tile_n=256)
+    # tiles: 32 3 3 2 1 1 0 1 -> 43, fair share 10.75, shards of at most 5 tiles
+    assert parts == [4, 1, 1, 1, 1, 1, 1, 1]       # capped at one shard per rank
+    assert len(shard_owner) == sum(parts) and sorted(set(shard_owner[:4])) == [0, 1, 2, 3]
+    assert sum(loads) == 4 * 8 + 11 and max(loads) - min(loads) <= 3
+    whole, owner, _ = ep.split_and_place_experts(counts, 1, 256)
+    assert whole == [1] * 8 and owner == [0] * 8

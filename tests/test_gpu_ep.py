@@ -188,6 +188,24 @@ def test_single_rank_fused_layer_and_gate(engine):
             assert torch.equal(y.view(torch.int16), want.view(torch.int16)), (push, opts)
         finally:
             plain.close()
+    # row shards: experts 0 and 3 are dealt to 3 and 2 shards (all on this one rank)
+    parts = [3, 1, 1, 2] + [1] * 36
+    expert_of_shard = [e for e, p in enumerate(parts) for _ in range(p)]
+    sharded = ep_fused.FusedExpertParallelLayer([0] * sum(parts), 512, 320, rank=0, world=1,
+                                                rows_cap=2400, assignments_cap=2400,
+                                                expert_parts=parts)
+    try:
+        assert sharded.local_experts == expert_of_shard
+        y = sharded.forward(x.cuda(), ids.cuda(), w[sharded.local_experts].cuda())
+        sharded.poll()
+        assert torch.equal(y.view(torch.int16), want.view(torch.int16))
+        per_shard = sharded.last_local_m
+        first = int((ids == 0).sum())
+        # dealt by assignment index: all rows accounted for, shards about equal
+        assert sum(per_shard[:3]) == first
+        assert max(per_shard[:3]) <= 1.4 * first / 3 and min(per_shard[:3]) >= 0.6 * first / 3
+    finally:
+        sharded.close()
     layer = ep_fused.FusedExpertParallelLayer([0] * 40, 512, 320, rank=0, world=1,
                                               rows_cap=2400, assignments_cap=2400)
     try:
@@ -303,9 +321,13 @@ def _ep_worker(rank, world, port, tmpdir):
         same = same and torch.equal(z.cpu().view(torch.int16), want_z.view(torch.int16))
         from bmoe_b200 import ep_fused
 
-        fused = ep_fused.FusedExpertParallelLayer(owner, 512, 320, rank=rank, world=world,
+        parts, shard_owner, _ = ep.split_and_place_experts(
+            torch.bincount(ids.reshape(-1), minlength=40).tolist(), world, 512, max_share=0.1)
+        assert max(parts) > 1                      # the Zipf head is split
+        fused = ep_fused.FusedExpertParallelLayer(shard_owner, 512, 320, rank=rank, world=world,
                                                   rows_cap=2400, assignments_cap=(hi - lo) * 4,
-                                                  exchange_groups=3, scheduler="dynamic_queue")
+                                                  exchange_groups=3, scheduler="dynamic_queue",
+                                                  expert_parts=parts)
         for i in range(4):
             y = fused.forward(x[lo:hi].cuda(), ids[lo:hi].cuda(), w[fused.local_experts].cuda(),
                               topk_weights=gates.cuda() if i == 3 else None)
