@@ -357,10 +357,7 @@ def run_single_gpu(args, spec, workload):
     sampler = ClockSampler(0)
     sampler.start()
     time.sleep(0.25)
-    torch.cuda.synchronize()
-    # per-launch samples for p50 / p99 (at least 1000 launches for the p99)
-    samples = time_policy(torch, plan, stream, max(args.steps, 1000))
-    # the timed region: exactly K steps inside one event pair
+    # the timed region: exactly K steps inside one event pair, right after the warm-up
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     launches_before = plan.stats().launches
@@ -373,10 +370,12 @@ def run_single_gpu(args, spec, workload):
     launches = plan.stats().launches - launches_before
     time.sleep(0.15)
     clocks = sampler.stop()
+    # per-launch samples for p50 / p99 (at least 1000 launches for the p99), after the region
+    samples = time_policy(torch, plan, stream, max(args.steps, 1000))
     check(plan, "timed region")
     ms_per_step = region_ms / args.steps
     value = flops / (ms_per_step * 1e-3) / 1e12
-    avg_launch_ms = sum(samples) / len(samples)
+    avg_launch_ms = region_ms / args.steps   # average launch duration over the timed region
 
     # The same launch with the per-step set-up inside the measurement: counts upload,
     # worklist kernels and TMA descriptors rebuilt before every run (routing changes per step).

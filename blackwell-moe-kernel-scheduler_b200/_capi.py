@@ -351,6 +351,11 @@ SIGNATURES = {
         [C.c_void_p, C.c_uint32, C.c_uint64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64,
          C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p],
     ),
+    "bmoe_ep_count": (
+        C.c_int,
+        [C.c_void_p, C.c_uint64, C.c_uint32, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p,
+         C.c_void_p, C.c_void_p],
+    ),
     "bmoe_ep_route": (C.c_int, [C.c_void_p]),
     "bmoe_ep_dispatch": (C.c_int, [C.c_void_p]),
     "bmoe_ep_return": (C.c_int, [C.c_void_p]),

@@ -301,6 +301,43 @@ __global__ void ep_wait_flags_kernel(const uint32_t* flags, uint32_t first_slot,
   }
 }
 
+// Routed rows per expert of this rank, and (optionally) the expert -> shard mapping of
+// split experts, in one pass: counts[id] += 1 for every valid assignment, where id is
+// the expert, or shard_base[expert] + i % parts[expert] when shards are given (the
+// shard ids are also written to ids_out). Invalid expert ids count nowhere and map to
+// -1. Shared-memory histogram per CTA, flushed with one atomic per non-empty bin.
+constexpr uint32_t kCountBins = 4096;
+
+__global__ void __launch_bounds__(256)
+ep_count_kernel(const int64_t* __restrict__ expert_ids, uint64_t assignments, uint32_t experts,
+                const int64_t* __restrict__ parts, const int64_t* __restrict__ shard_base,
+                uint32_t bins, int64_t* __restrict__ ids_out,
+                unsigned long long* __restrict__ counts) {
+  __shared__ uint32_t hist[kCountBins];
+  for (uint32_t b = threadIdx.x; b < bins; b += blockDim.x) hist[b] = 0;
+  __syncthreads();
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+  for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < assignments;
+       i += stride) {
+    const int64_t e = expert_ids[i];
+    int64_t id = -1;
+    if (e >= 0 && e < static_cast<int64_t>(experts)) {
+      id = e;
+      if (parts != nullptr) {
+        const int64_t p = parts[e];
+        id = p > 0 ? shard_base[e] + static_cast<int64_t>(i % static_cast<uint64_t>(p)) : -1;
+      }
+      if (id < 0 || id >= static_cast<int64_t>(bins)) id = -1;
+    }
+    if (ids_out != nullptr) ids_out[i] = id;
+    if (id >= 0) atomicAdd(&hist[id], 1u);
+  }
+  __syncthreads();
+  for (uint32_t b = threadIdx.x; b < bins; b += blockDim.x) {
+    if (hist[b] != 0) atomicAdd(&counts[b], static_cast<unsigned long long>(hist[b]));
+  }
+}
+
 uint32_t device_sms() {
   int device = 0, sms = 0;
   if (cudaGetDevice(&device) != cudaSuccess ||
@@ -313,6 +350,30 @@ uint32_t device_sms() {
 
 }  // namespace
 }  // namespace bmoe
+
+extern "C" int bmoe_ep_count(const int64_t* expert_ids_dev, uint64_t assignments,
+                             uint32_t experts, const int64_t* parts_dev,
+                             const int64_t* shard_base_dev, uint32_t bins, int64_t* ids_out_dev,
+                             int64_t* counts_dev, void* stream) {
+  if (counts_dev == nullptr || bins == 0 || bins > bmoe::kCountBins || experts == 0 ||
+      (assignments != 0 && expert_ids_dev == nullptr) ||
+      ((parts_dev == nullptr) != (shard_base_dev == nullptr)) ||
+      (parts_dev == nullptr && bins != experts)) {
+    return BMOE_INVALID_ARGUMENT;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(counts_dev, 0, sizeof(int64_t) * bins, s) != cudaSuccess) {
+    return BMOE_CUDA_ERROR;
+  }
+  if (assignments == 0) return BMOE_OK;
+  const uint64_t want = (assignments + 1023) / 1024;   // four assignments per thread
+  const uint64_t cap = 2ull * bmoe::device_sms();
+  const uint32_t grid = static_cast<uint32_t>(want < cap ? want : cap);
+  bmoe::ep_count_kernel<<<grid, 256, 0, s>>>(
+      expert_ids_dev, assignments, experts, parts_dev, shard_base_dev, bins, ids_out_dev,
+      reinterpret_cast<unsigned long long*>(counts_dev));
+  return cudaPeekAtLastError() == cudaSuccess ? BMOE_OK : BMOE_CUDA_ERROR;
+}
 
 extern "C" int bmoe_ep_route(const bmoe_ep_route_args* args) {
   if (args == nullptr) return BMOE_INVALID_ARGUMENT;

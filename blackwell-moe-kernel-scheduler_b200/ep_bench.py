@@ -131,6 +131,7 @@ def run(args, spec, workload):
         plain = layer if groups == 1 else ep.ExpertParallelLayer(
             owner, n, k, rank=rank, world=world,
             ops=ep.CudaOps(scheduler=args.policy, cta_group=args.cta_group))
+    exchange_sms_used = getattr(layer, "exchange_sms", 0)
     w_local = _expert_weights(torch, layer.local_experts, n, k, dev)
     total_flops = 2.0 * tokens * top_k * n * k
     stream = torch.cuda.current_stream()
@@ -255,7 +256,9 @@ def run(args, spec, workload):
                                  % (sum(p > 1 for p in parts), len(parts), sum(parts))),
                    "exchange": args.exchange,
                    "last_step": "weighted top-k sum" if gates is not None else "rows in assignment order",
-                   "pipeline_groups": groups, "comm_sms": args.comm_sms if groups > 1 else 0,
+                   "pipeline_groups": groups,
+                   "comm_sms": (exchange_sms_used if args.exchange == "fused"
+                                else args.comm_sms if groups > 1 else 0),
                    "rank_tiles": rank_tiles, "rank0_rows": local_rows,
                    "max_rank_rows": rows_max, "mean_rank_rows": tokens * top_k / world,
                    "l2": "per-rank weights exceed the 126 MB L2; no flush between steps",

@@ -349,14 +349,6 @@ class FusedExpertParallelLayer:
         top_k = int(expert_ids.shape[1])
         flat_ids = expert_ids.reshape(-1).contiguous()
         assignments = int(flat_ids.numel())
-        if self.expert_parts is not None:
-            # expert -> shard: rows of a split expert are dealt round-robin by assignment index
-            real = len(self.expert_parts)
-            valid = (flat_ids >= 0) & (flat_ids < real)
-            safe = flat_ids.clamp(0, real - 1)
-            deal = torch.arange(assignments, device=dev, dtype=torch.int64) % self._parts_dev[safe]
-            flat_ids = torch.where(valid, self._shard_base_dev[safe] + deal,
-                                   torch.full_like(flat_ids, -1))
         if assignments > self.assignments_cap:
             raise RuntimeError("more assignments than the result buffer holds")
         marks = []
@@ -368,9 +360,21 @@ class FusedExpertParallelLayer:
                 marks.append((name, ev))
 
         mark("start")
-        local_counts = torch.zeros(self.experts, dtype=torch.int64, device=dev)
-        local_counts.scatter_add_(0, flat_ids.clamp(0, self.experts - 1),
-                                  ((flat_ids >= 0) & (flat_ids < self.experts)).to(torch.int64))
+        # rows per expert (or per row shard of split experts, dealt by assignment index)
+        local_counts = torch.empty(self.experts, dtype=torch.int64, device=dev)
+        sharded = self.expert_parts is not None
+        shard_ids = torch.empty_like(flat_ids) if sharded else None
+        _capi.check(
+            self._lib.bmoe_ep_count(flat_ids.data_ptr(), assignments,
+                                    len(self.expert_parts) if sharded else self.experts,
+                                    self._parts_dev.data_ptr() if sharded else None,
+                                    self._shard_base_dev.data_ptr() if sharded else None,
+                                    self.experts, shard_ids.data_ptr() if sharded else None,
+                                    local_counts.data_ptr(), main.cuda_stream or None),
+            "bmoe_ep_count")
+        self.launches += 1
+        if sharded:
+            flat_ids = shard_ids
         if self.world > 1:
             flat = torch.empty(self.world * self.experts, dtype=torch.int64, device=dev)
             dist.all_gather_into_tensor(flat, local_counts, group=self.group)

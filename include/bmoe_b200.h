@@ -483,6 +483,17 @@ int bmoe_combine_topk(const void* const* src_bases_dev, uint32_t n_src,
 #define BMOE_EP_REMOTE 1u  /* only rows owned by other ranks; raises the group flags */
 #define BMOE_EP_ALL 2u
 
+/* Routed rows per expert of this rank in one pass over its assignments:
+ * counts_dev[id] (int64 [bins], zeroed here) += 1 for every assignment with a valid
+ * expert id in [0, experts). With parts_dev / shard_base_dev (int64 [experts], row
+ * shards of split experts) the id is shard_base[e] + i % parts[e] for assignment i and
+ * bins is the number of shards; otherwise id = e and bins = experts. ids_out_dev
+ * (int64 [assignments], may be NULL) receives the ids, -1 for dropped assignments.
+ * bins <= 4096. */
+int bmoe_ep_count(const int64_t* expert_ids_dev, uint64_t assignments, uint32_t experts,
+                  const int64_t* parts_dev, const int64_t* shard_base_dev, uint32_t bins,
+                  int64_t* ids_out_dev, int64_t* counts_dev, void* stream);
+
 typedef struct bmoe_ep_route_args {
   const int64_t* expert_ids_dev;   /* [assignments] expert of assignment i (token i / top_k);
                                       ids outside [0, experts) are dropped */

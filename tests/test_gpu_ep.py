@@ -224,6 +224,29 @@ def test_single_rank_fused_layer_and_gate(engine):
         layer.close()
 
     lib = engine._capi.load()
+    # count kernel: histogram of valid ids, and the shard dealing of split experts
+    gen = torch.Generator().manual_seed(8)
+    raw = torch.randint(-2, 9, (5000,), generator=gen)               # ids -2..8, experts = 7
+    counts = torch.empty(7, dtype=torch.int64, device="cuda")
+    assert lib.bmoe_ep_count(raw.cuda().data_ptr(), 5000, 7, None, None, 7, None,
+                             counts.data_ptr(), None) == 0
+    ok = (raw >= 0) & (raw < 7)
+    assert torch.equal(counts.cpu(), torch.bincount(raw[ok], minlength=7))
+    parts_t = torch.tensor([1, 3, 1, 2, 1, 1, 1])
+    base_t = torch.cumsum(parts_t, 0) - parts_t
+    out_ids = torch.empty(5000, dtype=torch.int64, device="cuda")
+    counts10 = torch.empty(10, dtype=torch.int64, device="cuda")
+    assert lib.bmoe_ep_count(raw.cuda().data_ptr(), 5000, 7, parts_t.cuda().data_ptr(),
+                             base_t.cuda().data_ptr(), 10, out_ids.data_ptr(),
+                             counts10.data_ptr(), None) == 0
+    safe = raw.clamp(0, 6)
+    want_ids = torch.where(ok, base_t[safe] + torch.arange(5000) % parts_t[safe],
+                           torch.full_like(raw, -1))
+    assert torch.equal(out_ids.cpu(), want_ids)
+    assert torch.equal(counts10.cpu(), torch.bincount(want_ids[ok], minlength=10))
+    assert lib.bmoe_ep_count(raw.cuda().data_ptr(), 5000, 7, None, None, 9, None,
+                             counts.data_ptr(), None) != 0            # bins must equal experts
+
     # wait kernel: rank 1 of 2 never reports -> status word, no hang
     flags = torch.zeros(64, dtype=torch.int32, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
