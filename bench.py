@@ -685,6 +685,8 @@ def main():
     ap.add_argument("--split-hot", action="store_true",
                     help="fused exchange: cut experts above half a rank's fair share of the "
                          "tiles into row shards placed on several ranks")
+    ap.add_argument("--bulk-copies", action="store_true",
+                    help="fused exchange: remote rows as TMA bulk copies through shared memory")
     ap.add_argument("--no-push", action="store_true",
                     help="fused exchange: return result rows with a kernel after the GEMM "
                          "instead of from its epilogue")

@@ -154,6 +154,7 @@ class EpDispatchArgs(C.Structure):
         ("row_bytes", C.c_uint32), ("ranks", C.c_uint32), ("self", C.c_uint32),
         ("groups", C.c_uint32), ("mode", C.c_uint32), ("epoch", C.c_uint32),
         ("max_ctas", C.c_uint32), ("block_threads", C.c_uint32), ("cluster", C.c_uint32),
+        ("bulk_copies", C.c_uint32), ("status_dev", C.c_void_p),
         ("stream", C.c_void_p),
     ]
 

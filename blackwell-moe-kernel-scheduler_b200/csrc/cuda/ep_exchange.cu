@@ -30,6 +30,7 @@
 #include <cstdint>
 
 #include "bmoe_b200.h"
+#include "ptx_sm100.cuh"
 
 namespace bmoe {
 namespace {
@@ -197,6 +198,8 @@ struct DispatchArgs {
   uint32_t mode;               // BMOE_EP_LOCAL / BMOE_EP_REMOTE / BMOE_EP_ALL
   uint32_t epoch;
   uint32_t span;               // entries per claim: 1..32
+  uint32_t row_bytes;
+  uint32_t* status;            // optional: set when a bulk-copy wait ran out
 };
 
 // Bucket by bucket (exchange groups in order, then - or only - the local bucket), a
@@ -236,6 +239,93 @@ __global__ void __launch_bounds__(1024) ep_dispatch_kernel(DispatchArgs a) {
                  a.a_bases[to] + static_cast<uint64_t>(row) * a.vec_per_row, a.vec_per_row, lane);
       }
     }
+    if (b < a.groups && a.ranks > 1) {
+      signal_peers_when_grid_done(&a.group_done[b], a.flag_bases, a.ranks, a.self,
+                                  b * a.ranks + a.self, a.epoch);
+    }
+  }
+}
+
+// Same walk as ep_dispatch_kernel, but the rows travel through the TMA engine: every
+// warp owns one row-sized stage in shared memory; its first lane loads a token row with
+// one bulk copy (global -> shared, counted on an mbarrier) and sends it on with one bulk
+// copy (shared -> peer memory). No load/store unit of the SM waits for NVLink. Needs
+// SMs of its own (the stages take most of the shared memory). Waits are bounded; a wait
+// that runs out sets *status and the warp stops copying (the flags are still raised so
+// that no other rank is left waiting for them; the status word tells the host).
+constexpr uint32_t kBulkMaxWarps = 16;   // stages per CTA: as many rows as fit in shared memory
+
+__global__ void __launch_bounds__(kBulkMaxWarps * 32) ep_dispatch_bulk_kernel(DispatchArgs a) {
+  extern __shared__ __align__(128) uint8_t bulk_smem[];
+  const uint32_t lane = threadIdx.x & 31;
+  const uint32_t warp = threadIdx.x >> 5;
+  const uint32_t stage_bytes = (a.row_bytes + 127u) & ~127u;
+  const uint32_t smem0 = ptx::smem_addr(bulk_smem);
+  const uint32_t warps = blockDim.x >> 5;
+  const uint32_t stage = smem0 + warp * stage_bytes;
+  const uint32_t bar = smem0 + warps * stage_bytes + warp * 8;
+  volatile uint32_t* const abort_word = reinterpret_cast<volatile uint32_t*>(
+      bulk_smem + warps * stage_bytes + warps * 8 + warp * 4);
+  if (lane == 0) {
+    ptx::mbar_init(bar, 1);
+    *abort_word = 0;
+    ptx::fence_barrier_init();
+  }
+  __syncwarp();
+  uint32_t parity = 0;
+  bool alive = true;
+  const uint32_t span = a.span;
+  const uint32_t first_bucket = a.mode == BMOE_EP_LOCAL ? a.groups : 0u;
+  const uint32_t end_bucket = a.mode == BMOE_EP_REMOTE ? a.groups : a.groups + 1u;
+  const uint8_t* const x = reinterpret_cast<const uint8_t*>(a.x);
+  for (uint32_t b = first_bucket; b < end_bucket; ++b) {
+    const uint32_t begin = a.bucket_offset[b];
+    const uint32_t count = a.bucket_offset[b + 1] - begin;
+    while (alive) {
+      uint32_t at = 0;
+      if (lane == 0) at = atomicAdd(&a.chunk_next[b], span);
+      at = __shfl_sync(0xffffffffu, at, 0);
+      if (at >= count) break;
+      RouteEntry entry{};
+      bool have = false;
+      if (lane < span && at + lane < count) {
+        entry = a.entries[begin + at + lane];
+        have = entry.to < a.ranks && entry.row < a.rows_cap && entry.token < a.tokens;
+      }
+      uint32_t todo = __ballot_sync(0xffffffffu, have);
+      while (todo != 0 && alive) {
+        const uint32_t l = __ffs(todo) - 1;
+        todo &= todo - 1;
+        const uint32_t token = __shfl_sync(0xffffffffu, entry.token, l);
+        const uint32_t to = __shfl_sync(0xffffffffu, entry.to, l);
+        const uint32_t row = __shfl_sync(0xffffffffu, entry.row, l);
+        if (lane == 0) {
+          ptx::tma_store_wait_read<0>();   // the previous row has left the stage
+          ptx::mbar_arrive_expect_tx(bar, a.row_bytes);
+          ptx::bulk_load_1d(stage, x + static_cast<uint64_t>(token) * a.row_bytes, a.row_bytes, bar);
+          if (ptx::mbar_wait(bar, parity, abort_word, 1000000000ull)) {
+            ptx::bulk_store_1d(reinterpret_cast<uint8_t*>(a.a_bases[to]) +
+                                   static_cast<uint64_t>(row) * a.row_bytes,
+                               stage, a.row_bytes);
+            ptx::tma_store_commit();
+          } else if (a.status != nullptr) {
+            atomicCAS(a.status, 0u, 0x40000000u | b);
+          }
+        }
+        parity ^= 1u;
+        alive = __shfl_sync(0xffffffffu, *abort_word == 0 ? 1u : 0u, 0) != 0;
+      }
+    }
+    if (lane == 0) {
+      ptx::tma_store_wait_all();  // this warp's rows of the bucket have landed
+      ptx::fence_proxy_async_all();
+      if (!alive) {
+        // a load that was given up on may still be writing the stage: let it land
+        const uint64_t t0 = timer_ns();
+        while (timer_ns() - t0 < 200000) __nanosleep(1000);
+      }
+    }
+    __syncwarp();
     if (b < a.groups && a.ranks > 1) {
       signal_peers_when_grid_done(&a.group_done[b], a.flag_bases, a.ranks, a.self,
                                   b * a.ranks + a.self, a.epoch);
@@ -479,6 +569,32 @@ extern "C" int bmoe_ep_dispatch(const bmoe_ep_dispatch_args* args) {
     config.numAttrs = 1;
   }
   config.gridDim = dim3(grid, 1, 1);
+  a.row_bytes = c.row_bytes;
+  a.status = c.status_dev;
+  if (c.bulk_copies != 0) {
+    // one row-sized stage per warp, as many warps as fit (the bytes in flight per SM
+    // bound its push rate: a row stays in its stage until NVLink has taken it)
+    const uint32_t stage_bytes = (c.row_bytes + 127u) & ~127u;
+    uint32_t bulk_warps = (220u * 1024u - 128u) / (stage_bytes + 12u);
+    if (bulk_warps > bmoe::kBulkMaxWarps) bulk_warps = bmoe::kBulkMaxWarps;
+    if (bulk_warps < 2) return BMOE_INVALID_ARGUMENT;
+    const uint32_t smem = bulk_warps * stage_bytes + bulk_warps * 12 + 128;
+    static bool attribute_set = false;
+    if (!attribute_set) {
+      if (cudaFuncSetAttribute(bmoe::ep_dispatch_bulk_kernel,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               220 * 1024) != cudaSuccess) {
+        return BMOE_CUDA_ERROR;
+      }
+      attribute_set = true;
+    }
+    config.blockDim = dim3(bulk_warps * 32, 1, 1);
+    config.dynamicSmemBytes = smem;
+    if (cudaLaunchKernelEx(&config, bmoe::ep_dispatch_bulk_kernel, a) != cudaSuccess) {
+      return BMOE_CUDA_ERROR;
+    }
+    return cudaPeekAtLastError() == cudaSuccess ? BMOE_OK : BMOE_CUDA_ERROR;
+  }
   if (cudaLaunchKernelEx(&config, bmoe::ep_dispatch_kernel, a) != cudaSuccess) {
     return BMOE_CUDA_ERROR;
   }

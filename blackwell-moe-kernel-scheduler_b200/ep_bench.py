@@ -109,7 +109,8 @@ def run(args, spec, workload):
             assignments_cap=(hi - lo) * top_k, scheduler=args.policy,
             exchange_groups=ep_groups, cta_group=args.cta_group,
             dispatch_ctas=args.dispatch_ctas, push_results=not args.no_push,
-            exchange_sms=args.exchange_sms, expert_parts=parts)
+            exchange_sms=args.exchange_sms, expert_parts=parts,
+            bulk_copies=args.bulk_copies)
         ops = layer
         plain = layer
         groups = layer.groups

@@ -179,7 +179,8 @@ class FusedExpertParallelLayer:
                  rows_cap: int, assignments_cap: int, group=None, scheduler="dynamic_queue",
                  exchange_groups: int = 4, dispatch_ctas: int = 0, wait_budget_ns: int = 0,
                  push_results: bool = True, exchange_sms: int = 16,
-                 expert_parts: Sequence[int] | None = None, **plan_options):
+                 expert_parts: Sequence[int] | None = None, bulk_copies: bool = False,
+                 **plan_options):
         """``rows_cap``: packed rows this rank can own; ``assignments_cap``: local
         assignments (tokens x top_k) per step; ``exchange_groups``: groups the
         experts of a rank are split into for the overlap (1 = no overlap).
@@ -231,6 +232,8 @@ class FusedExpertParallelLayer:
             self.plan_options["cta_group"] = 2 if pair else 1
             self.plan_options["cta_count"] = max(1, (sms - self.exchange_sms) // (2 if pair else 1))
         self.push_results = bool(push_results)
+        # remote rows as TMA bulk copies through shared-memory stages (needs exchange_sms)
+        self.bulk_copies = bool(bulk_copies)
         self.tile_m = 128 if plan_options.get("cta_group") == 1 else 256
         self.plan = GroupedGemmPlan()
         self._planner = StepPlanner(self.owner, rank, world, self.groups, self.tile_m)
@@ -318,6 +321,8 @@ class FusedExpertParallelLayer:
             max_ctas=(self.exchange_sms or self.dispatch_ctas) if remote else 0,
             block_threads=1024 if (remote and self.exchange_sms) else 256,
             cluster=2 if (remote and self.exchange_sms) else 0,
+            bulk_copies=1 if (remote and self.exchange_sms and self.bulk_copies) else 0,
+            status_dev=self._wait_status.data_ptr(),
             stream=stream.cuda_stream or None)
         _capi.check(self._lib.bmoe_ep_dispatch(C.byref(args)), "bmoe_ep_dispatch")
         self.launches += 1
@@ -491,6 +496,9 @@ class FusedExpertParallelLayer:
                 status, f"grouped GEMM (site {report.code}, cta {report.cta}, "
                         f"group {report.stage}, rank {report.aux})")
         word = int(self._wait_status.item()) & 0xffffffff
+        if word & 0x40000000:
+            raise _capi.EngineError(_capi.DEVICE_TIMEOUT,
+                                    f"a bulk copy of exchange group {word & 0xff} did not complete")
         if word:
             raise _capi.EngineError(
                 _capi.DEVICE_TIMEOUT,

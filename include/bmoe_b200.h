@@ -547,6 +547,10 @@ typedef struct bmoe_ep_dispatch_args {
   uint32_t max_ctas;               /* 0 = default: 4 per SM for LOCAL, 7/16 of the SMs otherwise */
   uint32_t block_threads;          /* 0 = 256; 256, 512 or 1024 */
   uint32_t cluster;                /* 2 = launch the CTAs as pairs that fill whole SM pairs */
+  uint32_t bulk_copies;            /* 1 = rows travel as TMA bulk copies through shared-memory
+                                      stages (one row per warp, as many warps as fit in 220 KB,
+                                      at most 16): for CTAs on SMs of their own */
+  uint32_t* status_dev;            /* optional: 0x40000000 | bucket if a bulk-copy wait ran out */
   void* stream;
 } bmoe_ep_dispatch_args;
 

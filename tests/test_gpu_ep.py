@@ -363,7 +363,7 @@ def _ep_worker(rank, world, port, tmpdir):
         kept = ep_fused.FusedExpertParallelLayer(owner, 512, 320, rank=rank, world=world,
                                                  rows_cap=2400, assignments_cap=(hi - lo) * 4,
                                                  exchange_groups=2, push_results=False,
-                                                 cta_group=1)
+                                                 cta_group=1, bulk_copies=True)
         for _ in range(2):
             y = kept.forward(x[lo:hi].cuda(), ids[lo:hi].cuda(), w[kept.local_experts].cuda())
         kept.poll()
