@@ -1,6 +1,6 @@
 """Generates tests/golden/reference_vectors.json from the REFERENCE itself.
 
-Run where the reference checkout is present (default /root/reference):
+Run where the reference checkout is present (its location: BMOE_REFERENCE_ROOT):
     python tests/golden/make_golden.py
 Sources of truth:
   * the reference's compiled host scheduler (oracle/_ref/libref_sched.so, built
