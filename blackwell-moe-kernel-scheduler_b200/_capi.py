@@ -373,6 +373,7 @@ SIGNATURES = {
     "bmoe_peer_open": (C.c_int, [C.c_void_p, _P(C.c_void_p)]),
     "bmoe_peer_close": (C.c_int, [C.c_void_p]),
     "bmoe_peer_free": (C.c_int, [C.c_void_p]),
+    "bmoe_preload_kernels": (C.c_int, []),
     "bmoe_build_info": (C.c_char_p, []),
 }
 

@@ -30,6 +30,7 @@
 #include <cstdint>
 
 #include "bmoe_b200.h"
+#include "preload.cuh"
 #include "ptx_sm100.cuh"
 
 namespace bmoe {
@@ -642,3 +643,15 @@ extern "C" int bmoe_ep_wait_flags(const uint32_t* flags_dev, uint32_t first_slot
       flags_dev, first_slot, ranks, self, epoch, budget_ns, status_dev);
   return cudaPeekAtLastError() == cudaSuccess ? BMOE_OK : BMOE_CUDA_ERROR;
 }
+
+namespace bmoe {
+cudaError_t preload_exchange_kernels() {
+  cudaError_t rc = preload_one(ep_count_kernel);
+  if (rc == cudaSuccess) rc = preload_one(ep_route_kernel);
+  if (rc == cudaSuccess) rc = preload_one(ep_dispatch_kernel);
+  if (rc == cudaSuccess) rc = preload_one(ep_dispatch_bulk_kernel);
+  if (rc == cudaSuccess) rc = preload_one(ep_return_kernel);
+  if (rc == cudaSuccess) rc = preload_one(ep_wait_flags_kernel);
+  return rc;
+}
+}  // namespace bmoe

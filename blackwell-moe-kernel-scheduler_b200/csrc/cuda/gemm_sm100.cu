@@ -22,6 +22,7 @@
 // (python/blackwell_moe_tirx/kernels/v1_static_ws.py:94-343 static,
 // atomic_ws.py:69-271 queue, v5_clc.py:59-263 launch control).
 #include "gemm_sm100.cuh"
+#include "preload.cuh"
 
 #include <cuda_runtime.h>
 
@@ -774,6 +775,15 @@ uint32_t gemm_smem_bytes(uint32_t tile_n, uint32_t cta_group) {
 uint32_t gemm_stage_count(uint32_t tile_n, uint32_t cta_group) {
   if (cta_group == 2) return Config<256, true>::kStages;
   return tile_n == 256 ? Config<256, false>::kStages : Config<128, false>::kStages;
+}
+
+cudaError_t preload_gemm_kernels() {
+  cudaError_t rc = preload_one(grouped_gemm_kernel<256, true, false>);
+  if (rc == cudaSuccess) rc = preload_one(grouped_gemm_kernel<256, false, false>);
+  if (rc == cudaSuccess) rc = preload_one(grouped_gemm_kernel<128, false, false>);
+  if (rc == cudaSuccess) rc = preload_one(grouped_gemm_kernel<256, true, true>);
+  if (rc == cudaSuccess) rc = preload_one(grouped_gemm_kernel<256, false, true>);
+  return rc;
 }
 
 cudaError_t launch_grouped_gemm(const GemmParams& params, uint32_t tile_n,

@@ -10,6 +10,7 @@
 #include <cstring>
 
 #include "bmoe_b200.h"
+#include "preload.cuh"
 
 namespace bmoe {
 namespace {
@@ -372,3 +373,14 @@ extern "C" int bmoe_peer_free(void* ptr) {
   if (ptr == nullptr) return BMOE_OK;
   return cudaFree(ptr) == cudaSuccess ? BMOE_OK : BMOE_CUDA_ERROR;
 }
+
+namespace bmoe {
+cudaError_t preload_permute_kernels() {
+  cudaError_t rc = preload_one(gather_rows_kernel);
+  if (rc == cudaSuccess) rc = preload_one(route_rows_kernel);
+  if (rc == cudaSuccess) rc = preload_one(combine_topk_kernel<1>);
+  if (rc == cudaSuccess) rc = preload_one(combine_topk_kernel<2>);
+  if (rc == cudaSuccess) rc = preload_one(combine_topk_kernel<4>);
+  return rc;
+}
+}  // namespace bmoe

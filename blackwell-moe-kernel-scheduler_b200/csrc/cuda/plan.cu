@@ -20,6 +20,7 @@
 #include "blackwell_moe/dispatch.hpp"
 #include "bmoe_b200.h"
 #include "gemm_sm100.cuh"
+#include "preload.cuh"
 
 namespace {
 
@@ -429,6 +430,15 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
   plan->stats.sm_count = static_cast<uint32_t>(sm_count);
   plan->ready = true;
   return BMOE_OK;
+}
+
+int bmoe_preload_kernels(void) {
+  cudaError_t rc = bmoe::preload_gemm_kernels();
+  if (rc == cudaSuccess) rc = bmoe::preload_worklist_kernels();
+  if (rc == cudaSuccess) rc = bmoe::preload_permute_kernels();
+  if (rc == cudaSuccess) rc = bmoe::preload_exchange_kernels();
+  if (rc == cudaSuccess) rc = bmoe::preload_probe_kernels();
+  return rc == cudaSuccess ? BMOE_OK : BMOE_CUDA_ERROR;
 }
 
 int bmoe_plan_set_gate(bmoe_plan* plan, const uint32_t* flags_dev, uint32_t epoch,

@@ -13,6 +13,7 @@
 
 #include "blackwell_moe/scheduler/dynamic_queue.cuh"
 #include "bmoe_b200.h"
+#include "preload.cuh"
 
 namespace bmoe {
 
@@ -138,3 +139,11 @@ const char* bmoe_probe_scheduler_name(uint32_t scheduler) {
 }
 
 }  // extern "C"
+
+namespace bmoe {
+cudaError_t preload_probe_kernels() {
+  cudaError_t rc = preload_one(probe_static_kernel);
+  if (rc == cudaSuccess) rc = preload_one(probe_queue_kernel);
+  return rc;
+}
+}  // namespace bmoe

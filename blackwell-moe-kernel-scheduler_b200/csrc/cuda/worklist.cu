@@ -19,6 +19,7 @@
 #include <cstdint>
 
 #include "bmoe_b200.h"
+#include "preload.cuh"
 
 namespace bmoe {
 
@@ -338,3 +339,11 @@ extern "C" int bmoe_worklist_build_static(const uint32_t* counts_dev,
   }
   return BMOE_OK;
 }
+
+namespace bmoe {
+cudaError_t preload_worklist_kernels() {
+  cudaError_t rc = preload_one(worklist_plan_kernel);
+  if (rc == cudaSuccess) rc = preload_one(worklist_expand_kernel);
+  return rc;
+}
+}  // namespace bmoe

@@ -242,6 +242,9 @@ class FusedExpertParallelLayer:
         dev = torch.device("cuda", torch.cuda.current_device())
         self.dev = dev
         flag_slots = (_capi.EP_MAX_GROUPS + 1) * world
+        # every rank loads its kernels before the first step: the step's bounded waits
+        # assume that all ranks launch within the wait budget
+        _capi.check(self._lib.bmoe_preload_kernels(), "bmoe_preload_kernels")
         self.shared = SharedBuffers(
             {"a": self.rows_cap * k * 2, "d": self.rows_cap * n * 2, "origin": self.rows_cap * 8,
              "y": self.assignments_cap * n * 2, "flags": flag_slots * 4},
@@ -472,7 +475,10 @@ class FusedExpertParallelLayer:
         mark("return")
         y = self.y[:assignments]
         if topk_weights is not None:
-            rows = torch.arange(assignments, device=dev, dtype=torch.int64).reshape(-1, top_k)
+            # dropped assignments (expert id out of range) have no result row: skip them
+            rows = torch.arange(assignments, device=dev, dtype=torch.int64)
+            rows = torch.where((flat_ids >= 0) & (flat_ids < self.experts), rows,
+                               torch.full_like(rows, -1)).reshape(-1, top_k)
             out = torch.empty(assignments // top_k, self.n, dtype=x.dtype, device=dev)
             weights = topk_weights.to(torch.float32).contiguous()
             _capi.check(

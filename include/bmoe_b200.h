@@ -619,6 +619,12 @@ int bmoe_peer_open(const uint8_t* handle, void** ptr_out);
 int bmoe_peer_close(void* ptr);
 int bmoe_peer_free(void* ptr);
 
+/* Loads every kernel of the library on the current device now (CUDA loads a kernel's
+ * module lazily at its first launch otherwise, which can take tens of milliseconds).
+ * Call it before latency-critical work and before the first multi-GPU step, whose
+ * bounded waits assume that all ranks launch within the wait budget. */
+int bmoe_preload_kernels(void);
+
 /* Library build information ("sm_100a", CUDA runtime version, ...). */
 const char* bmoe_build_info(void);
 

@@ -220,10 +220,25 @@ def test_single_rank_fused_layer_and_gate(engine):
         z = layer.forward(x.cuda(), ids.cuda(), w.cuda(), topk_weights=gates.cuda())
         assert torch.equal(z.cpu().view(torch.int16),
                            oracle_combine(want, gates, 4).view(torch.int16))
+        # dropped assignments (expert id -1 or out of range) take part in nothing
+        dropped = ids.clone()
+        dropped[5, 1] = -1
+        dropped[17, :] = 40
+        z = layer.forward(x.cuda(), dropped.cuda(), w.cuda(), topk_weights=gates.cuda())
+        layer.poll()
+        import support
+        rows = np.arange(2400, dtype=np.int64).reshape(-1, 4)
+        rows[5, 1] = -1
+        rows[17, :] = -1
+        want_bits = support.Oracle().combine_topk(
+            want.cpu().contiguous().view(torch.int16).numpy().view(np.uint16), rows, gates.numpy())
+        assert np.array_equal(z.cpu().view(torch.int16).numpy().view(np.uint16), want_bits)
+        assert sum(layer.last_local_m) == 2400 - 5
     finally:
         layer.close()
 
     lib = engine._capi.load()
+    assert lib.bmoe_preload_kernels() == 0
     # count kernel: histogram of valid ids, and the shard dealing of split experts
     gen = torch.Generator().manual_seed(8)
     raw = torch.randint(-2, 9, (5000,), generator=gen)               # ids -2..8, experts = 7
