@@ -145,9 +145,12 @@ class ClockSampler:
                     reasons.add(name)
         os.unlink(self.path)
         if clocks:
-            clocks.sort()
-            out["sm_mhz"] = clocks[len(clocks) // 2]
+            # median over the samples taken under load (the sampler also runs through the
+            # short idle gaps around the timed region): power within 60 % of the maximum
+            busy = sorted(c for c, w in zip(clocks, power) if w >= 0.6 * max(power))
+            out["sm_mhz"] = busy[len(busy) // 2]
             out["samples"] = len(clocks)
+            out["samples_under_load"] = len(busy)
             out["power_w_max"] = max(power)
         out["reasons"] = sorted(reasons)
         return out
