@@ -99,6 +99,24 @@ KernelStatus Bf16GroupedGemmPlan::poll() {
   return static_cast<KernelStatus>(bmoe_plan_poll(impl_->handle, nullptr));
 }
 
+KernelStatus Bf16GroupedGemmPlan::set_exchange_gate(const std::uint32_t* flags,
+                                                    std::uint32_t epoch, std::uint32_t ranks,
+                                                    std::uint32_t self,
+                                                    const std::uint8_t* group_of_expert) {
+  if (impl_ == nullptr || impl_->handle == nullptr) return KernelStatus::kInvalidArgument;
+  return static_cast<KernelStatus>(
+      bmoe_plan_set_gate(impl_->handle, flags, epoch, ranks, self, group_of_expert));
+}
+
+KernelStatus Bf16GroupedGemmPlan::set_result_push(const void* origin,
+                                                  const std::uint32_t* expert_first_row,
+                                                  void* const* y_bases, std::uint32_t ranks,
+                                                  std::uint64_t y_rows_cap) {
+  if (impl_ == nullptr || impl_->handle == nullptr) return KernelStatus::kInvalidArgument;
+  return static_cast<KernelStatus>(
+      bmoe_plan_set_push(impl_->handle, origin, expert_first_row, y_bases, ranks, y_rows_cap));
+}
+
 void* Bf16GroupedGemmPlan::native_handle() const {
   return impl_ == nullptr ? nullptr : impl_->handle;
 }

@@ -104,6 +104,20 @@ class Bf16GroupedGemmPlan {
   KernelStatus poll();
   // Extension: the underlying C handle (bmoe_plan*), for mixed C/C++ callers.
   void* native_handle() const;
+  // Extensions for the expert-parallel exchange (no counterpart in the reference).
+  // Both apply to the next run() calls and are cleared by initialize().
+  // Gate: a tile of expert e is scheduled only after the flag slots
+  // group_of_expert[e] * ranks + r (r != self) have reached `epoch`; a null
+  // `flags` removes the gate. All pointers are device pointers.
+  KernelStatus set_exchange_gate(const std::uint32_t* flags, std::uint32_t epoch,
+                                 std::uint32_t ranks, std::uint32_t self,
+                                 const std::uint8_t* group_of_expert);
+  // Push: result rows go to row `assignment` of y_bases[rank] following the
+  // origin record (rank << 40 | assignment) of each packed row instead of D;
+  // a null `origin` switches back to D.
+  KernelStatus set_result_push(const void* origin, const std::uint32_t* expert_first_row,
+                               void* const* y_bases, std::uint32_t ranks,
+                               std::uint64_t y_rows_cap);
 
  private:
   struct Impl;
