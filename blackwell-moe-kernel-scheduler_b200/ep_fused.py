@@ -381,6 +381,7 @@ class FusedExpertParallelLayer:
                                     local_counts.data_ptr(), main.cuda_stream or None),
             "bmoe_ep_count")
         self.launches += 1
+        self._scratch.zero_()          # cursors and counters of the step; before the host waits
         if sharded:
             flat_ids = shard_ids
         if self.world > 1:
@@ -403,7 +404,6 @@ class FusedExpertParallelLayer:
         buckets = step["bucket_offset"]
         stage[self._off_buckets:self._off_buckets + 4 * len(buckets)].view(np.uint32)[:] = buckets
         self._tables.copy_(self._stage, non_blocking=True)
-        self._scratch.zero_()
         self.epoch += 1
         routes = None
         if record_routes:
