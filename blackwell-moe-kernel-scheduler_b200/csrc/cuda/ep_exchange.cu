@@ -580,14 +580,11 @@ extern "C" int bmoe_ep_dispatch(const bmoe_ep_dispatch_args* args) {
     if (bulk_warps > bmoe::kBulkMaxWarps) bulk_warps = bmoe::kBulkMaxWarps;
     if (bulk_warps < 2) return BMOE_INVALID_ARGUMENT;
     const uint32_t smem = bulk_warps * stage_bytes + bulk_warps * 12 + 128;
-    static bool attribute_set = false;
-    if (!attribute_set) {
-      if (cudaFuncSetAttribute(bmoe::ep_dispatch_bulk_kernel,
-                               cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               220 * 1024) != cudaSuccess) {
-        return BMOE_CUDA_ERROR;
-      }
-      attribute_set = true;
+    // per device, and cheap: set on every launch
+    if (cudaFuncSetAttribute(bmoe::ep_dispatch_bulk_kernel,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             220 * 1024) != cudaSuccess) {
+      return BMOE_CUDA_ERROR;
     }
     config.blockDim = dim3(bulk_warps * 32, 1, 1);
     config.dynamicSmemBytes = smem;
