@@ -99,7 +99,7 @@ def measured_peaks():
 class ClockSampler:
     """nvidia-smi clock / throttle-reason samples during the timed region."""
 
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -107,6 +107,21 @@ class ClockSampler:
         self.device_index = device_index
         self.proc = None
         self.path = None
+        self.window = None   # (start, end) wall-clock seconds of the timed region
+
+    def mark_region(self, start: float, end: float):
+        """Host wall-clock bounds of the timed region: the median clock is taken over the
+        samples inside it (the sampler also runs through the idle gaps around it)."""
+        self.window = (start, end)
+
+    @staticmethod
+    def _seconds(stamp: str):
+        import datetime
+
+        try:
+            return datetime.datetime.strptime(stamp, "%Y/%m/%d %H:%M:%S.%f").timestamp()
+        except ValueError:
+            return None
 
     def start(self):
         try:
@@ -128,7 +143,7 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        clocks, reasons, power = [], set(), []
+        clocks, reasons, power, stamps = [], set(), [], []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in Path(self.path).read_text().splitlines():
             parts = [x.strip() for x in line.split(",")]
@@ -138,6 +153,7 @@ class ClockSampler:
                 clocks.append(float(parts[1]))
                 out["sm_max_mhz"] = float(parts[2])
                 power.append(float(parts[3]))
+                stamps.append(self._seconds(parts[0]))
             except ValueError:
                 continue
             for name, flag in zip(names, parts[5:9]):
@@ -145,9 +161,14 @@ class ClockSampler:
                     reasons.add(name)
         os.unlink(self.path)
         if clocks:
-            # median over the samples taken under load (the sampler also runs through the
-            # short idle gaps around the timed region): power within 60 % of the maximum
-            busy = sorted(c for c, w in zip(clocks, power) if w >= 0.6 * max(power))
+            # median over the samples taken inside the timed region (the sampler also runs
+            # through the short idle gaps around it); all samples if none fall inside
+            busy = []
+            if self.window is not None:
+                lo, hi = self.window
+                busy = sorted(c for c, t in zip(clocks, stamps) if t is not None and lo <= t <= hi)
+            if not busy:
+                busy = sorted(clocks)
             out["sm_mhz"] = busy[len(busy) // 2]
             out["samples"] = len(clocks)
             out["samples_under_load"] = len(busy)
@@ -364,11 +385,13 @@ def run_single_gpu(args, spec, workload):
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     launches_before = plan.stats().launches
+    wall0 = time.time()
     t0.record(stream)
     for _ in range(args.steps):
         plan.run(stream)
     t1.record(stream)
     torch.cuda.synchronize()
+    sampler.mark_region(wall0, time.time())
     region_ms = t0.elapsed_time(t1)
     launches = plan.stats().launches - launches_before
     time.sleep(0.15)

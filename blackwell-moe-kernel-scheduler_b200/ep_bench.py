@@ -149,11 +149,13 @@ def run(args, spec, workload):
     launches_before = ops.launches
     barrier()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    wall0 = time.time()
     t0.record(stream)
     for _ in range(args.steps):
         layer.forward(x_local, ids_local, w_local, **extra)
     t1.record(stream)
     barrier()
+    sampler.mark_region(wall0, time.time())
     ms_per_step = max_over_ranks(t0.elapsed_time(t1) / args.steps)
     launches = ops.launches - launches_before
     clocks = sampler.stop() if rank == 0 else None
