@@ -396,8 +396,15 @@ def run_single_gpu(args, spec, workload):
     launches = plan.stats().launches - launches_before
     time.sleep(0.15)
     clocks = sampler.stop()
-    # per-launch samples for p50 / p99 (at least 1000 launches for the p99), after the region
+    # per-launch samples for p50 / p99 (at least 1000 launches for the p99), after the region;
+    # clocks sampled again: this loop is long enough for the power cap to settle, and
+    # nvidia-smi's clock reading lags behind a 0.15 s region
+    loop_sampler = ClockSampler(0)
+    loop_sampler.start()
+    wall1 = time.time()
     samples = time_policy(torch, plan, stream, max(args.steps, 1000))
+    loop_sampler.mark_region(wall1 + 0.5 * (time.time() - wall1), time.time())
+    clocks_sustained = loop_sampler.stop()
     check(plan, "timed region")
     ms_per_step = region_ms / args.steps
     value = flops / (ms_per_step * 1e-3) / 1e12
@@ -574,6 +581,7 @@ def run_single_gpu(args, spec, workload):
         "p99_us_with_replan": percentile(replan_ms, 0.99) * 1e3,
         "policies": policies, "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
         "gpu_launches": launches, "clocks": clocks,
+        "clocks_sustained_loop": clocks_sustained,
     }
     plan.close()
     if e2e_plan is not None:
