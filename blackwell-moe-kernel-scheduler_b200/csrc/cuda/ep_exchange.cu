@@ -11,9 +11,11 @@
 //      until the flags of all other sources for that group have arrived
 //      (GemmParams::gate_*), so the math on early groups overlaps the transfer of
 //      late ones;
-//   3. pushes the result rows back to the rank each row came from
-//      (ep_return_kernel, which follows the per-row origin record the dispatcher
-//      left beside the row) and raises a "done" flag on every peer;
+//   3. sends the result rows back to the rank each row came from, following the
+//      per-row origin record the route kernel left beside the row: by default from
+//      the epilogue of the GEMM itself (GemmParams::push_*), with ep_return_kernel
+//      only raising the "done" flag on every peer afterwards; or, with D kept local,
+//      by ep_return_kernel copying the rows after the GEMM;
 //   4. waits for the other ranks' "done" flags (ep_wait_flags_kernel).
 //
 // Kernels of one GPU never wait on one another: rows whose owner is the sending
