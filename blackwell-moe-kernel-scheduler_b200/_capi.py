@@ -50,7 +50,8 @@ ORDER_SORTED_BY_WORK = 1
 RASTER_N_FASTEST = 0
 RASTER_M_FASTEST = 1
 
-DISTRIBUTIONS = {"uniform": 0, "heavy_hitter": 1, "heavy": 1, "sparse": 2, "zipf": 3}
+DISTRIBUTIONS = {"uniform": 0, "heavy_hitter": 1, "heavy": 1, "sparse": 2, "zipf": 3,
+                 "heavy_sparse": 4}
 
 VARIANT_NAMES = (
     "v0_nonpersistent",

@@ -19,7 +19,7 @@ def build_parser() -> argparse.ArgumentParser:
     parser = argparse.ArgumentParser(
         description="Check and benchmark a launch variant of the sm_100a grouped-GEMM kernel")
     parser.add_argument("--kernel", choices=("auto", *list_versions()), default="v1_static_ws")
-    parser.add_argument("--distribution", choices=("uniform", "heavy_hitter", "sparse", "zipf"),
+    parser.add_argument("--distribution", choices=("uniform", "heavy_hitter", "sparse", "zipf", "heavy_sparse"),
                         default="uniform")
     parser.add_argument("--experts", type=int, default=64)
     parser.add_argument("--tokens", type=int, default=4096)

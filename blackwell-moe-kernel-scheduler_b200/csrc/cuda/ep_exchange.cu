@@ -167,10 +167,20 @@ __global__ void __launch_bounds__(256) ep_route_kernel(RouteArgs a) {
     first_slot = __shfl_sync(0xffffffffu, first_slot, lead_b);
     if (!live) continue;
     const int64_t row = a.row_base[e] + first_pos + __popc(same_e & lanes_below);
-    // A bad table must never become a stray access to another GPU's memory.
-    if (row < 0 || static_cast<uint64_t>(row) >= a.rows_cap) continue;
     const uint32_t slot = a.bucket_offset[bucket] + first_slot + __popc(same_b & lanes_below);
     if (slot >= a.bucket_offset[bucket + 1] || slot >= a.assignments) continue;
+    // A bad table must never become a stray access to another GPU's memory: the slot
+    // this assignment reserved gets an entry no rank owns (the copy kernels skip it)
+    // instead of keeping whatever an earlier step left there.
+    if (row < 0 || static_cast<uint64_t>(row) >= a.rows_cap) {
+      RouteEntry none;
+      none.token = 0xffffffffu;
+      none.to = 0xffffffffu;
+      none.row = 0xffffffffu;
+      none.pad = 0;
+      a.entries[slot] = none;
+      continue;
+    }
     a.origin_bases[to][row] =
         static_cast<long long>((static_cast<uint64_t>(a.self) << kOriginRankShift) | i);
     RouteEntry entry;

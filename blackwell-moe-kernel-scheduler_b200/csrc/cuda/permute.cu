@@ -49,7 +49,8 @@ extern "C" int bmoe_gather_rows(const void* src_dev, void* dst_dev,
     return BMOE_INVALID_ARGUMENT;
   }
   const uint64_t want = (rows + 7) / 8;                 // 8 warps (rows) per CTA
-  const uint32_t grid = static_cast<uint32_t>(want < 148ull * 16 ? want : 148ull * 16);
+  const uint64_t resident = 16ull * bmoe::device_sm_count();
+  const uint32_t grid = static_cast<uint32_t>(want < resident ? want : resident);
   bmoe::gather_rows_kernel<<<grid, bmoe::kGatherThreads, 0,
                              static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(src_dev), static_cast<uint4*>(dst_dev), index_dev, rows,
@@ -150,7 +151,7 @@ extern "C" int bmoe_route_rows(const void* const* src_bases_dev, uint32_t n_src,
   a.src_rows_cap = src_rows_cap;
   a.dst_rows_cap = dst_rows_cap;
   const uint64_t want = (rows + 7) / 8;
-  uint64_t cap = max_ctas != 0 ? max_ctas : 148ull * 8;
+  uint64_t cap = max_ctas != 0 ? max_ctas : 8ull * bmoe::device_sm_count();
   const uint32_t grid = static_cast<uint32_t>(want < cap ? want : cap);
   bmoe::route_rows_kernel<<<grid, bmoe::kRouteThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
   return cudaPeekAtLastError() == cudaSuccess ? BMOE_OK : BMOE_CUDA_ERROR;

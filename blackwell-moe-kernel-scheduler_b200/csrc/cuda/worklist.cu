@@ -16,6 +16,8 @@
 // (baselines/cutlass/cutlass_baseline.cu:243-266).
 #include <cuda_runtime.h>
 
+#include <atomic>
+
 #include <cstdint>
 
 #include "bmoe_b200.h"
@@ -244,6 +246,12 @@ int bmoe_worklist_build(const uint32_t* counts_dev,
       (reinterpret_cast<uintptr_t>(workspace_dev) & 255u) != 0) {
     return BMOE_INVALID_ARGUMENT;
   }
+  // The sorted order ranks every expert against every other one inside one CTA
+  // (experts^2 / 1024 steps per thread): bounded so that it stays tens of microseconds.
+  if (request->order == BMOE_ORDER_SORTED_BY_WORK &&
+      request->experts > BMOE_WORKLIST_MAX_SORTED_EXPERTS) {
+    return BMOE_INVALID_ARGUMENT;
+  }
   bmoe_worklist_layout layout;
   const int rc = bmoe_worklist_layout_for(request->experts, &layout);
   if (rc != BMOE_OK) return rc;
@@ -267,7 +275,8 @@ int bmoe_worklist_build(const uint32_t* counts_dev,
   if (tile_capacity != 0) {
     // The tile total is only known on the device; a fixed grid strides over it.
     const uint32_t want = (tile_capacity + bmoe::kExpandThreads - 1) / bmoe::kExpandThreads;
-    const uint32_t grid = want < 1184u ? want : 1184u;  // 148 SMs x 8
+    const uint32_t resident = 8u * bmoe::device_sm_count();
+    const uint32_t grid = want < resident ? want : resident;
     bmoe::worklist_expand_kernel<<<grid, bmoe::kExpandThreads, 0, s>>>(
         counts_dev, *request, tiles_dev, tile_capacity, arrays);
     if (cudaPeekAtLastError() != cudaSuccess) return BMOE_CUDA_ERROR;
@@ -292,7 +301,22 @@ static __device__ __align__(256) unsigned char g_worklist_scratch[kStaticScratch
 // device address; the address is looked up once per device, with that device
 // current, and cached here.
 constexpr int kMaxDevices = 64;
-void* g_scratch_address[kMaxDevices] = {};
+// Two host threads may resolve the address at the same time; both store the same
+// value, and the atomic makes that a defined program.
+std::atomic<void*> g_scratch_address[kMaxDevices];
+
+// Device address of the array on the current device (looked up on first use).
+void* static_scratch_address() {
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess) return nullptr;
+  if (device < 0 || device >= kMaxDevices) return nullptr;
+  void* address = g_scratch_address[device].load(std::memory_order_acquire);
+  if (address == nullptr) {
+    if (cudaGetSymbolAddress(&address, g_worklist_scratch) != cudaSuccess) return nullptr;
+    g_scratch_address[device].store(address, std::memory_order_release);
+  }
+  return address;
+}
 
 }  // namespace
 }  // namespace bmoe
@@ -311,19 +335,10 @@ extern "C" int bmoe_worklist_build_static(const uint32_t* counts_dev,
       layout.bytes > bmoe::kStaticScratchBytes) {
     return BMOE_INVALID_ARGUMENT;
   }
-  int device = -1;
-  if (cudaGetDevice(&device) != cudaSuccess) return BMOE_CUDA_ERROR;
-  if (device < 0 || device >= bmoe::kMaxDevices) return BMOE_UNSUPPORTED_DEVICE;
-  if (bmoe::g_scratch_address[device] == nullptr) {
-    // First use on this device (keep it outside stream capture).
-    void* address = nullptr;
-    if (cudaGetSymbolAddress(&address, bmoe::g_worklist_scratch) != cudaSuccess ||
-        address == nullptr) {
-      return BMOE_CUDA_ERROR;
-    }
-    bmoe::g_scratch_address[device] = address;
-  }
-  void* const scratch = bmoe::g_scratch_address[device];
+  // First use on this device resolves the address (keep it outside stream capture;
+  // bmoe_preload_kernels does it too).
+  void* const scratch = bmoe::static_scratch_address();
+  if (scratch == nullptr) return BMOE_CUDA_ERROR;
   // The planning kernel writes every array element and every totals field it
   // or the expansion kernel later reads, so nothing needs clearing here.
   const int rc = bmoe_worklist_build(counts_dev, request, tiles_dev, tile_capacity,
@@ -344,6 +359,9 @@ namespace bmoe {
 cudaError_t preload_worklist_kernels() {
   cudaError_t rc = preload_one(worklist_plan_kernel);
   if (rc == cudaSuccess) rc = preload_one(worklist_expand_kernel);
+  // Also resolve the fixed array of the allocation-free entry point, so that a caller
+  // that preloads has nothing left to do before a stream capture.
+  if (rc == cudaSuccess && static_scratch_address() == nullptr) rc = cudaErrorUnknown;
   return rc;
 }
 }  // namespace bmoe

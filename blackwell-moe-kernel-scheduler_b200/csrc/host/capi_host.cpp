@@ -65,7 +65,7 @@ const char* bmoe_status_string(int status) {
 int bmoe_generate_workload(const bmoe_workload_config* config,
                            uint32_t* counts_out) {
   if (config == nullptr || counts_out == nullptr) return BMOE_INVALID_ARGUMENT;
-  if (config->distribution > 3) return BMOE_INVALID_ARGUMENT;
+  if (config->distribution > 4) return BMOE_INVALID_ARGUMENT;
   try {
     bm::WorkloadConfig c;
     c.experts = config->experts;

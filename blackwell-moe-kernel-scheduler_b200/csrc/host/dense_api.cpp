@@ -73,6 +73,12 @@ struct DensePlanState {
     if (!ready) return KernelStatus::kInvalidArgument;
     return static_cast<KernelStatus>(bmoe_plan_run(handle, stream));
   }
+
+  // Waits for the last launch and reports a device-side time-out, if any.
+  KernelStatus finish() {
+    if (!ready) return KernelStatus::kInvalidArgument;
+    return static_cast<KernelStatus>(bmoe_plan_poll(handle, nullptr));
+  }
 };
 
 }  // namespace
@@ -106,13 +112,12 @@ Sm100DenseGemmPlanStats Sm100DenseGemmPlan::stats() const {
 }
 
 KernelStatus launch_sm100_dense_gemm(const Sm100DenseGemmArguments& args) {
-  Sm100DenseGemmPlan plan;
-  const KernelStatus status = plan.initialize(args);
-  if (status != KernelStatus::kSuccess) return status;
-  const KernelStatus ran = plan.run(args.stream);
-  // The plan owns the worklist and descriptors the kernel reads: its
-  // destructor frees device memory, which waits for the launch.
-  return ran;
+  // The plan owns the worklist and descriptors the kernel reads: wait for the
+  // launch before it goes out of scope, and report a device-side time-out.
+  DensePlanState plan;
+  KernelStatus status = plan.initialize(args, 1, false);
+  if (status == KernelStatus::kSuccess) status = plan.run(args.stream);
+  return status == KernelStatus::kSuccess ? plan.finish() : status;
 }
 
 const char* sm100_dense_kernel_name() {
@@ -148,9 +153,10 @@ Sm100DenseGemmPlanStats Sm100TwoSmGemmPlan::stats() const {
 }
 
 KernelStatus launch_sm100_2sm_gemm(const Sm100DenseGemmArguments& args) {
-  Sm100TwoSmGemmPlan plan;
-  const KernelStatus status = plan.initialize(args);
-  return status == KernelStatus::kSuccess ? plan.run(args.stream) : status;
+  DensePlanState plan;
+  KernelStatus status = plan.initialize(args, 2, false);
+  if (status == KernelStatus::kSuccess) status = plan.run(args.stream);
+  return status == KernelStatus::kSuccess ? plan.finish() : status;
 }
 
 const char* sm100_2sm_kernel_name() {

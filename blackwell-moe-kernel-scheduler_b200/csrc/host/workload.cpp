@@ -2,6 +2,7 @@
 //
 // Behaviour follows src/workload/workload.cpp of the reference:
 //   expert weights per routing family          workload.cpp:13-49
+//     (+ kHeavySparse, the heavy-hitter and sparse rules combined; appended here)
 //   config validation                          workload.cpp:64-76
 //   generate_workload                          workload.cpp:100-113
 //   validate_workload                          workload.cpp:115-125
@@ -58,6 +59,24 @@ std::vector<double> expert_weights(const WorkloadConfig& cfg) {
         e - 1,
         static_cast<std::uint32_t>(std::floor(e * cfg.inactive_expert_fraction)));
     for (std::uint32_t i = 0; i < silent; ++i) w[i] = 0.0;
+  } else if (cfg.distribution == Distribution::kHeavySparse) {
+    // Hot set in front (the heavy-hitter rule), idle set at the back (the sparse
+    // rule's count), the experts in between share what the hot set leaves.
+    const std::uint32_t silent = std::min<std::uint32_t>(
+        e - 1,
+        static_cast<std::uint32_t>(std::floor(e * cfg.inactive_expert_fraction)));
+    const std::uint32_t heavy = std::min<std::uint32_t>(
+        e - silent,
+        std::max<std::uint32_t>(
+            1u, static_cast<std::uint32_t>(std::ceil(e * cfg.heavy_hitter_fraction))));
+    const std::uint32_t light = e - silent - heavy;
+    const double heavy_w =
+        (light == 0 ? 1.0 : cfg.heavy_hitter_token_share) / heavy;
+    const double light_w =
+        light == 0 ? 0.0 : (1.0 - cfg.heavy_hitter_token_share) / light;
+    for (std::uint32_t i = 0; i < e; ++i) {
+      w[i] = i < heavy ? heavy_w : (i < heavy + light ? light_w : 0.0);
+    }
   }
   return w;
 }
@@ -85,6 +104,7 @@ std::string to_string(Distribution distribution) {
     case Distribution::kHeavyHitter: return "heavy_hitter";
     case Distribution::kSparse: return "sparse";
     case Distribution::kZipf: return "zipf";
+    case Distribution::kHeavySparse: return "heavy_sparse";
   }
   throw std::invalid_argument("unknown distribution");
 }
@@ -96,6 +116,7 @@ Distribution parse_distribution(const std::string& value) {
       {"heavy", Distribution::kHeavyHitter},
       {"sparse", Distribution::kSparse},
       {"zipf", Distribution::kZipf},
+      {"heavy_sparse", Distribution::kHeavySparse},
   };
   for (const auto& row : table) {
     if (value == row.name) return row.d;

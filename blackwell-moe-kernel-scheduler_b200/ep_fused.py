@@ -502,6 +502,8 @@ class FusedExpertParallelLayer:
                 status, f"grouped GEMM (site {report.code}, cta {report.cta}, "
                         f"group {report.stage}, rank {report.aux})")
         word = int(self._wait_status.item()) & 0xffffffff
+        if word:
+            self._wait_status.zero_()   # reported once; the layer stays usable
         if word & 0x40000000:
             raise _capi.EngineError(_capi.DEVICE_TIMEOUT,
                                     f"a bulk copy of exchange group {word & 0xff} did not complete")

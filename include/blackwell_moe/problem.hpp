@@ -19,10 +19,17 @@ enum class Distribution {
   kHeavyHitter,  // 1: a leading fraction of experts takes a fixed token share
   kSparse,       // 2: a leading fraction of experts receives nothing
   kZipf,         // 3: weight 1/(rank+1)^alpha
+  // Appended (no reference counterpart): the two families above combined. The
+  // first ceil(E * heavy_hitter_fraction) experts share heavy_hitter_token_share,
+  // the LAST floor(E * inactive_expert_fraction) experts receive nothing, the
+  // experts in between share the rest evenly. Decode-shaped routing with a hot
+  // set and an idle set uses it.
+  kHeavySparse,  // 4
 };
 
 std::string to_string(Distribution distribution);
-// Accepts "uniform", "heavy_hitter" (alias "heavy"), "sparse", "zipf";
+// Accepts "uniform", "heavy_hitter" (alias "heavy"), "sparse", "zipf" and
+// "heavy_sparse";
 // anything else throws std::invalid_argument.
 Distribution parse_distribution(const std::string& value);
 

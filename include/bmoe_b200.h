@@ -70,7 +70,8 @@ typedef struct bmoe_tile {
 /* ======================================================================== */
 
 /* blackwell_moe::WorkloadConfig (include/blackwell_moe/problem.hpp:16-25).
- * distribution: 0 uniform, 1 heavy_hitter, 2 sparse, 3 zipf. */
+ * distribution: 0 uniform, 1 heavy_hitter, 2 sparse, 3 zipf, 4 heavy_sparse
+ * (appended: hot set in front, idle set at the back; no reference counterpart). */
 typedef struct bmoe_workload_config {
   uint32_t experts;
   uint32_t distribution;
@@ -226,6 +227,9 @@ int bmoe_worklist_layout_for(uint32_t experts, bmoe_worklist_layout* out);
 
 /* Largest expert count the single-CTA planning kernel accepts. */
 #define BMOE_WORKLIST_MAX_EXPERTS 16384u
+/* Largest expert count for BMOE_ORDER_SORTED_BY_WORK (the stable descending sort is a
+ * rank computation, experts^2 / 1024 steps per thread; 4096 experts take about 50 us). */
+#define BMOE_WORKLIST_MAX_SORTED_EXPERTS 4096u
 
 typedef struct bmoe_worklist_request {
   uint32_t experts;
@@ -274,6 +278,11 @@ int bmoe_worklist_build(const uint32_t* counts_dev,
  *   - No cudaMalloc / cudaFree or other allocating call is made.
  *   - The first call on each device looks up the device address of the array
  *     (cudaGetSymbolAddress); make that first call outside any stream capture.
+ *     bmoe_preload_kernels() performs the same lookup, so a caller that preloads
+ *     has already met this rule. The lookup result is cached per device ordinal
+ *     for the life of the process (two host threads making their first call
+ *     together both store the same address); after cudaDeviceReset the cache
+ *     is stale and the entry point must not be used again in that process.
  *   - All calls on one device share the array. Every word a call reads from it
  *     is written by that call first, so stale contents from an earlier call
  *     are harmless, but two calls whose kernels overlap on the GPU (different

@@ -87,14 +87,17 @@ static double canonical53(orc_mt64* g) {
 /* ------------------------------------------------------------------------ */
 static int fraction_ok(double x) { return x >= 0.0 && x <= 1.0; }
 
-/* distribution: 0 uniform, 1 heavy_hitter, 2 sparse, 3 zipf.
+/* distribution: 0 uniform, 1 heavy_hitter, 2 sparse, 3 zipf (the reference's
+ * four), 4 heavy_sparse (engine-side family without a reference counterpart:
+ * the heavy-hitter rule for the leading experts, the sparse rule's count of idle
+ * experts at the BACK, the rest shared evenly; same draw machinery).
  * Returns 0, or -1 for a configuration the reference rejects. */
 ORC_EXPORT int orc_generate_counts(uint32_t experts, uint64_t total_tokens,
                                    uint32_t distribution, uint64_t seed,
                                    double zipf_alpha, double heavy_fraction,
                                    double heavy_share, double inactive_fraction,
                                    uint32_t* counts_out) {
-  if (experts == 0 || distribution > 3 || !(zipf_alpha > 0.0)) return -1;
+  if (experts == 0 || distribution > 4 || !(zipf_alpha > 0.0)) return -1;
   if (!fraction_ok(heavy_fraction) || heavy_fraction == 0.0 ||
       !fraction_ok(heavy_share) || !fraction_ok(inactive_fraction)) {
     return -1;
@@ -116,6 +119,18 @@ ORC_EXPORT int orc_generate_counts(uint32_t experts, uint64_t total_tokens,
     uint32_t silent = (uint32_t)floor(experts * inactive_fraction);
     if (silent > experts - 1) silent = experts - 1;
     for (uint32_t i = 0; i < silent; ++i) w[i] = 0.0;
+  } else if (distribution == 4) {
+    uint32_t silent = (uint32_t)floor(experts * inactive_fraction);
+    if (silent > experts - 1) silent = experts - 1;
+    uint32_t heavy = (uint32_t)ceil(experts * heavy_fraction);
+    if (heavy < 1) heavy = 1;
+    if (heavy > experts - silent) heavy = experts - silent;
+    const uint32_t light = experts - silent - heavy;
+    const double hw = (light == 0 ? 1.0 : heavy_share) / heavy;
+    const double lw = light == 0 ? 0.0 : (1.0 - heavy_share) / light;
+    for (uint32_t i = 0; i < experts; ++i) {
+      w[i] = i < heavy ? hw : (i < heavy + light ? lw : 0.0);
+    }
   }
   memset(counts_out, 0, sizeof(uint32_t) * experts);
 

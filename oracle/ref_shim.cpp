@@ -9,6 +9,7 @@
 #include <cstdint>
 #include <cstring>
 #include <exception>
+#include <random>
 #include <vector>
 
 #include "blackwell_moe/scheduler/scheduler.cuh"
@@ -35,6 +36,20 @@ uint64_t copy_tiles(const std::vector<bm::ExpertTile>& tiles, void* out, uint64_
 }  // namespace
 
 extern "C" {
+
+// The reference's draw loop (src/workload/workload.cpp:100-113) over an explicit
+// weight vector: the same two standard-library objects, nothing else. Pins the
+// restated mt19937_64 / discrete_distribution on weight vectors that none of the
+// reference's four families produces (zero weights at the back).
+int ref_draw_counts(const double* weights, uint32_t experts, uint64_t total_tokens,
+                    uint64_t seed, uint32_t* counts_out) {
+  if (weights == nullptr || counts_out == nullptr || experts == 0) return -1;
+  std::mt19937_64 engine(seed);
+  std::discrete_distribution<std::uint32_t> pick(weights, weights + experts);
+  std::memset(counts_out, 0, sizeof(uint32_t) * experts);
+  for (uint64_t t = 0; t < total_tokens; ++t) counts_out[pick(engine)] += 1;
+  return 0;
+}
 
 int ref_generate_counts(uint32_t experts, uint64_t total_tokens, uint32_t distribution,
                         uint64_t seed, double zipf_alpha, double heavy_fraction,

@@ -12,6 +12,10 @@ Sources of truth:
     tests/test_sm100_*_correctness.cu), whose products are multiples of 1/256
     with |sum| small enough to be exact in FP32; the expected BF16 output is
     therefore fixed by arithmetic and is computed here in float64.
+  * "build_side_workloads": routing families that exist only in this engine (the
+    heavy_sparse family of the decode-shaped configuration). Their weights are
+    stated here and drawn through the reference's draw loop over the same
+    standard-library generator objects (ref_draw_counts in oracle/ref_shim.cpp).
 The JSON is committed; tests never read the reference checkout.
 """
 
@@ -140,6 +144,40 @@ def main() -> None:
                              "reals": [float(x).hex() for x in reals]}
         entry["schedule_148"] = sched
         out["workloads"][name] = entry
+
+    # ---- engine-side routing families (no generator in the reference) ----
+    # heavy_sparse: the first ceil(E * heavy_fraction) experts share heavy_share, the
+    # last floor(E * inactive_fraction) experts get nothing, the rest share evenly.
+    out["build_side_workloads"] = {}
+    for name, cfg, shape in [
+        ("c3_heavy_sparse_e256_decode",
+         dict(base, experts=256, total_tokens=2048, distribution=4, heavy_fraction=8 / 256,
+              heavy_share=0.5, inactive_fraction=0.4), (2048, 128, 128)),
+        ("heavy_sparse_e32", dict(base, experts=32, total_tokens=10000, distribution=4),
+         (7168, 128, 128)),
+    ]:
+        e = cfg["experts"]
+        silent = min(e - 1, int(np.floor(e * cfg["inactive_fraction"])))
+        heavy = min(e - silent, max(1, int(np.ceil(e * cfg["heavy_fraction"]))))
+        light = e - silent - heavy
+        weights = np.zeros(e, dtype=np.float64)
+        weights[:heavy] = (cfg["heavy_share"] if light else 1.0) / heavy
+        if light:
+            weights[heavy:heavy + light] = (1.0 - cfg["heavy_share"]) / light
+        counts = np.zeros(e, dtype=np.uint32)
+        rc = ref.ref_draw_counts(weights.ctypes.data_as(ctypes.c_void_p), u32(e),
+                                 u64(cfg["total_tokens"]), u64(cfg["seed"]),
+                                 counts.ctypes.data_as(ctypes.c_void_p))
+        assert rc == 0 and int(counts.sum()) == cfg["total_tokens"]
+        n, tm, tn = shape
+        m, mi = metrics(counts, n, tm, tn)
+        entry = {"config": cfg, "shape": [n, tm, tn], "counts": counts.tolist(),
+                 "metrics": [float(x).hex() for x in m],
+                 "active_experts": int(mi[0]), "total_tiles": int(mi[1])}
+        for tn2 in (128, 256):
+            for order in (0, 1):
+                entry[f"tiles_sha256_tn{tn2}_order{order}"] = sha(tiles_for(counts, n, tm, tn2, order))
+        out["build_side_workloads"][name] = entry
 
     # Small explicit tile cases (full records), incl. the reference's unit-test inputs.
     for counts, n, tm, tn in [([0, 1, 128, 129], 256, 128, 128), ([129], 129, 128, 128),

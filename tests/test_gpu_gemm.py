@@ -265,6 +265,101 @@ def test_benchmark_shape_properties(engine, oracle, golden):
     assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 1e-3
 
 
+def _device_inputs(counts, n, k, seed=2026):
+    """Seeded A ~ N(0,1), W ~ N(0, 1/sqrt(k)) drawn on the device (the full-size shapes
+    are too slow to draw on the host); the oracle sees the same bits copied back."""
+    import torch
+
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+    a = torch.randn(sum(counts), k, generator=gen, device="cuda").to(torch.bfloat16)
+    w = torch.empty(len(counts), n, k, dtype=torch.bfloat16, device="cuda")
+    for e in range(len(counts)):
+        w[e] = (torch.randn(n, k, generator=gen, device="cuda") * k ** -0.5).to(torch.bfloat16)
+    return a, w
+
+
+def _full_shape_properties(engine, oracle, counts, n, k, *, variants, row_stride, row_phase=1):
+    """The checks of a benchmark configuration at its real size: every tile run once,
+    every launch variant bit-identical to expert order, and a row sample (rows
+    r % row_stride == row_phase of every expert) within 2 BF16 ulp / 1e-3 relative
+    Frobenius error of the FP32 sequential-k oracle. The reference's rule for a
+    correctness check (python/blackwell_moe_tirx/runner.py:198-231) is weaker: rtol 2e-2,
+    atol 5e-2 per expert; it is asserted as well."""
+    a, w = _device_inputs(counts, n, k)
+    base = run_engine(engine, a, w, counts, "expert_order", observers=True)
+    assert np.all(base["visits"] == 1)
+    assert int(base["cta"].sum()) == base["stats"].total_tiles
+    assert base["stats"].active_experts == sum(c > 0 for c in counts)
+    for policy, opts in variants:
+        out = run_engine(engine, a, w, counts, policy, observers=True, **opts)
+        assert np.array_equal(out["bits"], base["bits"]), (policy, opts)
+        assert np.all(out["visits"] == 1), (policy, opts)
+    ref = oracle.grouped_gemm(bits_of(a), bits_of(w), counts, n, k, want_f32=True,
+                              row_stride=row_stride, row_phase=row_phase)
+    rows, row0 = [], 0
+    for m in counts:
+        rows.extend(range(row0 + row_phase, row0 + m, row_stride))
+        row0 += m
+    assert len(rows) == ref["rows"] and len(rows) > 0
+    exact = ref["f32"][rows].astype(np.float64)
+    got = support.bf16_bits_to_f32(base["bits"][rows]).astype(np.float64)
+    assert np.all(np.isfinite(support.bf16_bits_to_f32(base["bits"])))
+    mag = np.maximum(np.abs(exact), 2.0 ** -6)
+    err_ulp = (np.abs(got - exact) / 2.0 ** (np.floor(np.log2(mag)) - 7)).max()
+    assert err_ulp <= 2.0, f"max error {err_ulp:.3f} BF16 ulp"
+    want = support.bf16_bits_to_f32(ref["bf16"][rows]).astype(np.float64)
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 1e-3
+    assert np.all(np.abs(got - want) <= 5e-2 + 2e-2 * np.abs(want))
+    return base
+
+
+ALL_VARIANTS = [("static_persistent", {}), ("dynamic_queue", {}),
+                ("dynamic_queue", {"claim_size": 4}),
+                ("dynamic_queue", {"claim_size": 8, "hybrid_tail_tiles": 148}),
+                ("compacted", {}), ("clc", {}), ("auto", {}),
+                ("expert_order", {"cta_group": 1}), ("dynamic_queue", {"cta_group": 1}),
+                ("expert_order", {"cta_group": 2}), ("dynamic_queue", {"cta_group": 2}),
+                ("clc", {"cta_group": 2}), ("expert_order", {"cta_group": 1, "tile_n": 128})]
+
+
+def test_decode_shape_properties(engine, oracle, golden):
+    """DeepSeek-V3-shaped small-M decode at full size (E=256, 2048 routed rows, K=7168,
+    N=2048; 8 experts take half the rows, the last 102 experts are idle): all rows
+    against the oracle, all variants bit-identical, compaction skips the idle experts."""
+    entry = golden["build_side_workloads"]["c3_heavy_sparse_e256_decode"]
+    counts = entry["counts"]
+    base = _full_shape_properties(engine, oracle, counts, 2048, 7168, variants=ALL_VARIANTS,
+                                  row_stride=1, row_phase=0)
+    assert base["stats"].active_experts == entry["active_experts"]
+    assert set(np.unique(base["worklist"]["expert_id"])) == {e for e, c in enumerate(counts) if c}
+
+
+@pytest.mark.parametrize("point", ["c4_uniform_e128", "c4_zipf05_e128", "c4_zipf10_e128",
+                                   "c4_zipf15_e128"])
+def test_skew_sweep_shape_properties(engine, oracle, golden, point):
+    """Qwen3-MoE-shaped sweep points at full size (E=128, 131072 routed rows, K=2048,
+    N=768 = three 256-wide column tiles)."""
+    counts = golden["workloads"][point]["counts"]
+    _full_shape_properties(engine, oracle, counts, 768, 2048, variants=ALL_VARIANTS,
+                           row_stride=97)
+
+
+def test_expert_parallel_rank_shape_properties(engine, oracle, golden):
+    """The per-rank problem of the expert-parallel configuration (E=256, 262144 routed
+    rows, K=7168, N=2048, Zipf 1.0) under the 8-rank tile-balanced placement: the experts
+    one rank owns, with their global row counts, as one grouped GEMM on one GPU. Rank 0
+    holds the hottest expert alone (one 42650-row problem), rank 1 a mix of experts."""
+    from bmoe_b200 import ep
+
+    counts_all = golden["workloads"]["c5_zipf1_e256"]["counts"]
+    owner, _ = ep.place_experts(counts_all, 8, 2048)
+    for rank in (0, 1):
+        counts = [c for e, c in enumerate(counts_all) if owner[e] == rank]
+        assert 0.8 * 32768 <= sum(counts) <= 1.4 * 32768
+        _full_shape_properties(engine, oracle, counts, 2048, 7168,
+                               variants=ALL_VARIANTS[:7] + ALL_VARIANTS[9:12], row_stride=193)
+
+
 def test_fp32_output_epilogue(engine, oracle):
     """FP32 D (the unrounded accumulators, the direct-launcher contract): exact on the
     reference's known-answer inputs, within FP32 accumulation noise of the

@@ -44,6 +44,33 @@ def test_generator_equals_golden_and_oracle(engine, oracle, golden):
     assert gen_counts(engine, 8, 10, 2, inactive_fraction=1.5)[0] == engine._capi.INVALID_ARGUMENT
 
 
+def test_heavy_sparse_family_equals_golden_and_oracle(engine, oracle, golden):
+    """The decode-shaped routing family that exists only in this engine: hot set in front,
+    idle set at the back. Golden counts come from the standard library's own generator
+    objects over the stated weights."""
+    for name, entry in golden["build_side_workloads"].items():
+        cfg = entry["config"]
+        kw = dict(seed=cfg["seed"], zipf_alpha=cfg["zipf_alpha"], heavy_fraction=cfg["heavy_fraction"],
+                  heavy_share=cfg["heavy_share"], inactive_fraction=cfg["inactive_fraction"])
+        rc, counts = gen_counts(engine, cfg["experts"], cfg["total_tokens"], 4, **kw)
+        assert rc == 0 and counts.tolist() == entry["counts"], name
+        rc, counts = oracle.generate_counts(cfg["experts"], cfg["total_tokens"], 4, **kw)
+        assert rc == 0 and counts.tolist() == entry["counts"], name
+        silent = int(np.floor(cfg["experts"] * cfg["inactive_fraction"]))
+        assert not any(entry["counts"][cfg["experts"] - silent:])
+    c3 = golden["build_side_workloads"]["c3_heavy_sparse_e256_decode"]
+    assert sum(c3["counts"][:8]) / sum(c3["counts"]) == pytest.approx(0.5, abs=0.03)
+    assert 150 <= c3["active_experts"] <= 154
+    rng = np.random.default_rng(5)
+    for _ in range(20):
+        e, t = int(rng.integers(1, 300)), int(rng.integers(0, 20000))
+        kw = dict(seed=int(rng.integers(0, 2**50)), heavy_fraction=float(rng.uniform(0.01, 1)),
+                  heavy_share=float(rng.uniform(0, 1)), inactive_fraction=float(rng.uniform(0, 1)))
+        assert np.array_equal(gen_counts(engine, e, t, 4, **kw)[1],
+                              oracle.generate_counts(e, t, 4, **kw)[1]), (e, t, kw)
+    assert gen_counts(engine, 8, 10, 5)[0] == engine._capi.INVALID_ARGUMENT
+
+
 def test_workload_unit_expectations(engine):
     """tests/test_workload.cpp:18-57 of the reference."""
     for dist in range(4):

@@ -2,9 +2,10 @@
 allocate device memory (fixed memory pools, plug-ins that are only handed
 buffers). Its auxiliary arrays sit in a fixed array inside the library, so the
 only buffers involved are the caller's counts (input) and tile records /
-totals (outputs). Checked here against bmoe_worklist_build, record for record,
-on two calls in a row that share that array. Collected last on purpose: a run
-that stops at the first failure has then already run every other test."""
+totals (outputs). Checked here against bmoe_worklist_build and against the CPU
+oracle, record for record, on two calls in a row that share that array.
+Collected last on purpose: a run that stops at the first failure has then
+already run every other test."""
 
 import ctypes as C
 
@@ -41,7 +42,7 @@ def build_existing(engine, counts, n, tm, tn, order, raster, capacity):
     return tiles.cpu().numpy().view(support.TILE_DTYPE), arrays
 
 
-def test_two_calls_in_a_row_match_the_workspace_entry_point(engine):
+def test_two_calls_in_a_row_match_the_workspace_entry_point(engine, oracle):
     import torch
 
     rng = np.random.default_rng(2026)
@@ -62,6 +63,9 @@ def test_two_calls_in_a_row_match_the_workspace_entry_point(engine):
         torch.cuda.synchronize()
         got = tiles.cpu().numpy().view(support.TILE_DTYPE)[:total]
         assert np.array_equal(got, want[:total])
+        # and, directly, the CPU restatement of the reference's tile builder
+        assert np.array_equal(got, oracle.build_tiles(counts, n, tm, tn, order=order,
+                                                      raster=raster))
         t = totals.cpu().numpy().view(np.uint32)
         assert int(t[0]) == total and int(t[1]) == arrays["active_experts"]
         assert int(t[2]) | (int(t[3]) << 32) == arrays["total_rows"]
