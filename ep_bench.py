@@ -1,10 +1,13 @@
-"""Multi-GPU arm of bench.py: the expert-parallel configuration.
+"""Multi-GPU arm of bench.py (a benchmark driver, not part of the package): the
+expert-parallel configuration.
 
 E=256 experts, top-8, T tokens split evenly across ranks, K=7168, N=2048, BF16,
 Zipf s=1.0 routing (seeded multinomial without replacement per token). Experts are
 placed by tile-count balance once; every step runs counts exchange, dispatch
 all-to-all, local grouped GEMM and combine all-to-all. Timed on the device with
 CUDA events, maximum over ranks; total work is fixed as ranks grow (strong scaling).
+Outside the timed region every rank's result rows are compared, bit for bit, with the
+same workload computed by the single-GPU engine on rank 0; a mismatch fails the run.
 """
 
 from __future__ import annotations
@@ -201,40 +204,75 @@ def run(args, spec, workload):
     barrier()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1) / e2e_steps)
     ops.poll()
+    # this rank's result rows of one more step, kept for the parity check below
+    y_ep = layer.forward(x_local, ids_local, w_local, **extra).clone()
+    ops.poll()
 
     # The same workload on ONE GPU (rank 0 alone, no exchange), so that strong
     # scaling can be read from a single run.
     single_gpu = None
+    parity = None
     if world > 1 and not args.no_single_gpu_ref:
+        # Every rank's token rows (and router gates) travel to rank 0, which runs the whole
+        # batch through the single-GPU engine; each rank then receives the rows that belong
+        # to its tokens and compares them with what the expert-parallel step gave it.
+        per_rank = (hi - lo)
+        even = tokens % world == 0
+        x_parts = [torch.empty_like(x_local) for _ in range(world)] if rank == 0 and even else None
+        g_parts = None
+        if even:
+            dist.gather(x_local, x_parts, dst=0)
+            if gates is not None:
+                g_parts = [torch.empty_like(gates) for _ in range(world)] if rank == 0 else None
+                dist.gather(gates, g_parts, dst=0)
+        y_ref_parts = None
         if rank == 0:
-            if args.exchange != "nccl":
-                pass  # peer buffers stay mapped by the other ranks until they exit
             del w_local, layer, ops, plain
             torch.cuda.empty_cache()
             solo_owner = [0] * spec["experts"]
             solo_ops = ep.CudaOps(scheduler=args.policy, cta_group=args.cta_group)
             solo = ep.ExpertParallelLayer(solo_owner, n, k, rank=0, world=1, ops=solo_ops)
             w_all = _expert_weights(torch, list(range(spec["experts"])), n, k, dev)
-            gen.manual_seed(4000)
-            x_all = torch.randn(tokens, k, generator=gen, device=dev,
-                                dtype=torch.float32).to(torch.bfloat16)
+            if even:
+                x_all = torch.cat(x_parts, dim=0)
+                del x_parts
+            else:
+                gen.manual_seed(4000)
+                x_all = torch.randn(tokens, k, generator=gen, device=dev,
+                                    dtype=torch.float32).to(torch.bfloat16)
+            solo_extra = ({"topk_weights": torch.cat(g_parts, dim=0)}
+                          if gates is not None and even else {})
             ids_dev = ids_all.to(dev)
             for _ in range(3):
-                solo.forward(x_all, ids_dev, w_all)
+                solo.forward(x_all, ids_dev, w_all, **solo_extra)
             torch.cuda.synchronize()
             s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             solo_steps = max(3, min(args.steps, 10))
             s0.record(stream)
             for _ in range(solo_steps):
-                solo.forward(x_all, ids_dev, w_all)
+                y_all = solo.forward(x_all, ids_dev, w_all, **solo_extra)
             s1.record(stream)
             torch.cuda.synchronize()
             solo_ops.poll()
             solo_ms = s0.elapsed_time(s1) / solo_steps
             single_gpu = {"value": total_flops / (solo_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                           "ms_per_step": solo_ms, "steps": solo_steps}
+            if even:
+                y_ref_parts = list(y_all.reshape(world, -1, n).contiguous().unbind(0))
             del w_all, x_all
         dist.barrier()
+        if even:
+            y_ref = torch.empty_like(y_ep)
+            dist.scatter(y_ref, y_ref_parts, src=0)
+            bad_rows = (y_ref.view(torch.int16) != y_ep.view(torch.int16)).any(dim=1).sum()
+            tally = torch.stack([bad_rows.to(torch.int64),
+                                 torch.tensor(y_ep.shape[0], dtype=torch.int64, device=dev)])
+            dist.all_reduce(tally)
+            parity = {"checked": True, "rows_compared": int(tally[1].item()),
+                      "rows_differing": int(tally[0].item()),
+                      "against": "the same batch through the single-GPU engine on rank 0, bitwise"}
+            if parity["rows_differing"] != 0:
+                raise RuntimeError(f"expert-parallel output differs from the single-GPU engine: {parity}")
 
     if world > 1:
         dist.barrier()
@@ -251,6 +289,15 @@ def run(args, spec, workload):
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
+        # the same batch on ONE GPU in the same run, and this line's value over N times that
+        "single_gpu_same_workload": single_gpu,
+        "efficiency_same_workload": (total_flops / (ms_per_step * 1e-3) / 1e12
+                                     / (world * single_gpu["value"]) if single_gpu else None),
+        "parity_checked": bool(parity and parity["checked"]),
+        "rows_compared": parity["rows_compared"] if parity else 0,
+        "parity": parity,
+        "p50_us": bench.percentile(step_samples, 0.5) * 1e3,
+        "p99_us": bench.percentile(step_samples, 0.99) * 1e3,
         "config": {"workload": workload, "experts": spec["experts"], "top_k": top_k,
                    "tokens": tokens, "k": k, "n": n, "policy": args.policy,
                    "parallelism": f"ep{world}",
@@ -277,8 +324,6 @@ def run(args, spec, workload):
                             if args.exchange == "peer" else
                             "count all-gather + pack + all-to-all dispatch + unpack + "
                             "grouped GEMM + repack + all-to-all combine + un-permute")},
-        "p50_us": bench.percentile(step_samples, 0.5) * 1e3,
-        "p99_us": bench.percentile(step_samples, 0.99) * 1e3,
         "phases_ms_max_over_ranks": phases_ms,
         "phases_note": "per-phase times come from an un-pipelined pass; the timed steps "
                        "overlap them when pipeline_groups > 1",
@@ -288,7 +333,6 @@ def run(args, spec, workload):
                      "kernel": "grouped_gemm_kernel (rank 0, GEMM phase only)",
                      "avg_launch_ms": gemm_ms_local},
         "cpu_baseline": None,
-        "single_gpu_same_workload": single_gpu,
         "e2e": {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                 "h2d_bytes_per_step": x_host.numel() * 2 * world,
                 "d2h_bytes_per_step": y_host.numel() * 2 * world, "ms_per_step": e2e_ms},

@@ -542,13 +542,16 @@ static void row_block_f64(const uint16_t* a_row, const float* bt, uint32_t k,
  * Only rows r (index inside the expert) with r % row_stride == row_phase are
  * computed; others are left untouched. threads <= 0 uses all cores. Returns
  * the number of rows computed. */
-ORC_EXPORT uint64_t orc_grouped_gemm(const uint16_t* a, const uint16_t* b,
-                                     const uint32_t* counts, uint32_t experts,
-                                     uint32_t n, uint32_t k, uint16_t* d_bf16,
-                                     float* d_f32, double* d_f64,
-                                     uint32_t row_stride, uint32_t row_phase,
-                                     int threads) {
+static uint64_t grouped_gemm_impl(const uint16_t* a, const uint16_t* b,
+                                  const uint32_t* counts, uint32_t experts,
+                                  uint32_t n, uint32_t k, uint16_t* d_bf16,
+                                  float* d_f32, double* d_f64,
+                                  uint32_t row_stride, uint32_t row_phase,
+                                  uint32_t col_block_stride, uint32_t col_block_phase,
+                                  int threads, uint64_t* elements_out) {
   if (row_stride == 0) row_stride = 1;
+  if (col_block_stride == 0) col_block_stride = 1;
+  uint64_t elements = 0;
 #ifdef _OPENMP
   if (threads > 0) omp_set_num_threads(threads);
 #else
@@ -563,6 +566,8 @@ ORC_EXPORT uint64_t orc_grouped_gemm(const uint16_t* a, const uint16_t* b,
     const uint16_t* be = b + (size_t)e * n * k;
     for (uint32_t c0 = 0; c0 < n; c0 += ORC_COLS) {
       const uint32_t cols = n - c0 < ORC_COLS ? n - c0 : ORC_COLS;
+      if ((c0 / ORC_COLS) % col_block_stride != col_block_phase) continue;
+      for (uint32_t r = row_phase; r < rows; r += row_stride) elements += cols;
       /* Transposed FP32 copy of the weight block: bt[kk][c]. */
 #pragma omp parallel for schedule(static)
       for (uint32_t kk = 0; kk < k; ++kk) {
@@ -593,7 +598,36 @@ ORC_EXPORT uint64_t orc_grouped_gemm(const uint16_t* a, const uint16_t* b,
     row_base += rows;
   }
   free(bt);
+  if (elements_out != NULL) *elements_out = elements;
   return rows_done;
+}
+
+ORC_EXPORT uint64_t orc_grouped_gemm(const uint16_t* a, const uint16_t* b,
+                                     const uint32_t* counts, uint32_t experts,
+                                     uint32_t n, uint32_t k, uint16_t* d_bf16,
+                                     float* d_f32, double* d_f64,
+                                     uint32_t row_stride, uint32_t row_phase,
+                                     int threads) {
+  return grouped_gemm_impl(a, b, counts, experts, n, k, d_bf16, d_f32, d_f64, row_stride,
+                           row_phase, 1, 0, threads, NULL);
+}
+
+/* The same loop over a SAMPLE OF COLUMN BLOCKS: all rows of every expert, but only the
+ * 128-column blocks whose index % col_block_stride == col_block_phase. Every sampled
+ * block does what the full problem does for it (weight block made ready once, then all
+ * rows), so the time per output element is that of the full problem; a row sample is
+ * not (the per-expert weight preparation is then shared by fewer rows). Used to time a
+ * bounded part of a large configuration. Returns the number of output elements
+ * computed (FLOPs = 2 * k * elements). */
+ORC_EXPORT uint64_t orc_grouped_gemm_column_sample(const uint16_t* a, const uint16_t* b,
+                                                   const uint32_t* counts, uint32_t experts,
+                                                   uint32_t n, uint32_t k, uint16_t* d_bf16,
+                                                   uint32_t col_block_stride,
+                                                   uint32_t col_block_phase, int threads) {
+  uint64_t elements = 0;
+  grouped_gemm_impl(a, b, counts, experts, n, k, d_bf16, NULL, NULL, 1, 0, col_block_stride,
+                    col_block_phase, threads, &elements);
+  return elements;
 }
 
 /* Weighted top-k combine: out[t,:] = bf16(sum_j w[t,j] * float(src[row[t,j],:])),
