@@ -651,10 +651,16 @@ def run_skew_sweep(args):
     dev = torch.device("cuda:0")
     stream = torch.cuda.current_stream()
     base = dict(experts=128, top_k=8, tokens=16384, k=2048, n=768)
-    points = [("uniform", 0, 1.2), ("zipf0.5", 3, 0.5), ("zipf1.0", 3, 1.0), ("zipf1.5", 3, 1.5)]
+    points = [(label, dict(base, distribution=dist_id, zipf_alpha=alpha))
+              for label, dist_id, alpha in (("uniform", 0, 1.2), ("zipf0.5", 3, 0.5),
+                                            ("zipf1.0", 3, 1.0), ("zipf1.5", 3, 1.5))]
+    if args.sweep_all:
+        # the other single-GPU configurations, for the p99-vs-expert-order table
+        points += [("mixtral_zipf1.0", WORKLOADS[DEFAULT_WORKLOAD]),
+                   ("decode_heavy_sparse",
+                    WORKLOADS["deepseek_decode_e256_t256_k7168_n2048_heavy_sparse"])]
     out = []
-    for label, dist_id, alpha in points:
-        spec = dict(base, distribution=dist_id, zipf_alpha=alpha)
+    for label, spec in points:
         counts = workload_counts(engine, spec)
         n, k = spec["n"], spec["k"]
         arr = (C.c_uint32 * len(counts))(*counts)
@@ -717,7 +723,9 @@ def run_skew_sweep(args):
             plan.close()
         for row in timing.values():
             row["p99_speedup_vs_expert_order"] = timing["expert_order"]["p99_us"] / row["p99_us"]
-        out.append({"routing": label, "cv_m": wm.coefficient_of_variation,
+        out.append({"routing": label, "shape": {"experts": spec["experts"], "rows": sum(counts),
+                                                 "k": k, "n": n},
+                    "cv_m": wm.coefficient_of_variation,
                     "max_over_mean_m": wm.max_over_mean, "tile_count_cv": wm.tile_count_cv,
                     "small_m_expert_ratio": wm.small_m_expert_ratio,
                     "total_tiles_128x128": wm.total_tiles, "schedule_model_148_ctas": model,
@@ -728,6 +736,64 @@ def run_skew_sweep(args):
                       "n_gpus": 1, "dtype": "bf16", "data": "synthetic",
                       "config": {"workload": "qwen3_skew_sweep_e128_t16384_k2048_n768", **base},
                       "iters": args.policy_iters, "sweep": out}), flush=True)
+
+
+def run_dense_sweep(args):
+    """Dense M-sweep at N=7168, K=2048 (docs/sm100_native_dense.md:124-128 and
+    tools/run_b200_optimization_suite.sh:66-73 of the reference). All three columns come
+    from the reference's OWN benchmark program (benchmarks/sm100_dense_benchmark.cu /
+    sm100_2sm_benchmark.cu, unmodified: 20 warm-up launches, 200 timed with one CUDA-event
+    pair each, median): linked against this engine's drop-in dense plans (single CTA and
+    CTA pair), and linked against the reference's own sm_100a kernel, its CUTLASS 1-SM
+    collective (src/kernels/sm100_dense_gemm.cu). One JSON line with a "sweep" list."""
+    n, k = 7168, 2048
+    peaks = measured_peaks()
+    bin_dir = ROOT / "oracle" / "_ref" / "bin"
+    programs = {"engine_single_cta": bin_dir / "ref_sm100_dense_benchmark",
+                "engine_cta_pair": bin_dir / "ref_sm100_2sm_benchmark",
+                "reference_cutlass_1sm": bin_dir / "ref_native_sm100_dense_benchmark"}
+    missing = [str(p.relative_to(ROOT)) for p in programs.values() if not p.exists()]
+
+    def one(program, m):
+        proc = subprocess.run([str(program), f"--m={m}", f"--n={n}", f"--k={k}",
+                               "--warmup=20", "--iterations=200", "--csv"],
+                              capture_output=True, text=True, timeout=300)
+        lines = proc.stdout.strip().splitlines()
+        if proc.returncode != 0 or len(lines) < 2:
+            return {"unavailable": (proc.stderr.strip() or proc.stdout.strip())[-200:]}
+        rec = dict(zip(lines[0].split(","), lines[-1].split(",")))
+        return {"median_us": float(rec["median_ms"]) * 1e3, "p95_us": float(rec["p95_ms"]) * 1e3,
+                "tflops": float(rec["tflops"]), "kernel": rec["kernel"],
+                "tile": [int(rec["tile_m"]), int(rec["tile_n"]), int(rec["tile_k"])],
+                "ctas": int(rec["persistent_ctas"])}
+
+    rows = []
+    for m in (16, 32, 64, 128, 256, 512, 1024, 4096, 8192):
+        flops = 2.0 * m * n * k
+        algorithmic_bytes = 2.0 * (m * k + n * k + m * n)
+        floor_us = max(algorithmic_bytes / (peaks["hbm_gbs"] * 1e9),
+                       flops / (peaks["bf16_tflops"] * 1e12)) * 1e6
+        row = {"m": m, "roofline_floor_us": floor_us}
+        for label, program in programs.items():
+            row[label] = one(program, m) if program.exists() else {"unavailable": "not built"}
+        mine = [row[x]["median_us"] for x in ("engine_single_cta", "engine_cta_pair")
+                if "median_us" in row[x]]
+        if mine:
+            row["engine_best_us"] = min(mine)
+            row["engine_best_over_floor"] = min(mine) / floor_us
+            if "median_us" in row["reference_cutlass_1sm"]:
+                row["speedup_vs_reference"] = row["reference_cutlass_1sm"]["median_us"] / min(mine)
+        rows.append(row)
+    print(json.dumps({"metric": "median us per dense GEMM vs M (N=7168, K=2048)", "unit": "us",
+                      "n_gpus": 1, "dtype": "bf16", "data": "synthetic",
+                      "config": {"workload": "dense_sweep_n7168_k2048", "n": n, "k": k,
+                                 "warmup": 20, "iterations": 200,
+                                 "harness": "the reference's benchmark programs, unmodified"},
+                      "reference_arm": ("unavailable: not built: " + ", ".join(missing)) if missing
+                      else "the reference's CUTLASS 1-SM collective (cluster 1x1x1), unmodified "
+                           "sources, CUTLASS 4.5.0 headers found in site-packages (the "
+                           "reference pins 4.6.0)",
+                      "sweep": rows}), flush=True)
 
 
 def main():
@@ -777,11 +843,20 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--sweep", action="store_true",
                     help="run the Qwen3-shaped routing-skew sweep instead of the headline")
+    ap.add_argument("--sweep-all", action="store_true",
+                    help="with --sweep: add the Mixtral-shaped and the decode-shaped "
+                         "configurations to the routing points")
+    ap.add_argument("--dense-sweep", action="store_true",
+                    help="dense M-sweep (N=7168, K=2048): engine dense plans next to the "
+                         "reference's own CUTLASS 1-SM kernel")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
     if args.sweep:
         run_skew_sweep(args)
+        return
+    if args.dense_sweep:
+        run_dense_sweep(args)
         return
     workload = args.workload or (DEFAULT_WORKLOAD if args.gpus == 1 else EP_WORKLOAD)
     spec = WORKLOADS[workload]

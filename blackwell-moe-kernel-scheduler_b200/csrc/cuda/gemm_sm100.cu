@@ -54,8 +54,11 @@ struct Config {
   static constexpr uint32_t kGroup = PAIR ? 2 : 1;
   static constexpr uint32_t kBRows = TILE_N / kGroup;           // B rows this CTA loads
   static constexpr uint32_t kBBytes = kBRows * kBlockK * 2;
-  static constexpr uint32_t kStages = (kABytes + kBBytes) == 49152 ? 4 : 6;
   static constexpr uint32_t kCtaStageBytes = kABytes + kBBytes;  // bytes this CTA loads
+  // As many stages as 192 KiB hold: 4 of 48 KiB (128 x 256), 6 of 32 KiB (128 x 128 and
+  // the pair), 8 of 24 KiB (128 x 64, the narrow tile that spreads a small-M weight
+  // stream over all SMs and keeps 64 KiB of it in flight per SM).
+  static constexpr uint32_t kStages = (192u * 1024u) / kCtaStageBytes;
   static constexpr uint32_t kTxBytes = kCtaStageBytes * kGroup;  // bytes counted on the full barrier
   static constexpr uint32_t kTmemCols = 2 * TILE_N;
   // Offsets from the 1024-byte aligned base of dynamic shared memory.
@@ -769,11 +772,13 @@ cudaError_t launch_impl(const GemmParams& params, uint32_t units, cudaStream_t s
 
 uint32_t gemm_smem_bytes(uint32_t tile_n, uint32_t cta_group) {
   if (cta_group == 2) return Config<256, true>::kDynamicSmem;
+  if (tile_n == 64) return Config<64, false>::kDynamicSmem;
   return tile_n == 256 ? Config<256, false>::kDynamicSmem : Config<128, false>::kDynamicSmem;
 }
 
 uint32_t gemm_stage_count(uint32_t tile_n, uint32_t cta_group) {
   if (cta_group == 2) return Config<256, true>::kStages;
+  if (tile_n == 64) return Config<64, false>::kStages;
   return tile_n == 256 ? Config<256, false>::kStages : Config<128, false>::kStages;
 }
 
@@ -781,6 +786,7 @@ cudaError_t preload_gemm_kernels() {
   cudaError_t rc = preload_one(grouped_gemm_kernel<256, true, false>);
   if (rc == cudaSuccess) rc = preload_one(grouped_gemm_kernel<256, false, false>);
   if (rc == cudaSuccess) rc = preload_one(grouped_gemm_kernel<128, false, false>);
+  if (rc == cudaSuccess) rc = preload_one(grouped_gemm_kernel<64, false, false>);
   if (rc == cudaSuccess) rc = preload_one(grouped_gemm_kernel<256, true, true>);
   if (rc == cudaSuccess) rc = preload_one(grouped_gemm_kernel<256, false, true>);
   return rc;
@@ -798,6 +804,7 @@ cudaError_t launch_grouped_gemm(const GemmParams& params, uint32_t tile_n,
   if (cta_group == 2 && tile_n == 256) return launch_impl<256, true, false>(params, units, stream);
   if (cta_group == 1 && tile_n == 256) return launch_impl<256, false, false>(params, units, stream);
   if (cta_group == 1 && tile_n == 128) return launch_impl<128, false, false>(params, units, stream);
+  if (cta_group == 1 && tile_n == 64) return launch_impl<64, false, false>(params, units, stream);
   return cudaErrorInvalidValue;
 }
 

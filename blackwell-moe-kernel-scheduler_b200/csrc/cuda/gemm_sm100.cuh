@@ -90,7 +90,7 @@ struct GemmParams {
 //   10 MMA lane issuing tcgen05.mma / commit
 constexpr uint32_t kTraceWords = 16;
 
-// Dynamic shared memory / operand stages for a tile width (128 or 256) and CTA
+// Dynamic shared memory / operand stages for a tile width (64, 128 or 256) and CTA
 // group (1 = single CTA, 2 = CTA pair computing 256-row tiles; needs tile_n 256).
 uint32_t gemm_smem_bytes(uint32_t tile_n, uint32_t cta_group);
 uint32_t gemm_stage_count(uint32_t tile_n, uint32_t cta_group);

@@ -247,7 +247,9 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
   if (a.data_type != 0) return BMOE_UNSUPPORTED_DATA_TYPE;
   if (a.scheduler > BMOE_SCHED_CLC) return BMOE_UNSUPPORTED_SCHEDULER;
   if (a.experts > BMOE_WORKLIST_MAX_EXPERTS) return BMOE_INVALID_ARGUMENT;
-  if (a.tile_n != 0 && a.tile_n != 128 && a.tile_n != 256) return BMOE_INVALID_ARGUMENT;
+  if (a.tile_n != 0 && a.tile_n != 64 && a.tile_n != 128 && a.tile_n != 256) {
+    return BMOE_INVALID_ARGUMENT;
+  }
   if (a.cta_group > 2) return BMOE_INVALID_ARGUMENT;
   // CTA pairs compute 256 x 256 tiles; a narrower tile has no pair variant.
   if (a.cta_group == 2 && a.tile_n != 0 && a.tile_n != 256) return BMOE_INVALID_ARGUMENT;
@@ -287,7 +289,8 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
 
   // ---- engine configuration ----
   const bool out_f32 = a.output_f32 != 0;
-  if (out_f32 && a.tile_n == 128) return BMOE_INVALID_ARGUMENT;  // FP32 epilogue: 256-wide tiles
+  // FP32 epilogue: 256-wide tiles only
+  if (out_f32 && a.tile_n != 0 && a.tile_n != 256) return BMOE_INVALID_ARGUMENT;
   // cta_group 0 = choose: CTA pairs (256-row tiles, a third less operand traffic
   // per FLOP) unless 256-row tiles would pad the routed rows by more than 10 %
   // over 128-row tiles, as they do for small-M (decode-like) routing.
@@ -303,9 +306,29 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
     cta_group = (pair_ok && padded256 * 10 <= padded128 * 11) ? 2u : 1u;
   }
   const uint32_t tile_m = 128 * cta_group;
-  const uint32_t tile_n =
-      (cta_group == 2 || out_f32) ? 256u
-                                  : (a.tile_n != 0 ? a.tile_n : (a.n <= 128 ? 128u : 256u));
+  uint32_t tile_n = 256u;
+  if (cta_group == 1 && !out_f32) {
+    if (a.tile_n != 0) {
+      tile_n = a.tile_n;
+    } else {
+      // More tiles than SMs: 256-column tiles (fewest operand bytes per FLOP). Fewer:
+      // the launch is one wave and is bound by how many bytes of the weight stream
+      // each CTA keeps in flight, so the tiles are narrowed (128, then 64 columns) as
+      // long as they still fit one wave. The k order of a tile does not depend on its
+      // width, so results do not change.
+      const uint32_t wave = a.cta_count != 0 ? a.cta_count : static_cast<uint32_t>(sm_count);
+      tile_n = 256u;
+      if (bmoe_host_tile_count(a.tokens_per_expert, a.experts, a.n, tile_m, 256u) < wave) {
+        for (uint32_t width = 128u; width >= 64u; width /= 2) {
+          if (bmoe_host_tile_count(a.tokens_per_expert, a.experts, a.n, tile_m, width) > wave) {
+            break;
+          }
+          tile_n = width;
+        }
+      }
+      if (a.n <= 64) tile_n = 64u;
+    }
+  }
   const uint32_t raster =
       a.raster_along_m < 0 ? BMOE_RASTER_M_FASTEST
                            : (a.raster_along_m != 0 ? BMOE_RASTER_M_FASTEST

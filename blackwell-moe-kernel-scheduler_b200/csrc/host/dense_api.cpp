@@ -51,7 +51,10 @@ struct DensePlanState {
     c.k = args.k;
     c.scheduler = BMOE_SCHED_CLC;  // the reference collectives use the CLC tile scheduler
     c.cta_group = cta_group;
-    c.tile_n = 256;
+    // Pairs compute 256 x 256 tiles; the single-CTA plan lets the engine narrow the
+    // tile (256 / 128 / 64 columns) until every SM has one, which is what a small-M
+    // problem needs to stream its weights at full memory bandwidth.
+    c.tile_n = cta_group == 2 ? 256u : 0u;
     c.raster_along_m = -1;
     c.output_f32 = output_f32 ? 1u : 0u;
     c.stream = args.stream;

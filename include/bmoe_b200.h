@@ -312,8 +312,10 @@ typedef struct bmoe_gemm_args {
   uint32_t claim_size;
   uint32_t hybrid_tail_tiles;
   uint32_t cta_count;
-  uint32_t tile_n;
-  uint32_t cta_group;
+  uint32_t tile_n;    /* 64, 128 or 256 output columns per tile; 0 = the widest of them
+                         that still yields at least one tile per SM (single-CTA tiles) */
+  uint32_t cta_group; /* 1 = 128-row tiles, 2 = CTA pairs computing 256 x 256 tiles,
+                         0 = chosen from the routing (pairs unless they pad > 10 % more) */
   int32_t raster_along_m;
   uint32_t output_f32; /* 0: D is BF16 (reference contract); 1: D is row-major FP32,
                           the unrounded accumulators (direct_cute_gemm.cuh:16-18) */

@@ -21,9 +21,9 @@ REFERENCE_ROOT = Path(os.environ.get("BMOE_REFERENCE_ROOT", "/root/reference"))
 
 
 def _run(cmd: list[str]) -> None:
-    proc = subprocess.run(cmd, capture_output=True, text=True)
+    proc = subprocess.run(cmd, capture_output=True, text=True, errors="replace")
     if proc.returncode != 0:
-        raise RuntimeError(f"{' '.join(cmd)}\n{proc.stdout}\n{proc.stderr}")
+        raise RuntimeError(f"{' '.join(cmd)}\n{proc.stdout}\n{proc.stderr[-4000:]}")
 
 
 def _stale(target: Path, deps: list[Path]) -> bool:
@@ -94,7 +94,64 @@ def build_reference_harness() -> list[Path]:
     return built
 
 
+def cutlass_include_dirs() -> list[Path]:
+    """CUTLASS / CuTe header trees that happen to ship inside installed Python packages
+    (the reference pins CUTLASS v4.6.0 and fetches it from the network,
+    cmake/Dependencies.cmake:6-13; the copy found here may be another 4.x)."""
+    import site
+
+    for base in site.getsitepackages():
+        root = Path(base) / "flashinfer" / "data" / "cutlass"
+        if (root / "include" / "cutlass" / "cutlass.h").exists():
+            return [root / "include", root / "tools" / "util" / "include"]
+    return []
+
+
+# The reference's OWN sm_100a dense kernel (CUTLASS 1-SM collective, cluster 1x1x1,
+# src/kernels/sm100_dense_gemm.cu) with its own benchmark and known-answer test,
+# compiled unmodified against the REFERENCE's headers: the comparison arm of the dense
+# M-sweep. The 2-SM collective is left out on purpose (it relies on TMA multicast
+# inside CUTLASS, include/blackwell_moe/kernels/sm100_2sm_gemm.cuh:9-12).
+NATIVE_DENSE = {
+    "ref_native_sm100_dense_benchmark": "benchmarks/sm100_dense_benchmark.cu",
+    "ref_native_sm100_dense_test": "tests/test_sm100_dense_correctness.cu",
+}
+
+
+def build_reference_native_dense() -> list[Path]:
+    """nvcc-compile the reference's CUTLASS dense kernel + its benchmark / test.
+    Returns the programs present afterwards; raises with the compiler's output if the
+    headers found do not compile it."""
+    if not reference_available():
+        return sorted(HARNESS_DIR.glob("ref_native_*")) if HARNESS_DIR.exists() else []
+    includes = cutlass_include_dirs()
+    if not includes:
+        return []
+    HARNESS_DIR.mkdir(parents=True, exist_ok=True)
+    kernel_src = REFERENCE_ROOT / "src" / "kernels" / "sm100_dense_gemm.cu"
+    shim = ORACLE_DIR / "ref_status_shim.cpp"
+    flags = ["-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-std=c++17",
+             "--expt-relaxed-constexpr", "-diag-suppress", "20012",
+             f"-I{REFERENCE_ROOT / 'include'}", *[f"-I{d}" for d in includes],
+             "-DBLACKWELL_MOE_CUTLASS_REVISION=\"4.5.0-vendored-headers\""]
+    kernel_obj = REF_DIR / "ref_native_sm100_dense_gemm.o"
+    if _stale(kernel_obj, [kernel_src]):
+        _run(["nvcc", *flags, "-c", str(kernel_src), "-o", str(kernel_obj)])
+    shim_obj = REF_DIR / "ref_status_shim.o"
+    if _stale(shim_obj, [shim]):
+        _run(["nvcc", *flags, "-x", "cu", "-c", str(shim), "-o", str(shim_obj)])
+    built = []
+    for name, rel in NATIVE_DENSE.items():
+        src = REFERENCE_ROOT / rel
+        out = HARNESS_DIR / name
+        if _stale(out, [src, kernel_obj, shim_obj]):
+            _run(["nvcc", *flags, str(src), str(shim_obj), str(kernel_obj), "-o", str(out)])
+        built.append(out)
+    return built
+
+
 if __name__ == "__main__":
     print(build_oracle())
     print(build_reference())
     print(build_reference_harness())
+    print(build_reference_native_dense())

@@ -93,7 +93,7 @@ def test_reference_known_answers_bit_exact(engine, golden, name):
     counts, n, k, a_bits, w_bits = support.kat_inputs(name)
     a = torch.from_numpy(a_bits.view(np.int16).copy()).view(torch.bfloat16)
     w = torch.from_numpy(w_bits.view(np.int16).copy()).view(torch.bfloat16)
-    for tile_n, group in ((0, 0), (128, 1), (256, 1), (256, 2)):
+    for tile_n, group in ((0, 0), (64, 1), (128, 1), (256, 1), (256, 2)):
         out = run_engine(engine, a, w, counts, tile_n=tile_n, cta_group=group)
         assert out["stats"].active_experts == sum(c > 0 for c in counts)
         assert support.sha(out["bits"].reshape(-1)) == golden["gemm_kats"][name]["d_sha256"]
@@ -169,9 +169,9 @@ def test_ragged_cases_all_policies(engine, oracle, counts, n, k):
                           oracle.build_tiles(counts, n, 128, base["stats"].tile_n))
     assert np.all(base["visits"] == 1)
     assert int(base["cta"].sum()) == base["stats"].total_tiles
-    # (tile_n, cta_group): single-CTA tiles of 128 x 128 / 128 x 256, and CTA pairs
-    # computing 256 x 256 tiles. All of them must agree bit for bit.
-    for tile_n, group in ((128, 1), (256, 1), (256, 2)):
+    # (tile_n, cta_group): single-CTA tiles of 128 x 64 / 128 x 128 / 128 x 256, and CTA
+    # pairs computing 256 x 256 tiles. All of them must agree bit for bit.
+    for tile_n, group in ((64, 1), (128, 1), (256, 1), (256, 2)):
         for raster in (0, 1):
             for policy, opts in POLICIES:
                 out = run_engine(engine, a, w, counts, policy, observers=True, tile_n=tile_n,
@@ -319,7 +319,8 @@ ALL_VARIANTS = [("static_persistent", {}), ("dynamic_queue", {}),
                 ("compacted", {}), ("clc", {}), ("auto", {}),
                 ("expert_order", {"cta_group": 1}), ("dynamic_queue", {"cta_group": 1}),
                 ("expert_order", {"cta_group": 2}), ("dynamic_queue", {"cta_group": 2}),
-                ("clc", {"cta_group": 2}), ("expert_order", {"cta_group": 1, "tile_n": 128})]
+                ("clc", {"cta_group": 2}), ("expert_order", {"cta_group": 1, "tile_n": 128}),
+                ("dynamic_queue", {"cta_group": 1, "tile_n": 64})]
 
 
 def test_decode_shape_properties(engine, oracle, golden):
