@@ -230,6 +230,10 @@ class GemmArgs(C.Structure):
         ("raster_along_m", C.c_int32),
         ("output_f32", C.c_uint32),
         ("stream", C.c_void_p),
+        ("packed_a", C.c_void_p),
+        ("packed_rows", C.c_uint64),
+        ("results_pushed", C.c_uint32),
+        ("reserved0", C.c_uint32),
     ]
 
 

@@ -399,8 +399,11 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       }
       if (tile == kSentinel) break;
 
-      const CUtensorMap* const map_a = p.tmap_a + expert;
+      const bool packed_a = p.a_row_offsets != nullptr;
+      const CUtensorMap* const map_a = packed_a ? p.tmap_a : p.tmap_a + expert;
       const CUtensorMap* const map_b = p.tmap_b + expert;
+      const uint32_t a_row0 =
+          packed_a ? row0 + static_cast<uint32_t>(p.a_row_offsets[expert]) : row0;
       // Gated launch: the rows of this tile were stored by other GPUs; order this
       // warp's TMA loads after the scheduler's observation of their flags.
       if (p.gate_flags != nullptr) ptx::fence_proxy_async_all();
@@ -428,11 +431,11 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             // Both CTAs' bytes are counted on the leader's barrier.
             if (leader) ptx::mbar_arrive_expect_tx(bar_full(stage), Cfg::kTxBytes);
             const uint32_t full = ptx::map_to_cta(bar_full(stage), 0);
-            ptx::tma_load_2d_pair(dst_a, map_a, full, k0, static_cast<int32_t>(row0));
+            ptx::tma_load_2d_pair(dst_a, map_a, full, k0, static_cast<int32_t>(a_row0));
             ptx::tma_load_2d_pair(dst_b, map_b, full, k0, static_cast<int32_t>(col0));
           } else {
             ptx::mbar_arrive_expect_tx(bar_full(stage), Cfg::kTxBytes);
-            ptx::tma_load_2d(dst_a, map_a, bar_full(stage), k0, static_cast<int32_t>(row0));
+            ptx::tma_load_2d(dst_a, map_a, bar_full(stage), k0, static_cast<int32_t>(a_row0));
             ptx::tma_load_2d(dst_b, map_b, bar_full(stage), k0, static_cast<int32_t>(col0));
           }
         }

@@ -79,6 +79,12 @@ struct GemmParams {
   uint64_t push_rows_cap;           // rows each result buffer holds
   uint32_t push_vec_per_row;        // n / 8
   uint32_t push_ranks;
+  // Optional packed A: when non-null, tmap_a[0] describes ONE row-major buffer that
+  // holds the rows of all experts back to back and a_row_offsets[e] is the first row of
+  // expert e in it (the worklist builder's row-offset array). A tile at an expert's
+  // ragged edge then also loads rows of the next expert; they only feed accumulator
+  // rows beyond valid_m, which are never written.
+  const unsigned long long* a_row_offsets;
 };
 
 // Words per CTA of GemmParams::trace (SM cycles):

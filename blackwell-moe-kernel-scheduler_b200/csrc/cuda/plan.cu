@@ -129,6 +129,12 @@ struct bmoe_plan {
   DeviceBlock worklist;   // bmoe_tile [capacity]
   DeviceBlock workspace;  // worklist builder arrays
 
+  // What the B descriptors in the staging area were encoded for (reused while the
+  // expert's weight pointer, the shape and the box do not change).
+  std::vector<const void*> b_encoded_for;
+  uint32_t b_key_n = 0, b_key_k = 0, b_key_box = 0, b_key_experts = 0;
+  bool needs_push = false;   // results_pushed: run() only after set_push
+
   bmoe::GemmParams params{};
   uint32_t units = 0;      // persistent CTAs or CTA pairs (tile count for CLC)
   uint32_t tile_n = 0;
@@ -139,6 +145,7 @@ struct bmoe_plan {
   void release_all() {
     meta.release();
     staging.release();
+    b_encoded_for.clear();
     worklist.release();
     workspace.release();
     if (setup_done != nullptr) cudaEventDestroy(setup_done);
@@ -239,11 +246,15 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
   const bmoe_gemm_args& a = *args;
 
   // ---- argument checks, in the reference's order ----
-  if (a.a == nullptr || a.b == nullptr || a.d == nullptr ||
+  const bool packed = a.packed_a != nullptr;
+  const bool pushed = a.results_pushed != 0;
+  if ((a.a == nullptr && !packed) || a.b == nullptr || (a.d == nullptr && !pushed) ||
       a.tokens_per_expert == nullptr || a.experts == 0 || a.n == 0 || a.k == 0 ||
       a.n % 8 != 0 || a.k % 8 != 0) {
     return BMOE_INVALID_ARGUMENT;
   }
+  if (packed && (misaligned16(a.packed_a) || a.packed_rows == 0)) return BMOE_INVALID_ARGUMENT;
+  if (pushed && a.output_f32 != 0) return BMOE_INVALID_ARGUMENT;
   if (a.data_type != 0) return BMOE_UNSUPPORTED_DATA_TYPE;
   if (a.scheduler > BMOE_SCHED_CLC) return BMOE_UNSUPPORTED_SCHEDULER;
   if (a.experts > BMOE_WORKLIST_MAX_EXPERTS) return BMOE_INVALID_ARGUMENT;
@@ -269,14 +280,17 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
   }
 
   uint32_t active = 0;
+  uint64_t routed_rows = 0;
   for (uint32_t e = 0; e < a.experts; ++e) {
     if (a.tokens_per_expert[e] == 0) continue;
-    if (a.a[e] == nullptr || a.b[e] == nullptr || a.d[e] == nullptr ||
-        misaligned16(a.a[e]) || misaligned16(a.b[e]) || misaligned16(a.d[e])) {
+    if ((!packed && (a.a[e] == nullptr || misaligned16(a.a[e]))) || a.b[e] == nullptr ||
+        misaligned16(a.b[e]) || (!pushed && (a.d[e] == nullptr || misaligned16(a.d[e])))) {
       return BMOE_INVALID_ARGUMENT;
     }
+    routed_rows += a.tokens_per_expert[e];
     ++active;
   }
+  if (packed && routed_rows > a.packed_rows) return BMOE_INVALID_ARGUMENT;
   plan->stats.active_experts = active;
   plan->default_stream = static_cast<cudaStream_t>(a.stream);
   plan->setup_stream = plan->default_stream;
@@ -352,6 +366,7 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
   const size_t off_counts = 512;
   const size_t off_maps = (off_counts + sizeof(uint32_t) * a.experts + 127) / 128 * 128;
   const size_t meta_bytes = off_maps + map_bytes;
+  const void* const staging_before = plan->staging.ptr;
   if (!plan->meta.reserve(meta_bytes) || !plan->staging.reserve(meta_bytes) ||
       !plan->worklist.reserve(sizeof(bmoe_tile) * static_cast<size_t>(tiles)) ||
       !plan->workspace.reserve(layout.bytes)) {
@@ -365,6 +380,7 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
     // the previous set-up copy still reads the staging area
     return BMOE_CUDA_ERROR;
   }
+  const bool staging_moved = plan->staging.ptr != staging_before;
   cudaStream_t stream = plan->setup_stream;
   uint8_t* const stage = static_cast<uint8_t*>(plan->staging.ptr);
   uint8_t* const meta = static_cast<uint8_t*>(plan->meta.ptr);
@@ -378,17 +394,39 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
   CUtensorMap* const maps_a = reinterpret_cast<CUtensorMap*>(stage + off_maps);
   CUtensorMap* const maps_b = maps_a + a.experts;
   CUtensorMap* const maps_d = maps_b + a.experts;
+  // B descriptors survive in the staging area from the previous initialize when the
+  // layout of that area, the shape and the box are the same; only experts whose weight
+  // pointer changed are encoded again.
+  const uint32_t b_box = tile_n / cta_group;
+  const bool b_cache_valid = !staging_moved && plan->b_key_experts == a.experts &&
+                             plan->b_key_n == a.n && plan->b_key_k == a.k &&
+                             plan->b_key_box == b_box &&
+                             plan->b_encoded_for.size() == a.experts;
+  if (!b_cache_valid) plan->b_encoded_for.assign(a.experts, nullptr);
+  plan->b_key_experts = a.experts;
+  plan->b_key_n = a.n;
+  plan->b_key_k = a.k;
+  plan->b_key_box = b_box;
+  if (packed && !encode_matrix(&maps_a[0], a.packed_a, a.packed_rows, a.k, 128, false)) {
+    return BMOE_CUDA_ERROR;
+  }
   for (uint32_t e = 0; e < a.experts; ++e) {
     const uint64_t rows = a.tokens_per_expert[e];
     if (rows == 0) {
-      std::memset(&maps_a[e], 0, sizeof(CUtensorMap));
+      if (!packed || e != 0) std::memset(&maps_a[e], 0, sizeof(CUtensorMap));
       std::memset(&maps_b[e], 0, sizeof(CUtensorMap));
       std::memset(&maps_d[e], 0, sizeof(CUtensorMap));
+      plan->b_encoded_for[e] = nullptr;
       continue;
     }
-    if (!encode_matrix(&maps_a[e], a.a[e], rows, a.k, 128, false) ||
-        !encode_matrix(&maps_b[e], a.b[e], a.n, a.k, tile_n / cta_group, false) ||
-        !encode_matrix(&maps_d[e], a.d[e], rows, a.n, 32, out_f32)) {
+    if (!packed && !encode_matrix(&maps_a[e], a.a[e], rows, a.k, 128, false)) {
+      return BMOE_CUDA_ERROR;
+    }
+    if (plan->b_encoded_for[e] != a.b[e]) {
+      if (!encode_matrix(&maps_b[e], a.b[e], a.n, a.k, b_box, false)) return BMOE_CUDA_ERROR;
+      plan->b_encoded_for[e] = a.b[e];
+    }
+    if (!pushed && !encode_matrix(&maps_d[e], a.d[e], rows, a.n, 32, out_f32)) {
       return BMOE_CUDA_ERROR;
     }
   }
@@ -430,6 +468,12 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
   p.tile_visits = nullptr;
   p.cta_tiles = nullptr;
   p.wait_budget_ns = 1000000000ull;  // 1 s per wait, then the kernel gives up
+  if (packed) {
+    // first row of every expert in the packed buffer, as the worklist builder left it
+    p.a_row_offsets = reinterpret_cast<const unsigned long long*>(
+        static_cast<const uint8_t*>(plan->workspace.ptr) + layout.off_row_offsets);
+  }
+  plan->needs_push = pushed;
 
   plan->tile_n = tile_n;
   plan->stats_n = a.n;
@@ -507,6 +551,7 @@ int bmoe_plan_set_push(bmoe_plan* plan, const void* origin_dev,
 int bmoe_plan_run(bmoe_plan* plan, void* stream) {
   if (plan == nullptr || !plan->ready) return BMOE_INVALID_ARGUMENT;
   if (plan->stats.active_experts == 0) return BMOE_OK;
+  if (plan->needs_push && plan->params.push_origin == nullptr) return BMOE_INVALID_ARGUMENT;
   cudaStream_t s = stream == nullptr ? plan->default_stream
                                      : static_cast<cudaStream_t>(stream);
   if (s != plan->setup_stream &&

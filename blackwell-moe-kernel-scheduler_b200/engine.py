@@ -85,8 +85,15 @@ class GroupedGemmPlan:
         cta_group: int = 0,
         raster_along_m: int = -1,
         output_f32: bool = False,
+        packed_a: int = 0,
+        packed_rows: int = 0,
+        results_pushed: bool = False,
     ) -> int:
-        """Pointer-array form of the reference arguments. Returns a status."""
+        """Pointer-array form of the reference arguments. Returns a status.
+        ``packed_a`` / ``packed_rows``: base and row capacity of ONE buffer holding all
+        experts' rows back to back (one tensor map instead of one per expert; ``a_ptrs``
+        is then ignored). ``results_pushed``: no D descriptors, results leave through
+        ``set_push``."""
         experts = len(tokens_per_expert)
 
         def pointers(values):
@@ -118,14 +125,22 @@ class GroupedGemmPlan:
             raster_along_m=raster_along_m,
             output_f32=1 if output_f32 else 0,
             stream=_stream_ptr(stream),
+            packed_a=int(packed_a) or None,
+            packed_rows=int(packed_rows),
+            results_pushed=1 if results_pushed else 0,
+            reserved0=0,
         )
         return int(self._lib.bmoe_plan_initialize(self._handle, C.byref(args)))
 
-    def initialize_packed(self, a, w, d, tokens_per_expert: Sequence[int], **options) -> int:
+    def initialize_packed(self, a, w, d, tokens_per_expert: Sequence[int], *,
+                          single_a_map: bool = False, **options) -> int:
         """Packed form: ``a`` [sum M, k], ``w`` [E, n, k], ``d`` [sum M, n] CUDA BF16
         tensors, rows of expert 0 first. Row offsets are the exclusive prefix sum
         of the counts; every expert's slice starts on a 16-byte boundary because
-        k and n are multiples of 8."""
+        k and n are multiples of 8. ``single_a_map``: one tensor map over the whole of
+        ``a`` instead of one per expert (cheaper to re-plan; tiles at an expert's ragged
+        edge then also load the next expert's rows, which costs bandwidth when experts
+        have few rows and changes no result)."""
         experts = len(tokens_per_expert)
         n, k = int(w.shape[1]), int(w.shape[2])
         d_elem = 4 if options.get("output_f32") else 2
@@ -144,6 +159,8 @@ class GroupedGemmPlan:
         b_ptrs = np.uint64(w.data_ptr()) + np.arange(experts, dtype=np.uint64) * np.uint64(n * k * 2)
         d_ptrs = np.uint64(d.data_ptr()) + first_row * np.uint64(n * d_elem)
         self._keep = (a, w, d)
+        if single_a_map:
+            options.update(packed_a=a.data_ptr(), packed_rows=int(a.shape[0]))
         return self.initialize(a_ptrs, b_ptrs, d_ptrs, counts, n, k, **options)
 
     # --------------------------------------------------------------- run --

@@ -439,8 +439,12 @@ class FusedExpertParallelLayer:
 
         total_local = step["total_local"]
         if total_local:
+            # one A descriptor over the packed buffer, cached B descriptors and (when the
+            # epilogue pushes the rows) no D descriptors: a re-plan encodes next to nothing
             _capi.check(self.plan.initialize_packed(self.a, w_local, self.d, step["local_m"],
                                                     scheduler=self.scheduler, stream=main,
+                                                    single_a_map=True,
+                                                    results_pushed=self.push_results,
                                                     **self.plan_options),
                         "bmoe_plan_initialize")
             if self.world > 1:

@@ -320,6 +320,19 @@ typedef struct bmoe_gemm_args {
   uint32_t output_f32; /* 0: D is BF16 (reference contract); 1: D is row-major FP32,
                           the unrounded accumulators (direct_cute_gemm.cuh:16-18) */
   void* stream;
+  /* Packed layout (appended; zero = the pointer-array form above). When packed_a is
+   * set, the rows of all experts lie back to back in ONE row-major buffer
+   * [packed_rows, k] in expert order (row offsets = exclusive prefix sum of the
+   * counts, derived on the device); a[] is then ignored and one tensor map serves every
+   * expert, so a re-plan with new counts encodes no per-expert A descriptor. B
+   * descriptors of experts whose pointer did not change since the plan's previous
+   * initialize are reused as well. */
+  const void* packed_a;
+  uint64_t packed_rows;
+  /* 1: D is never stored through the plan (results leave through bmoe_plan_set_push,
+   * which must then be set before run); d[] is ignored and no D descriptor is made. */
+  uint32_t results_pushed;
+  uint32_t reserved0;
 } bmoe_gemm_args;
 
 /* blackwell_moe::GroupedGemmPlanStats (grouped_gemm.cuh:42-46) + extensions. */

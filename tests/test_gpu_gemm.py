@@ -189,6 +189,41 @@ def test_ragged_cases_all_policies(engine, oracle, counts, n, k):
                                            raster=raster))
 
 
+@pytest.mark.parametrize("counts,n,k", CASES[2:])
+def test_single_descriptor_over_packed_rows(engine, oracle, counts, n, k):
+    """One tensor map over the whole packed A buffer (tiles at a ragged edge then load the
+    next expert's rows into accumulator rows that are never written): same bits as one
+    descriptor per expert, for every tile shape, and again after a re-plan with other
+    counts on the same plan object (cached weight descriptors)."""
+    import torch
+
+    a, w = make_inputs(counts, n, k)
+    base = run_engine(engine, a, w, counts, "expert_order")
+    for policy, opts in (("expert_order", {"tile_n": 64, "cta_group": 1}),
+                         ("dynamic_queue", {"tile_n": 128, "cta_group": 1}),
+                         ("clc", {"cta_group": 1}), ("dynamic_queue", {"cta_group": 2})):
+        out = run_engine(engine, a, w, counts, policy, observers=True, single_a_map=True, **opts)
+        assert np.array_equal(out["bits"], base["bits"]), (policy, opts)
+        assert np.all(out["visits"] == 1)
+    # the same plan object, re-planned: shuffled counts, same weights
+    counts2 = list(reversed(counts))
+    a2, _ = make_inputs(counts2, n, k, seed=9)
+    want2 = run_engine(engine, a2, w, counts2, "expert_order")["bits"]
+    a_dev, a2_dev, w_dev = a.cuda(), a2.cuda(), w.cuda()
+    d_dev = torch.zeros(sum(counts), n, dtype=torch.bfloat16, device="cuda")
+    plan = engine.GroupedGemmPlan()
+    try:
+        for rows, bits in ((a_dev, base["bits"]), (a2_dev, want2), (a_dev, base["bits"])):
+            cts = counts if rows is a_dev else counts2
+            d_dev.fill_(float("nan"))
+            assert plan.initialize_packed(rows, w_dev, d_dev, cts, scheduler="dynamic_queue",
+                                          single_a_map=True) == 0
+            assert plan.run() == 0 and plan.poll()[0] == 0
+            assert np.array_equal(bits_of(d_dev), bits)
+    finally:
+        plan.close()
+
+
 def test_policy_specific_launch_shapes(engine):
     counts, n, k = [300, 5, 0, 300, 129], 520, 128
     a, w = make_inputs(counts, n, k)
