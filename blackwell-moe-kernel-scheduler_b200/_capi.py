@@ -143,7 +143,17 @@ class EpRouteArgs(C.Structure):
         ("top_k", C.c_uint32), ("experts", C.c_uint32), ("ranks", C.c_uint32),
         ("self", C.c_uint32), ("groups", C.c_uint32),
         ("stream", C.c_void_p),
+        ("staging_row_base_dev", C.c_void_p), ("staging_rows_cap", C.c_uint64),
     ]
+
+
+class CopyItem(C.Structure):
+    _fields_ = [("dst", C.c_void_p), ("src", C.c_void_p), ("bytes", C.c_uint64),
+                ("stream", C.c_uint32), ("reserved", C.c_uint32)]
+
+
+COPY_ITEM_DTYPE = [("dst", "<u8"), ("src", "<u8"), ("bytes", "<u8"), ("stream", "<u4"),
+                   ("reserved", "<u4")]
 
 
 class EpDispatchArgs(C.Structure):
@@ -172,7 +182,12 @@ class EpReturnArgs(C.Structure):
 
 
 EP_MAX_GROUPS = 16
-EP_LOCAL, EP_REMOTE, EP_ALL = 0, 1, 2
+EP_LOCAL, EP_REMOTE, EP_ALL, EP_PACK = 0, 1, 2, 3
+
+
+def ep_copy_flags(ranks: int) -> int:
+    """First slot of the flag plane for rows that arrive as peer copies."""
+    return (EP_MAX_GROUPS + 1) * ranks
 
 
 class WorklistTotals(C.Structure):
@@ -372,6 +387,8 @@ SIGNATURES = {
     ),
     "bmoe_plan_set_gate": (
         C.c_int, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p]),
+    "bmoe_plan_set_gate_copies": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "bmoe_peer_copy_batch": (C.c_int, [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32]),
     "bmoe_plan_set_push": (
         C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint64]),
     "bmoe_peer_alloc": (C.c_int, [C.c_uint64, _P(C.c_void_p), C.c_void_p]),

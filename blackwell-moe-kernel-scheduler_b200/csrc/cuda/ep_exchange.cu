@@ -111,9 +111,12 @@ struct RouteArgs {
   const uint8_t* group_of;     // [experts] group of the expert on its owner
   uint32_t* cursor;            // [experts] rows handed out so far (zero at step start)
   long long* const* origin_bases;  // [ranks] origin record per packed row
-  RouteEntry* entries;         // [assignments] bucketed: groups 0..G-1 (remote), G (local)
-  const uint32_t* bucket_offset;   // [groups + 2] from the host's count matrix
-  uint32_t* bucket_fill;       // [groups + 1] zero at step start
+  RouteEntry* entries;         // [assignments] bucketed: groups 0..G-1 (remote), G (local),
+                               // G + 1 (rows of copy-engine blocks, into the staging buffer)
+  const uint32_t* bucket_offset;   // [groups + 3] from the host's count matrix
+  uint32_t* bucket_fill;       // [groups + 2] zero at step start
+  const int64_t* staging_row_base;  // [experts] >= 0: copy-engine block, first staging row
+  uint64_t staging_rows_cap;
   int32_t* dst_rank_out;       // [assignments] or nullptr: where each assignment went
   int64_t* dst_row_out;        // [assignments] or nullptr
   uint64_t assignments;
@@ -148,6 +151,11 @@ __global__ void __launch_bounds__(256) ep_route_kernel(RouteArgs a) {
         if (to >= 0 && static_cast<uint32_t>(to) < a.ranks) {
           bucket = static_cast<uint32_t>(to) == a.self ? a.groups : a.group_of[e];
           if (bucket > a.groups) bucket = 0xffffffffu;
+          // a block that travels as one peer copy is first packed into local staging
+          if (bucket < a.groups && a.staging_row_base != nullptr &&
+              a.staging_row_base[e] >= 0) {
+            bucket = a.groups + 1;
+          }
         }
       }
     }
@@ -188,6 +196,16 @@ __global__ void __launch_bounds__(256) ep_route_kernel(RouteArgs a) {
     entry.to = static_cast<uint32_t>(to);
     entry.row = static_cast<uint32_t>(row);
     entry.pad = 0;
+    if (bucket == a.groups + 1) {
+      // staged row: same position inside the block as in the owner's A
+      const int64_t staged = a.staging_row_base[e] + (row - a.row_base[e]);
+      entry.to = a.self;
+      entry.row = static_cast<uint32_t>(staged);
+      if (staged < 0 || static_cast<uint64_t>(staged) >= a.staging_rows_cap) {
+        entry.token = 0xffffffffu;
+        entry.to = 0xffffffffu;   // no rank owns it: the copy kernels skip the entry
+      }
+    }
     a.entries[slot] = entry;
     if (a.dst_rank_out != nullptr) a.dst_rank_out[i] = to;
     if (a.dst_row_out != nullptr) a.dst_row_out[i] = row;
@@ -224,8 +242,12 @@ struct DispatchArgs {
 __global__ void __launch_bounds__(1024) ep_dispatch_kernel(DispatchArgs a) {
   const uint32_t lane = threadIdx.x & 31;
   const uint32_t span = a.span;
-  const uint32_t first_bucket = a.mode == BMOE_EP_LOCAL ? a.groups : 0u;
-  const uint32_t end_bucket = a.mode == BMOE_EP_REMOTE ? a.groups : a.groups + 1u;
+  const uint32_t first_bucket = a.mode == BMOE_EP_LOCAL  ? a.groups
+                                : a.mode == BMOE_EP_PACK ? a.groups + 1u
+                                                         : 0u;
+  const uint32_t end_bucket = a.mode == BMOE_EP_REMOTE ? a.groups
+                              : a.mode == BMOE_EP_PACK ? a.groups + 2u
+                                                       : a.groups + 1u;
   for (uint32_t b = first_bucket; b < end_bucket; ++b) {
     const uint32_t begin = a.bucket_offset[b];
     const uint32_t count = a.bucket_offset[b + 1] - begin;
@@ -509,6 +531,8 @@ extern "C" int bmoe_ep_route(const bmoe_ep_route_args* args) {
   a.ranks = c.ranks;
   a.self = c.self;
   a.groups = c.groups;
+  a.staging_row_base = c.staging_row_base_dev;
+  a.staging_rows_cap = c.staging_rows_cap;
   const uint64_t want = (c.assignments + 255) / 256;
   const uint64_t cap = 4ull * bmoe::device_sms();
   const uint32_t grid = static_cast<uint32_t>(want < cap ? want : cap);
@@ -520,10 +544,11 @@ extern "C" int bmoe_ep_dispatch(const bmoe_ep_dispatch_args* args) {
   if (args == nullptr) return BMOE_INVALID_ARGUMENT;
   const bmoe_ep_dispatch_args& c = *args;
   if (c.ranks == 0 || c.self >= c.ranks || c.groups == 0 || c.groups > BMOE_EP_MAX_GROUPS ||
-      c.mode > BMOE_EP_ALL || c.row_bytes == 0 || c.row_bytes % 16 != 0 ||
+      c.mode > BMOE_EP_PACK || c.row_bytes == 0 || c.row_bytes % 16 != 0 ||
+      (c.mode == BMOE_EP_PACK && c.bulk_copies != 0) ||
       c.a_bases_dev == nullptr || c.entries_dev == nullptr || c.bucket_offset_dev == nullptr ||
       c.chunk_next_dev == nullptr || (c.assignments != 0 && c.x_dev == nullptr) ||
-      (c.ranks > 1 && c.mode != BMOE_EP_LOCAL &&
+      (c.ranks > 1 && (c.mode == BMOE_EP_REMOTE || c.mode == BMOE_EP_ALL) &&
        (c.flag_bases_dev == nullptr || c.group_done_dev == nullptr))) {
     return BMOE_INVALID_ARGUMENT;
   }
@@ -556,11 +581,14 @@ extern "C" int bmoe_ep_dispatch(const bmoe_ep_dispatch_args* args) {
   }
   const uint64_t sms = bmoe::device_sms();
   const uint64_t cap = c.max_ctas != 0 ? c.max_ctas
-                       : c.mode == BMOE_EP_LOCAL ? 4 * sms : (sms * 7 / 16 > 0 ? sms * 7 / 16 : 1);
+                       : (c.mode == BMOE_EP_LOCAL || c.mode == BMOE_EP_PACK)
+                           ? 4 * sms
+                           : (sms * 7 / 16 > 0 ? sms * 7 / 16 : 1);
   // Entries per claim: few enough that every warp of the grid gets several claims per
   // bucket (the buckets of a step hold about assignments / buckets entries each).
   const uint64_t warps_cap = cap * (threads / 32);
-  const uint64_t per_bucket = c.assignments / (c.mode == BMOE_EP_LOCAL ? 1 : c.groups) + 1;
+  const uint64_t per_bucket =
+      c.assignments / ((c.mode == BMOE_EP_LOCAL || c.mode == BMOE_EP_PACK) ? 1 : c.groups) + 1;
   uint32_t span = 8;
   while (span > 1 && per_bucket / span < 4 * warps_cap) span >>= 1;
   a.span = span;
@@ -651,6 +679,25 @@ extern "C" int bmoe_ep_wait_flags(const uint32_t* flags_dev, uint32_t first_slot
   bmoe::ep_wait_flags_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
       flags_dev, first_slot, ranks, self, epoch, budget_ns, status_dev);
   return cudaPeekAtLastError() == cudaSuccess ? BMOE_OK : BMOE_CUDA_ERROR;
+}
+
+extern "C" int bmoe_peer_copy_batch(const bmoe_copy_item* items, uint32_t count,
+                                    void* const* streams, uint32_t stream_count) {
+  if (count == 0) return BMOE_OK;
+  if (items == nullptr || streams == nullptr || stream_count == 0) return BMOE_INVALID_ARGUMENT;
+  for (uint32_t i = 0; i < count; ++i) {
+    const bmoe_copy_item& item = items[i];
+    if (item.bytes == 0) continue;
+    if (item.dst == nullptr || item.src == nullptr || item.stream >= stream_count) {
+      return BMOE_INVALID_ARGUMENT;
+    }
+    // Unified addressing tells the runtime which GPUs the two pointers live on.
+    if (cudaMemcpyAsync(item.dst, item.src, item.bytes, cudaMemcpyDefault,
+                        static_cast<cudaStream_t>(streams[item.stream])) != cudaSuccess) {
+      return BMOE_CUDA_ERROR;
+    }
+  }
+  return BMOE_OK;
 }
 
 namespace bmoe {

@@ -233,23 +233,30 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         const uint32_t g = p.gate_group_of[expert];
         if (g >= 32 || ((groups_ready >> g) & 1u) != 0) return true;
         uint64_t start = 0;
-        for (uint32_t r = 0; r < p.gate_ranks; ++r) {
-          if (r == p.gate_self) continue;
-          const uint32_t* flag = p.gate_flags + g * p.gate_ranks + r;
-          for (uint32_t spin = 1;; ++spin) {
-            if (static_cast<int32_t>(ptx::ld_acquire_sys_u32(flag) - p.gate_epoch) >= 0) break;
-            if ((spin & 0xf) == 0) {
-              if (*abort_word != 0) return false;
-              const uint64_t now = ptx::global_timer_ns();
-              if (start == 0) {
-                start = now;
-              } else if (now - start > budget) {
-                *abort_word = 1;
-                report(p, kSiteSchedGate, 0, expert, g, r);
-                return false;
+        // plane 0: rows pushed by the sources' SMs; plane 1: rows sent as peer copies
+        const uint32_t copy_mask = p.gate_copy_mask != nullptr ? p.gate_copy_mask[g] : 0u;
+        for (uint32_t plane = 0; plane < 2; ++plane) {
+          if (plane == 1 && copy_mask == 0) break;
+          for (uint32_t r = 0; r < p.gate_ranks; ++r) {
+            if (r == p.gate_self) continue;
+            if (plane == 1 && ((copy_mask >> r) & 1u) == 0) continue;
+            const uint32_t* flag =
+                p.gate_flags + plane * p.gate_copy_plane + g * p.gate_ranks + r;
+            for (uint32_t spin = 1;; ++spin) {
+              if (static_cast<int32_t>(ptx::ld_acquire_sys_u32(flag) - p.gate_epoch) >= 0) break;
+              if ((spin & 0xf) == 0) {
+                if (*abort_word != 0) return false;
+                const uint64_t now = ptx::global_timer_ns();
+                if (start == 0) {
+                  start = now;
+                } else if (now - start > budget) {
+                  *abort_word = 1;
+                  report(p, kSiteSchedGate, 0, expert, g, r | (plane << 8));
+                  return false;
+                }
               }
+              __nanosleep(200);
             }
-            __nanosleep(200);
           }
         }
         // The rows were written by other GPUs' ordinary stores; the TMA loads that

@@ -69,6 +69,11 @@ struct GemmParams {
   uint32_t gate_epoch;
   uint32_t gate_ranks;
   uint32_t gate_self;
+  // Rows that arrive as peer copies have a flag plane of their own behind the first one
+  // (gate_copy_plane slots further): group g also waits for the sources whose bit is set
+  // in gate_copy_mask[g]. nullptr = no such rows.
+  const uint32_t* gate_copy_mask;
+  uint32_t gate_copy_plane;
   // Optional result push (expert-parallel exchange, BF16 output): instead of the TMA
   // store into D, the epilogue writes every valid tile row to row `assignment` of its
   // origin rank's result buffer (plain 16-byte stores, 128 contiguous bytes per row

@@ -512,6 +512,8 @@ int bmoe_plan_set_gate(bmoe_plan* plan, const uint32_t* flags_dev, uint32_t epoc
                        uint32_t ranks, uint32_t self, const uint8_t* group_of_expert_dev) {
   if (plan == nullptr || !plan->ready) return BMOE_INVALID_ARGUMENT;
   bmoe::GemmParams& p = plan->params;
+  p.gate_copy_mask = nullptr;
+  p.gate_copy_plane = 0;
   if (flags_dev == nullptr || ranks <= 1) {
     p.gate_flags = nullptr;
     p.gate_group_of = nullptr;
@@ -523,6 +525,15 @@ int bmoe_plan_set_gate(bmoe_plan* plan, const uint32_t* flags_dev, uint32_t epoc
   p.gate_epoch = epoch;
   p.gate_ranks = ranks;
   p.gate_self = self;
+  return BMOE_OK;
+}
+
+int bmoe_plan_set_gate_copies(bmoe_plan* plan, const uint32_t* copy_mask_dev) {
+  if (plan == nullptr || !plan->ready) return BMOE_INVALID_ARGUMENT;
+  bmoe::GemmParams& p = plan->params;
+  if (copy_mask_dev != nullptr && p.gate_flags == nullptr) return BMOE_INVALID_ARGUMENT;
+  p.gate_copy_mask = copy_mask_dev;
+  p.gate_copy_plane = copy_mask_dev != nullptr ? BMOE_EP_COPY_FLAGS(p.gate_ranks) : 0u;
   return BMOE_OK;
 }
 

@@ -173,6 +173,11 @@ class GroupedGemmPlan:
         return int(self._lib.bmoe_plan_set_gate(self._handle, flags_ptr, epoch, ranks, self_rank,
                                                 group_of_ptr))
 
+    def set_gate_copies(self, copy_mask_ptr) -> int:
+        """Also hold a group's tiles back until the sources in ``copy_mask[group]`` have
+        raised the flags of their peer copies (``bmoe_plan_set_gate_copies``)."""
+        return int(self._lib.bmoe_plan_set_gate_copies(self._handle, copy_mask_ptr or None))
+
     def set_push(self, origin_ptr, expert_row_ptr, y_bases_ptr, ranks: int, y_rows_cap: int) -> int:
         """Send result rows straight to their origin ranks' buffers instead of D (see
         ``bmoe_plan_set_push``); ``origin_ptr`` None switches back."""

@@ -17,6 +17,12 @@ transfer and the math run at the same time:
   ranks' "done" flags are in. (``push_results=False`` keeps D local and sends the
   rows back with a separate kernel after the GEMM.)
 
+Large (expert, source) blocks do not go through the SMs at all: the source packs the
+rows of such a block into a local staging buffer in the order they take in the owner's
+``A`` and sends the block as ONE peer copy (copy engines reach a higher NVLink rate than
+SM stores and leave the SMs to the GEMM), followed in the same stream by a 4-byte copy
+that raises a flag of a second plane; the gate of the GEMM waits for both planes.
+
 The only NCCL call per step is the all-gather of the per-expert counts. Kernels
 of one GPU never wait on each other: rows that stay on the rank are copied by a
 launch that precedes the GEMM in the same stream, and the gate looks at the flags
@@ -55,13 +61,21 @@ class StepPlanner:
         self.local = np.nonzero(owner_a == rank)[0]
         self.owner_a = owner_a
 
-    def step(self, counts_all):
+    def step(self, counts_all, copy_min_rows: int = 0):
         """``counts_all`` [world, experts] (numpy int64, identical on every rank). Returns a
         dict with ``local_experts``, ``local_m`` (rows per local expert), ``row_base``
         (int64 [experts]: first row of (expert, this rank) in the owner's A), ``group_of``
         (uint8 [experts]), ``group_local`` (uint8 per local expert), ``bucket_offset``
-        (uint32 [groups + 2]: this rank's route entries per exchange group, then the rows
-        that stay) and ``total_local``."""
+        (uint32 [groups + 3]: this rank's route entries per exchange group, then the rows
+        that stay, then the rows of copy-engine blocks) and ``total_local``.
+
+        ``copy_min_rows`` > 0: an (expert, source) block of at least that many rows whose
+        owner is another rank travels as one peer copy. ``staging_row_base`` (int64
+        [experts], -1 = not such a block) places this rank's blocks in its staging buffer,
+        ``copy_experts`` lists them in sending order (group, owner, id) and ``copy_mask``
+        (uint32 [groups]) has bit r set where source r sends such a block for one of this
+        rank's experts of that group. Every rank derives the same decisions from the same
+        count matrix."""
         counts_all = np.asarray(counts_all, dtype=np.int64)
         totals = counts_all.sum(axis=0)
         before_me = counts_all[:self.rank].sum(axis=0)
@@ -81,12 +95,30 @@ class StepPlanner:
         # ranks), then the rows that stay
         mine = counts_all[self.rank]
         away = self.owner_a != self.rank
-        sizes = np.zeros(self.groups + 1, dtype=np.int64)
-        sizes[:self.groups] = np.bincount(group_of[away], weights=mine[away],
+        by_copy = away & (mine >= copy_min_rows) if copy_min_rows > 0 else np.zeros_like(away)
+        by_sm = away & ~by_copy
+        sizes = np.zeros(self.groups + 2, dtype=np.int64)
+        sizes[:self.groups] = np.bincount(group_of[by_sm], weights=mine[by_sm],
                                           minlength=self.groups)[:self.groups]
         sizes[self.groups] = mine[~away].sum()
-        bucket_offset = np.zeros(self.groups + 2, dtype=np.uint32)
+        sizes[self.groups + 1] = mine[by_copy].sum()
+        bucket_offset = np.zeros(self.groups + 3, dtype=np.uint32)
         bucket_offset[1:] = np.cumsum(sizes)
+        staging_row_base = np.full(self.experts, -1, dtype=np.int64)
+        copy_experts = np.nonzero(by_copy)[0]
+        if copy_experts.size:
+            copy_experts = copy_experts[np.lexsort((copy_experts, self.owner_a[copy_experts],
+                                                    group_of[copy_experts]))]
+            rows = mine[copy_experts]
+            staging_row_base[copy_experts] = np.cumsum(rows) - rows
+        copy_mask = np.zeros(self.groups, dtype=np.uint32)
+        if copy_min_rows > 0 and self.local.size:
+            arrives = counts_all[:, self.local] >= copy_min_rows          # [world, local experts]
+            arrives[self.rank] = False
+            groups_local = group_of[self.local]
+            for r in np.nonzero(arrives.any(axis=1))[0]:
+                for g in np.unique(groups_local[arrives[r]]):
+                    copy_mask[g] |= np.uint32(1 << int(r))
         local_m = totals[self.local]
         return {
             "local_experts": self.local.tolist(),
@@ -96,13 +128,18 @@ class StepPlanner:
             "group_local": group_of[self.local],
             "bucket_offset": bucket_offset,
             "total_local": int(local_m.sum()),
+            "staging_row_base": staging_row_base,
+            "copy_experts": copy_experts,
+            "copy_mask": copy_mask,
         }
 
 
-def plan_step(counts_all, owner: Sequence[int], rank: int, groups: int, tile_m: int = 256):
+def plan_step(counts_all, owner: Sequence[int], rank: int, groups: int, tile_m: int = 256,
+              copy_min_rows: int = 0):
     """One-shot form of ``StepPlanner(...).step(counts_all)`` with ``local_m`` as a list."""
     counts_all = np.asarray(counts_all, dtype=np.int64)
-    out = StepPlanner(owner, rank, counts_all.shape[0], groups, tile_m).step(counts_all)
+    out = StepPlanner(owner, rank, counts_all.shape[0], groups, tile_m).step(counts_all,
+                                                                            copy_min_rows)
     out["local_m"] = out["local_m"].tolist()
     return out
 
@@ -155,6 +192,7 @@ class SharedBuffers:
                     _capi.check(self._lib.bmoe_peer_open(raw, C.byref(ptr)), "bmoe_peer_open")
                     self._opened.append(ptr.value)
                     table[name][r] = ptr.value
+        self.host_bases = table     # name -> [world] pointers, for host-issued peer copies
         for name in names:
             self.bases[name] = torch.tensor(table[name], dtype=torch.int64, device=dev)
         torch.cuda.synchronize()
@@ -180,7 +218,7 @@ class FusedExpertParallelLayer:
                  exchange_groups: int = 4, dispatch_ctas: int = 0, wait_budget_ns: int = 0,
                  push_results: bool = True, exchange_sms: int = 16,
                  expert_parts: Sequence[int] | None = None, bulk_copies: bool = False,
-                 **plan_options):
+                 copy_engine_min_bytes: int = 2 << 20, **plan_options):
         """``rows_cap``: packed rows this rank can own; ``assignments_cap``: local
         assignments (tokens x top_k) per step; ``exchange_groups``: groups the
         experts of a rank are split into for the overlap (1 = no overlap).
@@ -196,7 +234,11 @@ class FusedExpertParallelLayer:
         on it, so sharing SMs with GEMM CTAs costs more than giving a few away. The
         GEMM must then be a persistent policy (its grid is what leaves the SMs free).
         0 = share: ``dispatch_ctas`` 256-thread CTAs (default 7/16 of the SMs) that fit
-        beside resident GEMM CTAs; any policy."""
+        beside resident GEMM CTAs; any policy.
+
+        ``copy_engine_min_bytes`` (multi-rank only): an (expert, source) block of at least
+        this size travels as one peer copy issued by the host (copy engines, no SMs)
+        instead of SM stores; 0 = every row goes through the SMs."""
         import torch
 
         from .engine import GroupedGemmPlan
@@ -241,7 +283,10 @@ class FusedExpertParallelLayer:
         self.epoch = 0
         dev = torch.device("cuda", torch.cuda.current_device())
         self.dev = dev
-        flag_slots = (_capi.EP_MAX_GROUPS + 1) * world
+        flag_slots = 2 * (_capi.EP_MAX_GROUPS + 1) * world   # pushed rows | peer copies
+        self.copy_min_rows = 0
+        if world > 1 and copy_engine_min_bytes > 0:
+            self.copy_min_rows = max(1, -(-int(copy_engine_min_bytes) // (k * 2)))
         # every rank loads its kernels before the first step: the step's bounded waits
         # assume that all ranks launch within the wait budget
         _capi.check(self._lib.bmoe_preload_kernels(), "bmoe_preload_kernels")
@@ -256,18 +301,21 @@ class FusedExpertParallelLayer:
             .view(self.assignments_cap, n)
         # per-step tables: int64 row_base[E] | uint8 group_of[E] | uint8 group_local[E] |
         # (4-aligned) uint32 first packed row of every local expert [E]
-        # | uint32 bucket offsets [MAX_GROUPS + 2]
+        # | uint32 bucket offsets [MAX_GROUPS + 3] | uint32 copy mask [MAX_GROUPS]
+        # | (8-aligned) int64 staging row base [E]
         self._off_expert_row = (10 * self.experts + 3) // 4 * 4
         self._off_buckets = self._off_expert_row + 4 * self.experts
-        self._table_bytes = self._off_buckets + 4 * (_capi.EP_MAX_GROUPS + 2)
+        self._off_copy_mask = self._off_buckets + 4 * (_capi.EP_MAX_GROUPS + 3)
+        self._off_staging = (self._off_copy_mask + 4 * _capi.EP_MAX_GROUPS + 7) // 8 * 8
+        self._table_bytes = self._off_staging + 8 * self.experts
         self._stage = torch.empty(self._table_bytes, dtype=torch.uint8).pin_memory()
         self._tables = torch.empty(self._table_bytes, dtype=torch.uint8, device=dev)
         self._owner_dev = torch.tensor(self.owner, dtype=torch.int32, device=dev)
         # uint32 scratch zeroed every step: cursor[E] | group_done[MAX_GROUPS] | return
-        # counter | claim counters of the remote and of the local copy launch
-        # [MAX_GROUPS + 1 each] | bucket fill [MAX_GROUPS + 1]
-        g1 = _capi.EP_MAX_GROUPS + 1
-        self._scratch = torch.zeros(self.experts + _capi.EP_MAX_GROUPS + 1 + 3 * g1,
+        # counter | claim counters of the remote, the local and the staging copy launch
+        # [MAX_GROUPS + 2 each] | bucket fill [MAX_GROUPS + 2]
+        g2 = _capi.EP_MAX_GROUPS + 2
+        self._scratch = torch.zeros(self.experts + _capi.EP_MAX_GROUPS + 1 + 4 * g2,
                                     dtype=torch.int32, device=dev)
         self._entries = torch.empty(max(1, self.assignments_cap) * 16, dtype=torch.uint8,
                                     device=dev)
@@ -280,6 +328,25 @@ class FusedExpertParallelLayer:
         self._ev_start = torch.cuda.Event()
         self._ev_comm = torch.cuda.Event()
         self.routes = None
+        self.copy_bytes = 0      # bytes of the last step that went as peer copies
+        if self.copy_min_rows:
+            # staging for the rows of copy-engine blocks (worst case: every local assignment)
+            self._staging = torch.empty(max(1, self.assignments_cap), k, dtype=torch.bfloat16,
+                                        device=dev)
+            self._staging_base = torch.tensor([self._staging.data_ptr()] * world,
+                                              dtype=torch.int64, device=dev)
+            self._pack = torch.cuda.Stream(device=dev)
+            self._ev_pack = torch.cuda.Event()
+            # one stream per destination: blocks for one rank stay in order (its flag copy
+            # follows its data), blocks for different ranks go out side by side
+            self._copy_streams = [torch.cuda.Stream(device=dev) for _ in range(world)]
+            self._copy_stream_table = (C.c_void_p * world)(
+                *[st.cuda_stream for st in self._copy_streams])
+            self._ev_copies = [torch.cuda.Event() for _ in range(world)]
+            self._copy_streams_used = []
+            # the flag words the 4-byte copies read: word i holds epoch _epoch_base + i
+            self._epoch_base = 0
+            self._epoch_words = torch.arange(0, 1 << 16, dtype=torch.int32, device=dev)
 
     def close(self):
         self.plan.close()
@@ -290,15 +357,18 @@ class FusedExpertParallelLayer:
         return self._scratch.data_ptr() + 4 * word
 
     def _route(self, flat_ids, top_k, stream, routes):
-        e, g1 = self.experts, _capi.EP_MAX_GROUPS + 1
+        e, g2 = self.experts, _capi.EP_MAX_GROUPS + 2
         t = self._tables.data_ptr()
+        staged = self.copy_min_rows > 0
         args = _capi.EpRouteArgs(
             expert_ids_dev=flat_ids.data_ptr(), row_base_dev=t,
             owner_dev=self._owner_dev.data_ptr(), group_of_dev=t + 8 * e,
             cursor_dev=self._scratch_ptr(0),
             origin_bases_dev=self.shared.bases["origin"].data_ptr(),
             entries_dev=self._entries.data_ptr(), bucket_offset_dev=t + self._off_buckets,
-            bucket_fill_dev=self._scratch_ptr(e + _capi.EP_MAX_GROUPS + 1 + 2 * g1),
+            bucket_fill_dev=self._scratch_ptr(e + _capi.EP_MAX_GROUPS + 1 + 3 * g2),
+            staging_row_base_dev=(t + self._off_staging) if staged else None,
+            staging_rows_cap=int(self._staging.shape[0]) if staged else 0,
             dst_rank_out_dev=routes[0].data_ptr() if routes else None,
             dst_row_out_dev=routes[1].data_ptr() if routes else None,
             assignments=int(flat_ids.numel()), rows_cap=self.rows_cap, top_k=top_k,
@@ -309,16 +379,19 @@ class FusedExpertParallelLayer:
             self.launches += 1
 
     def _dispatch(self, x, assignments, mode, stream):
-        e, g1 = self.experts, _capi.EP_MAX_GROUPS + 1
-        remote = mode != _capi.EP_LOCAL
+        e, g2 = self.experts, _capi.EP_MAX_GROUPS + 2
+        remote = mode == _capi.EP_REMOTE
+        pack = mode == _capi.EP_PACK
+        claim_set = 0 if remote else (2 if pack else 1)
         args = _capi.EpDispatchArgs(
             x_dev=x.data_ptr(), entries_dev=self._entries.data_ptr(),
             bucket_offset_dev=self._tables.data_ptr() + self._off_buckets,
-            a_bases_dev=self.shared.bases["a"].data_ptr(),
+            a_bases_dev=(self._staging_base if pack else self.shared.bases["a"]).data_ptr(),
             flag_bases_dev=self.shared.bases["flags"].data_ptr(),
             group_done_dev=self._scratch_ptr(e),
-            chunk_next_dev=self._scratch_ptr(e + _capi.EP_MAX_GROUPS + 1 + (0 if remote else g1)),
-            assignments=assignments, tokens=int(x.shape[0]), rows_cap=self.rows_cap,
+            chunk_next_dev=self._scratch_ptr(e + _capi.EP_MAX_GROUPS + 1 + claim_set * g2),
+            assignments=assignments, tokens=int(x.shape[0]),
+            rows_cap=int(self._staging.shape[0]) if pack else self.rows_cap,
             row_bytes=self.k * 2, ranks=self.world, self=self.rank, groups=self.groups,
             mode=mode, epoch=self.epoch,
             max_ctas=(self.exchange_sms or self.dispatch_ctas) if remote else 0,
@@ -329,6 +402,59 @@ class FusedExpertParallelLayer:
             stream=stream.cuda_stream or None)
         _capi.check(self._lib.bmoe_ep_dispatch(C.byref(args)), "bmoe_ep_dispatch")
         self.launches += 1
+
+    def _send_copies(self, x, step, mine, assignments):
+        """Packs the rows of this step's copy-engine blocks into the staging buffer (one
+        launch on a stream of its own) and enqueues one peer copy per block plus one
+        4-byte flag copy per (destination, group), each destination on its own stream."""
+        import torch
+
+        experts = step["copy_experts"]
+        self._copy_streams_used = []
+        self.copy_bytes = 0
+        if experts.size == 0:
+            return
+        self._pack.wait_event(self._ev_start)
+        self._dispatch(x, assignments, _capi.EP_PACK, self._pack)
+        self._ev_pack.record(self._pack)
+        if self.epoch - self._epoch_base >= self._epoch_words.numel():
+            torch.cuda.synchronize()
+            self._epoch_base = self.epoch
+            self._epoch_words.copy_(torch.arange(self.epoch, self.epoch + self._epoch_words.numel(),
+                                                 dtype=torch.int64).to(torch.int32))
+        row_bytes = self.k * 2
+        owners = self._planner.owner_a[experts]
+        groups = step["group_of"][experts].astype(np.int64)
+        a_base = np.asarray(self.shared.host_bases["a"], dtype=np.uint64)
+        flag_base = np.asarray(self.shared.host_bases["flags"], dtype=np.uint64)
+        # a flag copy after the last block of every (group, destination) run
+        last_of_run = np.ones(experts.size, dtype=bool)
+        last_of_run[:-1] = (owners[1:] != owners[:-1]) | (groups[1:] != groups[:-1])
+        items = np.zeros(experts.size + int(last_of_run.sum()), dtype=_capi.COPY_ITEM_DTYPE)
+        at = np.arange(experts.size) + np.concatenate(([0], np.cumsum(last_of_run)[:-1]))
+        items["dst"][at] = a_base[owners] + step["row_base"][experts].astype(np.uint64) * np.uint64(row_bytes)
+        items["src"][at] = np.uint64(self._staging.data_ptr()) + \
+            step["staging_row_base"][experts].astype(np.uint64) * np.uint64(row_bytes)
+        items["bytes"][at] = mine[experts].astype(np.uint64) * np.uint64(row_bytes)
+        items["stream"][at] = owners
+        flag_at = at[last_of_run] + 1
+        plane = _capi.ep_copy_flags(self.world)
+        slots = plane + groups[last_of_run] * self.world + self.rank
+        items["dst"][flag_at] = flag_base[owners[last_of_run]] + slots.astype(np.uint64) * np.uint64(4)
+        items["src"][flag_at] = np.uint64(self._epoch_words.data_ptr()
+                                          + 4 * (self.epoch - self._epoch_base))
+        items["bytes"][flag_at] = 4
+        items["stream"][flag_at] = owners[last_of_run]
+        used = sorted(set(int(o) for o in owners))
+        for o in used:
+            self._copy_streams[o].wait_event(self._ev_pack)
+        _capi.check(self._lib.bmoe_peer_copy_batch(items.ctypes.data, len(items),
+                                                   self._copy_stream_table, self.world),
+                    "bmoe_peer_copy_batch")
+        for o in used:
+            self._ev_copies[o].record(self._copy_streams[o])
+        self._copy_streams_used = used
+        self.copy_bytes = int(items["bytes"][at].sum())
 
     def _return(self, rows, stream):
         b = self.shared.bases
@@ -390,7 +516,7 @@ class FusedExpertParallelLayer:
             counts_all = flat.reshape(self.world, self.experts).cpu().numpy()
         else:
             counts_all = local_counts.reshape(1, -1).cpu().numpy()
-        step = self._planner.step(counts_all)
+        step = self._planner.step(counts_all, self.copy_min_rows)
         if step["total_local"] > self.rows_cap:
             raise RuntimeError("routed rows exceed the packed buffer capacity")
         stage = self._stage.numpy()
@@ -403,6 +529,9 @@ class FusedExpertParallelLayer:
             np.cumsum(local_m) - local_m
         buckets = step["bucket_offset"]
         stage[self._off_buckets:self._off_buckets + 4 * len(buckets)].view(np.uint32)[:] = buckets
+        mask = step["copy_mask"]
+        stage[self._off_copy_mask:self._off_copy_mask + 4 * len(mask)].view(np.uint32)[:] = mask
+        stage[self._off_staging:self._off_staging + 8 * e].view(np.int64)[:] = step["staging_row_base"]
         self._tables.copy_(self._stage, non_blocking=True)
         self.epoch += 1
         routes = None
@@ -413,9 +542,10 @@ class FusedExpertParallelLayer:
         self._route(flat_ids, top_k, main, routes)
         mark("counts")
 
+        self._ev_start.record(main)       # routes planned: the copy launches may start
+
         def push_remote():
             # rows bound for other GPUs: side stream, overlapped with everything below
-            self._ev_start.record(main)
             self._comm.wait_event(self._ev_start)
             if record_events:
                 self._remote_marks = (torch.cuda.Event(enable_timing=True),
@@ -432,6 +562,8 @@ class FusedExpertParallelLayer:
         # stores wait for NVLink slows this short copy several times.
         if self.world > 1 and self.exchange_sms:
             push_remote()
+        if self.copy_min_rows:
+            self._send_copies(x, step, counts_all[self.rank], assignments)
         self._dispatch(x, assignments, _capi.EP_LOCAL, main)
         if self.world > 1 and not self.exchange_sms:
             push_remote()
@@ -452,6 +584,10 @@ class FusedExpertParallelLayer:
                                                self.world, self.rank,
                                                self._tables.data_ptr() + 9 * e),
                             "bmoe_plan_set_gate")
+                if self.copy_min_rows:
+                    _capi.check(self.plan.set_gate_copies(self._tables.data_ptr()
+                                                          + self._off_copy_mask),
+                                "bmoe_plan_set_gate_copies")
             if self.push_results:
                 _capi.check(self.plan.set_push(self.shared.local["origin"].data_ptr(),
                                                self._tables.data_ptr() + self._off_expert_row,
@@ -476,6 +612,8 @@ class FusedExpertParallelLayer:
                 "bmoe_ep_wait_flags")
             self.launches += 1
             main.wait_event(self._ev_comm)
+            for o in self._copy_streams_used:   # the staging buffer is free again
+                main.wait_event(self._ev_copies[o])
         mark("return")
         y = self.y[:assignments]
         if topk_weights is not None:

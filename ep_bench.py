@@ -113,7 +113,7 @@ def run(args, spec, workload):
             exchange_groups=ep_groups, cta_group=args.cta_group,
             dispatch_ctas=args.dispatch_ctas, push_results=not args.no_push,
             exchange_sms=args.exchange_sms, expert_parts=parts,
-            bulk_copies=args.bulk_copies)
+            bulk_copies=args.bulk_copies, copy_engine_min_bytes=args.copy_engine_kb * 1024)
         ops = layer
         plain = layer
         groups = layer.groups
@@ -136,6 +136,7 @@ def run(args, spec, workload):
             owner, n, k, rank=rank, world=world,
             ops=ep.CudaOps(scheduler=args.policy, cta_group=args.cta_group))
     exchange_sms_used = getattr(layer, "exchange_sms", 0)
+    copy_bytes = 0
     w_local = _expert_weights(torch, layer.local_experts, n, k, dev)
     total_flops = 2.0 * tokens * top_k * n * k
     stream = torch.cuda.current_stream()
@@ -161,6 +162,7 @@ def run(args, spec, workload):
     sampler.mark_region(wall0, time.time())
     ms_per_step = max_over_ranks(t0.elapsed_time(t1) / args.steps)
     launches = ops.launches - launches_before
+    copy_bytes = getattr(layer, "copy_bytes", 0)
     clocks = sampler.stop() if rank == 0 else None
     ops.poll()
 
@@ -309,6 +311,8 @@ def run(args, spec, workload):
                    "pipeline_groups": groups,
                    "comm_sms": (exchange_sms_used if args.exchange == "fused"
                                 else args.comm_sms if groups > 1 else 0),
+                   "copy_engine_min_kb": args.copy_engine_kb if args.exchange == "fused" else None,
+                   "rank0_copy_engine_bytes_per_step": copy_bytes,
                    "rank_tiles": rank_tiles, "rank0_rows": local_rows,
                    "max_rank_rows": rows_max, "mean_rank_rows": tokens * top_k / world,
                    "l2": "per-rank weights exceed the 126 MB L2; no flush between steps",

@@ -506,6 +506,13 @@ int bmoe_combine_topk(const void* const* src_bases_dev, uint32_t n_src,
 #define BMOE_EP_LOCAL 0u   /* only rows whose owner is this rank; raises no flag */
 #define BMOE_EP_REMOTE 1u  /* only rows owned by other ranks; raises the group flags */
 #define BMOE_EP_ALL 2u
+#define BMOE_EP_PACK 3u    /* only the rows of copy-engine blocks, into the local staging buffer */
+/* Second flag plane, for rows that arrive as peer copies: slot
+ * BMOE_EP_COPY_FLAGS(ranks) + g*ranks + s holds the last step for which ALL copy-engine
+ * blocks of source s for expert group g have landed (written by a 4-byte peer copy that
+ * follows the data copies in the same stream). A flag array therefore has
+ * 2 * (BMOE_EP_MAX_GROUPS + 1) * ranks slots. */
+#define BMOE_EP_COPY_FLAGS(ranks) ((BMOE_EP_MAX_GROUPS + 1u) * (ranks))
 
 /* Routed rows per expert of this rank in one pass over its assignments:
  * counts_dev[id] (int64 [bins], zeroed here) += 1 for every assignment with a valid
@@ -527,10 +534,11 @@ typedef struct bmoe_ep_route_args {
   uint32_t* cursor_dev;            /* [experts] zero at step start */
   void* const* origin_bases_dev;   /* [ranks] int64 origin record per packed row */
   void* entries_dev;               /* [assignments] 16-byte route entries, written here */
-  const uint32_t* bucket_offset_dev; /* [groups + 2] first entry of bucket b: groups 0..G-1 hold
+  const uint32_t* bucket_offset_dev; /* [groups + 3] first entry of bucket b: groups 0..G-1 hold
                                       the rows bound for other ranks, bucket G the rows that
-                                      stay; sizes follow from the count matrix */
-  uint32_t* bucket_fill_dev;       /* [groups + 1] zero at step start */
+                                      stay, bucket G + 1 the rows of copy-engine blocks (below);
+                                      sizes follow from the count matrix */
+  uint32_t* bucket_fill_dev;       /* [groups + 2] zero at step start */
   int32_t* dst_rank_out_dev;       /* [assignments] or NULL: destination of every assignment */
   int64_t* dst_row_out_dev;        /* [assignments] or NULL */
   uint64_t assignments;            /* < 2^32 */
@@ -541,6 +549,14 @@ typedef struct bmoe_ep_route_args {
   uint32_t self;
   uint32_t groups;
   void* stream;
+  /* Copy-engine blocks (appended; NULL = none). staging_row_base_dev[e] >= 0 marks expert
+   * e as one whose rows of this rank travel to the owner as ONE peer copy instead of
+   * SM stores: its entries go to bucket G + 1 with this rank as destination and row
+   * staging_row_base_dev[e] + position, i.e. into a local staging buffer in the order
+   * the rows take in the owner's A (bmoe_ep_dispatch mode BMOE_EP_PACK fills it,
+   * bmoe_peer_copy_batch sends it). The origin record is written as for any row. */
+  const int64_t* staging_row_base_dev;  /* [experts] or NULL */
+  uint64_t staging_rows_cap;
 } bmoe_ep_route_args;
 
 /* Route planning of one step: the destination row of every assignment (the row inside
@@ -558,7 +574,7 @@ typedef struct bmoe_ep_dispatch_args {
   void* const* a_bases_dev;        /* [ranks] packed A buffers, rows_cap rows each */
   void* const* flag_bases_dev;     /* [ranks] flag arrays (REMOTE / ALL with ranks > 1) */
   uint32_t* group_done_dev;        /* [groups] zero at step start (REMOTE / ALL) */
-  uint32_t* chunk_next_dev;        /* [groups + 1] zero at step start */
+  uint32_t* chunk_next_dev;        /* [groups + 2] zero at step start */
   uint64_t assignments;            /* entries in all buckets together (sizes the grid) */
   uint64_t tokens;                 /* rows of x */
   uint64_t rows_cap;
@@ -566,7 +582,9 @@ typedef struct bmoe_ep_dispatch_args {
   uint32_t ranks;
   uint32_t self;
   uint32_t groups;
-  uint32_t mode;                   /* BMOE_EP_LOCAL / REMOTE / ALL */
+  uint32_t mode;                   /* BMOE_EP_LOCAL / REMOTE / ALL / PACK (PACK: bucket
+                                      G + 1 only, a_bases_dev[self] = the staging buffer,
+                                      rows_cap = its rows; raises no flag) */
   uint32_t epoch;
   uint32_t max_ctas;               /* 0 = default: 4 per SM for LOCAL, 7/16 of the SMs otherwise */
   uint32_t block_threads;          /* 0 = 256; 256, 512 or 1024 */
@@ -620,6 +638,30 @@ int bmoe_ep_wait_flags(const uint32_t* flags_dev, uint32_t first_slot, uint32_t 
  * group_of_expert_dev: [experts of the plan] uint8, values < 32. */
 int bmoe_plan_set_gate(bmoe_plan* plan, const uint32_t* flags_dev, uint32_t epoch,
                        uint32_t ranks, uint32_t self, const uint8_t* group_of_expert_dev);
+
+/* Extends the gate to rows that arrive as peer copies (copy-engine blocks): a tile of
+ * group g is also held back until, for every source s whose bit is set in
+ * copy_mask_dev[g], slot BMOE_EP_COPY_FLAGS(ranks) + g*ranks + s of the flag array given
+ * to bmoe_plan_set_gate has reached the gate's epoch. copy_mask_dev: uint32 [groups of
+ * this rank], NULL switches the extension off. Call after bmoe_plan_set_gate. No
+ * counterpart in the reference (it has no multi-GPU path). */
+int bmoe_plan_set_gate_copies(bmoe_plan* plan, const uint32_t* copy_mask_dev);
+
+/* One device-to-device copy of a batch (bmoe_peer_copy_batch). */
+typedef struct bmoe_copy_item {
+  void* dst;        /* device pointer on any GPU mapped into this process */
+  const void* src;
+  uint64_t bytes;
+  uint32_t stream;  /* index into the stream table */
+  uint32_t reserved;
+} bmoe_copy_item;
+
+/* Enqueues `count` asynchronous copies, item i on streams[items[i].stream], in array
+ * order, one cudaMemcpyAsync each (the copy engines move the bytes; no SM is used).
+ * Used for the large (expert, source) blocks of the expert-parallel exchange and for the
+ * 4-byte flag words that follow them. items and streams are host arrays. */
+int bmoe_peer_copy_batch(const bmoe_copy_item* items, uint32_t count, void* const* streams,
+                         uint32_t stream_count);
 
 /* Result push for the next bmoe_plan_run calls (BF16 output only): the epilogue
  * writes every valid result row to row `assignment` of y_bases_dev[rank], following

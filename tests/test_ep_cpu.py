@@ -206,7 +206,7 @@ def test_fused_exchange_step_tables_cover_every_owner_buffer_once(engine):
         cursor = np.zeros(experts, dtype=np.int64)
         flat = ids_all[bounds[r]:bounds[r + 1]].reshape(-1).numpy()
         # route entries per bucket: exchange groups of rows that leave, then rows that stay
-        sizes = np.zeros(groups + 1, dtype=np.int64)
+        sizes = np.zeros(groups + 2, dtype=np.int64)     # the last bucket: copy-engine blocks
         for e in flat:
             sizes[groups if owner[e] == r else steps[r]["group_of"][e]] += 1
         assert np.array_equal(np.diff(steps[r]["bucket_offset"].astype(np.int64)), sizes)
@@ -219,6 +219,44 @@ def test_fused_exchange_step_tables_cover_every_owner_buffer_once(engine):
     for q in range(world):
         want = np.repeat(steps[q]["local_experts"], steps[q]["local_m"])
         assert np.array_equal(filled[q], want)
+
+
+def test_copy_engine_blocks_are_agreed_on_by_sender_and_receiver(engine):
+    """Blocks of at least copy_min_rows rows leave as peer copies: the sender's list, its
+    staging layout and bucket sizes, and every receiver's per-group source mask follow from
+    the same count matrix and must describe the same set of blocks."""
+    from bmoe_b200 import ep_fused
+
+    rng = np.random.default_rng(5)
+    world, experts, groups, min_rows = 4, 23, 3, 120
+    counts_all = (rng.integers(0, 400, size=(world, experts)) *
+                  (rng.random((world, experts)) > 0.2)).astype(np.int64)
+    owner = [int(x) for x in rng.integers(0, world, size=experts)]
+    steps = [ep_fused.plan_step(counts_all, owner, r, groups, tile_m=64, copy_min_rows=min_rows)
+             for r in range(world)]
+    none = [ep_fused.plan_step(counts_all, owner, r, groups, tile_m=64) for r in range(world)]
+    masks = np.zeros((world, groups), dtype=np.uint32)
+    for r in range(world):
+        st = steps[r]
+        want = [e for e in range(experts) if owner[e] != r and counts_all[r][e] >= min_rows]
+        assert sorted(st["copy_experts"].tolist()) == want
+        assert none[r]["copy_experts"].size == 0 and not none[r]["copy_mask"].any()
+        assert np.array_equal(st["row_base"], none[r]["row_base"])       # placement unchanged
+        # sending order: by (group, owner, id); staging rows back to back in that order
+        keys = [(int(st["group_of"][e]), owner[e], int(e)) for e in st["copy_experts"]]
+        assert keys == sorted(keys)
+        at = 0
+        for e in st["copy_experts"]:
+            assert st["staging_row_base"][e] == at
+            at += counts_all[r][e]
+        assert all(st["staging_row_base"][e] == -1 for e in range(experts) if e not in want)
+        sizes = np.diff(st["bucket_offset"].astype(np.int64))
+        assert sizes[groups + 1] == at and sizes.sum() == counts_all[r].sum()
+        assert sizes[groups] == sum(counts_all[r][e] for e in range(experts) if owner[e] == r)
+        for e in want:
+            masks[owner[e], st["group_of"][e]] |= np.uint32(1 << r)
+    for q in range(world):
+        assert np.array_equal(steps[q]["copy_mask"], masks[q]), q
 
 
 def test_hot_experts_are_split_into_row_shards(engine):

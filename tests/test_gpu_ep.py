@@ -375,10 +375,27 @@ def _ep_worker(rank, world, port, tmpdir):
         same = same and torch.equal(y.cpu().view(torch.int16), want_z.view(torch.int16))
         dist.barrier()
         fused.close()
+        # blocks of 8 rows and more travel as peer copies (copy engines), the rest as SM
+        # stores; both kinds of flags gate the GEMM
+        copied = ep_fused.FusedExpertParallelLayer(owner, 512, 320, rank=rank, world=world,
+                                                   rows_cap=2400, assignments_cap=(hi - lo) * 4,
+                                                   exchange_groups=3, scheduler="dynamic_queue",
+                                                   copy_engine_min_bytes=8 * 640)
+        for i in range(4):
+            y = copied.forward(x[lo:hi].cuda(), ids[lo:hi].cuda(), w[copied.local_experts].cuda(),
+                               topk_weights=gates.cuda() if i == 3 else None)
+            if i == 2:
+                same = same and torch.equal(y.view(torch.int16), want.view(torch.int16))
+                same = same and copied.copy_bytes > 0
+        copied.poll()
+        same = same and torch.equal(y.cpu().view(torch.int16), want_z.view(torch.int16))
+        dist.barrier()
+        copied.close()
         kept = ep_fused.FusedExpertParallelLayer(owner, 512, 320, rank=rank, world=world,
                                                  rows_cap=2400, assignments_cap=(hi - lo) * 4,
                                                  exchange_groups=2, push_results=False,
-                                                 cta_group=1, bulk_copies=True)
+                                                 cta_group=1, bulk_copies=True,
+                                                 copy_engine_min_bytes=0)
         for _ in range(2):
             y = kept.forward(x[lo:hi].cuda(), ids[lo:hi].cuda(), w[kept.local_experts].cuda())
         kept.poll()
