@@ -830,7 +830,7 @@ def main():
     ap.add_argument("--exchange-sms", type=int, default=16,
                     help="fused exchange: SMs the GEMM leaves to the remote-row kernel "
                          "(0 = share SMs, see --dispatch-ctas)")
-    ap.add_argument("--copy-engine-kb", type=int, default=2048,
+    ap.add_argument("--copy-engine-kb", type=int, default=0,
                     help="fused exchange: (expert, source) blocks of at least this many KiB "
                          "travel as peer copies issued by the host (copy engines) instead of "
                          "SM stores; 0 = all rows through the SMs")

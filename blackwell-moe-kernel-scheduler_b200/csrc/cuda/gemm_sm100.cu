@@ -181,6 +181,30 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   };
   const long long kernel_t0 = tracing ? clock64() : 0;
 
+  // The first tile of a unit is known before any set-up (static stride and launch
+  // control start at the unit's own index, the queue's first claim needs nothing but the
+  // counter): the scheduler lane fetches it, and warms the descriptors it needs, while
+  // barriers and Tensor Memory are being set up. A small problem is one tile per CTA, so
+  // this takes the two dependent global reads off the front of the launch.
+  bmoe_tile first_rec{};
+  uint32_t first_index = 0xffffffffu;   // worklist index of first_rec, if fetched
+  uint32_t first_claim = 0;             // queue mode: the claim made ahead of the set-up
+  if (warp == 2 && lane == 0 && leader) {
+    if (p.sched_mode == kSchedQueue) {
+      first_claim = atomicAdd(&p.queue[0], p.claim_size);
+      if (first_claim < p.main_end) first_index = first_claim;
+    } else if (unit < p.tile_count) {
+      first_index = unit;
+    }
+    if (first_index != 0xffffffffu) {
+      first_rec = p.tiles[first_index];
+      const uint32_t e = first_rec.expert_id;
+      ptx::tensormap_prefetch(p.a_row_offsets != nullptr ? p.tmap_a : p.tmap_a + e);
+      ptx::tensormap_prefetch(p.tmap_b + e);
+      if (p.push_origin == nullptr) ptx::tensormap_prefetch(p.tmap_d + e);
+    }
+  }
+
   // ------------------------------------------------------------- set-up --
   if (threadIdx.x == 0) {
     for (uint32_t s = 0; s < Cfg::kStages; ++s) {
@@ -268,8 +292,11 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       auto publish = [&](int32_t tile_index) -> bool {
         const uint32_t slot = published % kSchedSlots;
         const uint32_t round = (published / kSchedSlots) & 1u;
-        if (p.gate_flags != nullptr && tile_index != kSentinel &&
-            !gate(p.tiles[tile_index].expert_id)) {
+        bmoe_tile t{};
+        if (tile_index != kSentinel) {
+          t = static_cast<uint32_t>(tile_index) == first_index ? first_rec : p.tiles[tile_index];
+        }
+        if (p.gate_flags != nullptr && tile_index != kSentinel && !gate(t.expert_id)) {
           return false;
         }
         if (!wait(bar_sched_empty(slot), round ^ 1u)) {
@@ -279,7 +306,6 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         TileInfo rec{};
         rec.tile = tile_index;
         if (tile_index != kSentinel) {
-          const bmoe_tile t = p.tiles[tile_index];
           rec.expert = t.expert_id;
           rec.row0 = t.tile_m * (kCtaRows * Cfg::kGroup);
           rec.col0 = t.tile_n * TILE_N;
@@ -334,10 +360,13 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           alive = publish(static_cast<int32_t>(t));
         }
       } else if (p.sched_mode == kSchedQueue) {
-        // Main part: chunks of claim_size below main_end.
+        // Main part: chunks of claim_size below main_end (the first claim was made
+        // before the set-up).
+        bool claimed_ahead = true;
         while (alive) {
           if (!pace()) { alive = false; break; }
-          const uint32_t begin = atomicAdd(&p.queue[0], p.claim_size);
+          const uint32_t begin = claimed_ahead ? first_claim : atomicAdd(&p.queue[0], p.claim_size);
+          claimed_ahead = false;
           if (begin >= p.main_end) break;
           const uint32_t end = min(begin + p.claim_size, p.main_end);
           for (uint32_t t = begin; alive && t < end; ++t) {

@@ -17,11 +17,11 @@ transfer and the math run at the same time:
   ranks' "done" flags are in. (``push_results=False`` keeps D local and sends the
   rows back with a separate kernel after the GEMM.)
 
-Large (expert, source) blocks do not go through the SMs at all: the source packs the
-rows of such a block into a local staging buffer in the order they take in the owner's
-``A`` and sends the block as ONE peer copy (copy engines reach a higher NVLink rate than
-SM stores and leave the SMs to the GEMM), followed in the same stream by a 4-byte copy
-that raises a flag of a second plane; the gate of the GEMM waits for both planes.
+Optionally (``copy_engine_min_bytes``) large (expert, source) blocks do not go through
+the SMs: the source packs the rows of such a block into a local staging buffer in the
+order they take in the owner's ``A`` and sends the block as ONE peer copy, followed in
+the same stream by a 4-byte copy that raises a flag of a second plane; the gate of the
+GEMM waits for both planes. Off by default (it measured slower than SM stores).
 
 The only NCCL call per step is the all-gather of the per-expert counts. Kernels
 of one GPU never wait on each other: rows that stay on the rank are copied by a
@@ -218,7 +218,7 @@ class FusedExpertParallelLayer:
                  exchange_groups: int = 4, dispatch_ctas: int = 0, wait_budget_ns: int = 0,
                  push_results: bool = True, exchange_sms: int = 16,
                  expert_parts: Sequence[int] | None = None, bulk_copies: bool = False,
-                 copy_engine_min_bytes: int = 2 << 20, **plan_options):
+                 copy_engine_min_bytes: int = 0, **plan_options):
         """``rows_cap``: packed rows this rank can own; ``assignments_cap``: local
         assignments (tokens x top_k) per step; ``exchange_groups``: groups the
         experts of a rank are split into for the overlap (1 = no overlap).
@@ -238,7 +238,10 @@ class FusedExpertParallelLayer:
 
         ``copy_engine_min_bytes`` (multi-rank only): an (expert, source) block of at least
         this size travels as one peer copy issued by the host (copy engines, no SMs)
-        instead of SM stores; 0 = every row goes through the SMs."""
+        instead of SM stores; 0 (default) = every row goes through the SMs. Measured on
+        B200 / NVSwitch the copies lose: the 30-60 copies of a step (5-15 MB each) run one
+        after the other at 25-30 us apiece, 160-350 GB/s per GPU, against 360-450 GB/s for
+        SM stores from 16 SMs; the path is kept for systems where that differs."""
         import torch
 
         from .engine import GroupedGemmPlan
@@ -329,6 +332,7 @@ class FusedExpertParallelLayer:
         self._ev_comm = torch.cuda.Event()
         self.routes = None
         self.copy_bytes = 0      # bytes of the last step that went as peer copies
+        self._copy_streams_used = []
         if self.copy_min_rows:
             # staging for the rows of copy-engine blocks (worst case: every local assignment)
             self._staging = torch.empty(max(1, self.assignments_cap), k, dtype=torch.bfloat16,
@@ -415,8 +419,15 @@ class FusedExpertParallelLayer:
         if experts.size == 0:
             return
         self._pack.wait_event(self._ev_start)
+        timed = getattr(self, "_timing_copies", False)
+        if timed:
+            self._copy_marks = [torch.cuda.Event(enable_timing=True)]
+            self._copy_marks[0].record(self._pack)
         self._dispatch(x, assignments, _capi.EP_PACK, self._pack)
         self._ev_pack.record(self._pack)
+        if timed:
+            self._copy_marks.append(torch.cuda.Event(enable_timing=True))
+            self._copy_marks[1].record(self._pack)
         if self.epoch - self._epoch_base >= self._epoch_words.numel():
             torch.cuda.synchronize()
             self._epoch_base = self.epoch
@@ -453,6 +464,9 @@ class FusedExpertParallelLayer:
                     "bmoe_peer_copy_batch")
         for o in used:
             self._ev_copies[o].record(self._copy_streams[o])
+            if timed:
+                self._copy_marks.append(torch.cuda.Event(enable_timing=True))
+                self._copy_marks[-1].record(self._copy_streams[o])
         self._copy_streams_used = used
         self.copy_bytes = int(items["bytes"][at].sum())
 
@@ -493,6 +507,8 @@ class FusedExpertParallelLayer:
                 ev.record(main)
                 marks.append((name, ev))
 
+        self._timing_copies = bool(record_events)
+        self._copy_marks = None
         mark("start")
         # rows per expert (or per row shard of split experts, dealt by assignment index)
         local_counts = torch.empty(self.experts, dtype=torch.int64, device=dev)
@@ -562,9 +578,11 @@ class FusedExpertParallelLayer:
         # stores wait for NVLink slows this short copy several times.
         if self.world > 1 and self.exchange_sms:
             push_remote()
+        # the rows that stay are what the GEMM's stream waits for: their launch goes ahead
+        # of the staging launch, which may share the SMs with the start of the GEMM
+        self._dispatch(x, assignments, _capi.EP_LOCAL, main)
         if self.copy_min_rows:
             self._send_copies(x, step, counts_all[self.rank], assignments)
-        self._dispatch(x, assignments, _capi.EP_LOCAL, main)
         if self.world > 1 and not self.exchange_sms:
             push_remote()
         mark("local_rows")
@@ -663,4 +681,10 @@ class FusedExpertParallelLayer:
         if self.world > 1 and getattr(self, "_remote_marks", None):
             # side stream: runs beside local_rows / gemm, not part of their sum
             out["remote_rows_overlapped"] = self._remote_marks[0].elapsed_time(self._remote_marks[1])
+        if getattr(self, "_copy_marks", None):
+            # staging launch, then the peer copies on their streams (start of staging to
+            # the end of the last copy), beside everything else
+            m = self._copy_marks
+            out["staging_overlapped"] = m[0].elapsed_time(m[1])
+            out["peer_copies_overlapped"] = max(m[0].elapsed_time(end) for end in m[2:])
         return out
