@@ -147,6 +147,19 @@ class EpRouteArgs(C.Structure):
     ]
 
 
+class EpPlanArgs(C.Structure):
+    _fields_ = [
+        ("counts_all_dev", C.c_void_p), ("owner_dev", C.c_void_p), ("order_dev", C.c_void_p),
+        ("row_base_dev", C.c_void_p), ("group_of_dev", C.c_void_p),
+        ("group_local_dev", C.c_void_p), ("expert_row_dev", C.c_void_p),
+        ("local_rows_dev", C.c_void_p), ("bucket_offset_dev", C.c_void_p),
+        ("totals_dev", C.c_void_p), ("rows_cap", C.c_uint64),
+        ("experts", C.c_uint32), ("ranks", C.c_uint32), ("self", C.c_uint32),
+        ("groups", C.c_uint32), ("tile_m", C.c_uint32),
+        ("stream", C.c_void_p),
+    ]
+
+
 class CopyItem(C.Structure):
     _fields_ = [("dst", C.c_void_p), ("src", C.c_void_p), ("bytes", C.c_uint64),
                 ("stream", C.c_uint32), ("reserved", C.c_uint32)]
@@ -249,6 +262,7 @@ class GemmArgs(C.Structure):
         ("packed_rows", C.c_uint64),
         ("results_pushed", C.c_uint32),
         ("reserved0", C.c_uint32),
+        ("tokens_per_expert_dev", C.c_void_p),
     ]
 
 
@@ -377,6 +391,7 @@ SIGNATURES = {
         [C.c_void_p, C.c_uint64, C.c_uint32, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p,
          C.c_void_p, C.c_void_p],
     ),
+    "bmoe_ep_plan": (C.c_int, [C.c_void_p]),
     "bmoe_ep_route": (C.c_int, [C.c_void_p]),
     "bmoe_ep_dispatch": (C.c_int, [C.c_void_p]),
     "bmoe_ep_return": (C.c_int, [C.c_void_p]),

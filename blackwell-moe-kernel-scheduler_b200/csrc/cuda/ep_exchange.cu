@@ -463,6 +463,158 @@ ep_count_kernel(const int64_t* __restrict__ expert_ids, uint64_t assignments, ui
   }
 }
 
+// ---------------------------------------------------------------------------
+// Step tables on the device (what the Python layer's host planner computes with numpy).
+// One CTA; position i runs over the experts sorted by (owner, id), so an owner's experts
+// are one contiguous segment in packed order.
+// ---------------------------------------------------------------------------
+struct PlanArgs {
+  const int64_t* counts_all;
+  const int32_t* owner;
+  const int32_t* order;
+  int64_t* row_base;
+  uint8_t* group_of;
+  uint8_t* group_local;
+  uint32_t* expert_row;
+  uint32_t* local_rows;
+  uint32_t* bucket_offset;
+  uint32_t* totals;
+  uint64_t rows_cap;
+  uint32_t experts;
+  uint32_t ranks;
+  uint32_t self;
+  uint32_t groups;
+  uint32_t tile_m;
+};
+
+constexpr uint32_t kPlanThreads = 1024;
+constexpr uint32_t kPlanMaxExperts = 4096;
+constexpr uint32_t kPlanMaxRanks = 32;
+constexpr uint32_t kTileShift = 40;   // scanned value: rows | tiles << 40
+
+__global__ void __launch_bounds__(kPlanThreads) ep_plan_kernel(PlanArgs a) {
+  extern __shared__ unsigned long long plan_scan[];   // [experts] exclusive (rows | tiles << 40)
+  __shared__ unsigned long long warp_sum[kPlanThreads / 32];
+  __shared__ uint32_t seg_first[kPlanMaxRanks + 1];   // first position of every owner's segment
+  __shared__ unsigned long long bucket[BMOE_EP_MAX_GROUPS + 2];
+  const uint32_t tid = threadIdx.x;
+  const uint32_t lane = tid & 31, warp = tid >> 5;
+  const uint32_t per_thread = (a.experts + kPlanThreads - 1) / kPlanThreads;   // <= 4
+  const uint32_t first = tid * per_thread;
+  for (uint32_t r = tid; r <= kPlanMaxRanks; r += kPlanThreads) seg_first[r] = a.experts;
+  for (uint32_t b = tid; b < BMOE_EP_MAX_GROUPS + 2; b += kPlanThreads) bucket[b] = 0;
+  __syncthreads();
+
+  // totals per expert (in packed order), and where each owner's segment starts
+  unsigned long long value[4];
+  unsigned long long mine = 0;
+  for (uint32_t j = 0; j < per_thread; ++j) {
+    const uint32_t i = first + j;
+    value[j] = 0;
+    if (i >= a.experts) continue;
+    const int32_t e = a.order[i];
+    unsigned long long rows = 0;
+    for (uint32_t r = 0; r < a.ranks; ++r) {
+      rows += static_cast<unsigned long long>(a.counts_all[static_cast<size_t>(r) * a.experts + e]);
+    }
+    const unsigned long long tiles = (rows + a.tile_m - 1) / a.tile_m;
+    value[j] = rows | (tiles << kTileShift);
+    mine += value[j];
+    const int32_t o = a.owner[e];
+    if ((i == 0 || a.owner[a.order[i - 1]] != o) && o >= 0 &&
+        static_cast<uint32_t>(o) < a.ranks) {
+      seg_first[o] = i;
+    }
+  }
+  // block-wide exclusive scan of the per-thread sums
+  unsigned long long inclusive = mine;
+  for (uint32_t d = 1; d < 32; d <<= 1) {
+    const unsigned long long up = __shfl_up_sync(0xffffffffu, inclusive, d);
+    if (lane >= d) inclusive += up;
+  }
+  if (lane == 31) warp_sum[warp] = inclusive;
+  __syncthreads();
+  if (warp == 0) {
+    unsigned long long w = warp_sum[lane];
+    for (uint32_t d = 1; d < 32; d <<= 1) {
+      const unsigned long long up = __shfl_up_sync(0xffffffffu, w, d);
+      if (lane >= d) w += up;
+    }
+    warp_sum[lane] = w;   // inclusive over warps
+  }
+  __syncthreads();
+  unsigned long long running = inclusive - mine + (warp == 0 ? 0ull : warp_sum[warp - 1]);
+  for (uint32_t j = 0; j < per_thread; ++j) {
+    const uint32_t i = first + j;
+    if (i < a.experts) plan_scan[i] = running;
+    running += value[j];
+  }
+  const unsigned long long grand = warp_sum[kPlanThreads / 32 - 1];
+  __syncthreads();
+  // an owner without experts starts where the next one does
+  if (tid == 0) {
+    seg_first[a.ranks] = a.experts;
+    for (int32_t r = static_cast<int32_t>(a.ranks) - 1; r >= 0; --r) {
+      if (seg_first[r] > seg_first[r + 1]) seg_first[r] = seg_first[r + 1];
+    }
+  }
+  __syncthreads();
+
+  const unsigned long long row_mask = (1ull << kTileShift) - 1;
+  const uint32_t local_first = seg_first[a.self];
+  for (uint32_t j = 0; j < per_thread; ++j) {
+    const uint32_t i = first + j;
+    if (i >= a.experts) continue;
+    const int32_t e = a.order[i];
+    const uint32_t o = static_cast<uint32_t>(a.owner[e]);
+    if (o >= a.ranks) continue;   // an expert nobody owns takes part in nothing
+    const uint32_t s0 = seg_first[o], s1 = seg_first[o + 1];
+    const unsigned long long at = plan_scan[i], seg = plan_scan[s0];
+    const unsigned long long seg_end = s1 < a.experts ? plan_scan[s1] : grand;
+    unsigned long long before_me = 0, from_me = 0;
+    for (uint32_t r = 0; r <= a.self; ++r) {
+      const unsigned long long c =
+          static_cast<unsigned long long>(a.counts_all[static_cast<size_t>(r) * a.experts + e]);
+      if (r < a.self) before_me += c; else from_me = c;
+    }
+    const unsigned long long row_in_owner = (at & row_mask) - (seg & row_mask);
+    a.row_base[e] = static_cast<int64_t>(row_in_owner + before_me);
+    uint32_t group = 0;
+    if (a.groups > 1) {
+      const unsigned long long tiles_before = (at >> kTileShift) - (seg >> kTileShift);
+      unsigned long long owner_tiles = (seg_end >> kTileShift) - (seg >> kTileShift);
+      if (owner_tiles == 0) owner_tiles = 1;
+      const unsigned long long g = tiles_before * a.groups / owner_tiles;
+      group = g < a.groups - 1 ? static_cast<uint32_t>(g) : a.groups - 1;
+    }
+    a.group_of[e] = static_cast<uint8_t>(group);
+    if (o == a.self) {
+      const uint32_t local = i - local_first;
+      a.group_local[local] = static_cast<uint8_t>(group);
+      a.expert_row[local] = static_cast<uint32_t>(row_in_owner);
+      a.local_rows[local] = static_cast<uint32_t>(value[j] & row_mask);
+      if (from_me != 0) atomicAdd(&bucket[a.groups], from_me);
+    } else if (from_me != 0) {
+      atomicAdd(&bucket[group], from_me);
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    uint32_t at = 0;
+    for (uint32_t b = 0; b < a.groups + 2; ++b) {
+      a.bucket_offset[b] = at;
+      at += static_cast<uint32_t>(bucket[b]);   // bucket groups + 1 (peer copies) stays empty
+    }
+    a.bucket_offset[a.groups + 2] = at;
+    const uint32_t l1 = seg_first[a.self + 1];
+    const unsigned long long owned =
+        ((l1 < a.experts ? plan_scan[l1] : grand) & row_mask) -
+        ((local_first < a.experts ? plan_scan[local_first] : grand) & row_mask);
+    a.totals[0] = static_cast<uint32_t>(owned < 0xffffffffull ? owned : 0xffffffffull);
+    a.totals[1] = owned > a.rows_cap ? 1u : 0u;
+  }
+}
+
 uint32_t device_sms() {
   int device = 0, sms = 0;
   if (cudaGetDevice(&device) != cudaSuccess ||
@@ -497,6 +649,39 @@ extern "C" int bmoe_ep_count(const int64_t* expert_ids_dev, uint64_t assignments
   bmoe::ep_count_kernel<<<grid, 256, 0, s>>>(
       expert_ids_dev, assignments, experts, parts_dev, shard_base_dev, bins, ids_out_dev,
       reinterpret_cast<unsigned long long*>(counts_dev));
+  return cudaPeekAtLastError() == cudaSuccess ? BMOE_OK : BMOE_CUDA_ERROR;
+}
+
+extern "C" int bmoe_ep_plan(const bmoe_ep_plan_args* args) {
+  if (args == nullptr) return BMOE_INVALID_ARGUMENT;
+  const bmoe_ep_plan_args& c = *args;
+  if (c.experts == 0 || c.experts > bmoe::kPlanMaxExperts || c.ranks == 0 ||
+      c.ranks > bmoe::kPlanMaxRanks || c.self >= c.ranks || c.groups == 0 ||
+      c.groups > BMOE_EP_MAX_GROUPS || c.tile_m == 0 || c.counts_all_dev == nullptr ||
+      c.owner_dev == nullptr || c.order_dev == nullptr || c.row_base_dev == nullptr ||
+      c.group_of_dev == nullptr || c.group_local_dev == nullptr || c.expert_row_dev == nullptr ||
+      c.local_rows_dev == nullptr || c.bucket_offset_dev == nullptr || c.totals_dev == nullptr) {
+    return BMOE_INVALID_ARGUMENT;
+  }
+  bmoe::PlanArgs a;
+  a.counts_all = c.counts_all_dev;
+  a.owner = c.owner_dev;
+  a.order = c.order_dev;
+  a.row_base = c.row_base_dev;
+  a.group_of = c.group_of_dev;
+  a.group_local = c.group_local_dev;
+  a.expert_row = c.expert_row_dev;
+  a.local_rows = c.local_rows_dev;
+  a.bucket_offset = c.bucket_offset_dev;
+  a.totals = c.totals_dev;
+  a.rows_cap = c.rows_cap;
+  a.experts = c.experts;
+  a.ranks = c.ranks;
+  a.self = c.self;
+  a.groups = c.groups;
+  a.tile_m = c.tile_m;
+  bmoe::ep_plan_kernel<<<1, bmoe::kPlanThreads, sizeof(unsigned long long) * c.experts,
+                         static_cast<cudaStream_t>(c.stream)>>>(a);
   return cudaPeekAtLastError() == cudaSuccess ? BMOE_OK : BMOE_CUDA_ERROR;
 }
 
@@ -703,6 +888,7 @@ extern "C" int bmoe_peer_copy_batch(const bmoe_copy_item* items, uint32_t count,
 namespace bmoe {
 cudaError_t preload_exchange_kernels() {
   cudaError_t rc = preload_one(ep_count_kernel);
+  if (rc == cudaSuccess) rc = preload_one(ep_plan_kernel);
   if (rc == cudaSuccess) rc = preload_one(ep_route_kernel);
   if (rc == cudaSuccess) rc = preload_one(ep_dispatch_kernel);
   if (rc == cudaSuccess) rc = preload_one(ep_dispatch_bulk_kernel);

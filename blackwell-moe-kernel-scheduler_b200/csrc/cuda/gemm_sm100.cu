@@ -150,6 +150,14 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   const bool leader = cta_rank == 0;
   const uint32_t unit = PAIR ? blockIdx.x / 2 : blockIdx.x;
   const uint32_t units = PAIR ? gridDim.x / 2 : gridDim.x;
+  // Tile total: a launch parameter, or read from where the worklist builder left it.
+  uint32_t tile_count = p.tile_count;
+  uint32_t main_end = p.main_end;
+  if (p.tile_count_dev != nullptr) {
+    const uint32_t on_device = *p.tile_count_dev;
+    tile_count = on_device < p.tile_count ? on_device : p.tile_count;
+    main_end = tile_count;
+  }
 
   // Barrier helpers that hide where the barrier lives. In pair mode the
   // operand-full, accumulator-empty and slot-empty barriers of the LEADER are
@@ -192,8 +200,8 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   if (warp == 2 && lane == 0 && leader) {
     if (p.sched_mode == kSchedQueue) {
       first_claim = atomicAdd(&p.queue[0], p.claim_size);
-      if (first_claim < p.main_end) first_index = first_claim;
-    } else if (unit < p.tile_count) {
+      if (first_claim < main_end) first_index = first_claim;
+    } else if (unit < tile_count) {
       first_index = unit;
     }
     if (first_index != 0xffffffffu) {
@@ -356,7 +364,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       };
 
       if (p.sched_mode == kSchedStatic) {
-        for (uint32_t t = unit; alive && t < p.tile_count; t += units) {
+        for (uint32_t t = unit; alive && t < tile_count; t += units) {
           alive = publish(static_cast<int32_t>(t));
         }
       } else if (p.sched_mode == kSchedQueue) {
@@ -367,8 +375,8 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           if (!pace()) { alive = false; break; }
           const uint32_t begin = claimed_ahead ? first_claim : atomicAdd(&p.queue[0], p.claim_size);
           claimed_ahead = false;
-          if (begin >= p.main_end) break;
-          const uint32_t end = min(begin + p.claim_size, p.main_end);
+          if (begin >= main_end) break;
+          const uint32_t end = min(begin + p.claim_size, main_end);
           for (uint32_t t = begin; alive && t < end; ++t) {
             if (t != begin && !pace()) { alive = false; break; }
             alive = publish(static_cast<int32_t>(t));
@@ -378,13 +386,13 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         while (alive) {
           if (!pace()) { alive = false; break; }
           const uint32_t t = atomicAdd(&p.queue[1], 1u);
-          if (t >= p.tile_count) break;
+          if (t >= tile_count) break;
           alive = publish(static_cast<int32_t>(t));
         }
       } else {  // kSchedClc: one CTA (pair) per tile, steal units not yet started
         uint32_t clc_round = 0;
         uint32_t t = unit;
-        if (t < p.tile_count) alive = publish(static_cast<int32_t>(t));
+        if (t < tile_count) alive = publish(static_cast<int32_t>(t));
         while (alive) {
           if (!pace()) { alive = false; break; }
           ptx::mbar_arrive_expect_tx(bar_clc, 16);
@@ -400,7 +408,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           ptx::fence_async_shared();
           if (!got) break;  // no pending unit left; must not ask again
           t = PAIR ? stolen / 2 : stolen;
-          if (t < p.tile_count) alive = publish(static_cast<int32_t>(t));
+          if (t < tile_count) alive = publish(static_cast<int32_t>(t));
         }
       }
       if (alive) publish(kSentinel);
@@ -768,7 +776,9 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       const uint32_t exited = atomicAdd(&p.queue[2], 1u);
       if (exited + 1 == units) {
         p.queue[0] = 0;
-        p.queue[1] = p.main_end;
+        // (with a device-side tile total there is no singly-claimed tail: park the
+        // tail counter at the capacity so that it never hands anything out)
+        p.queue[1] = p.tile_count_dev != nullptr ? p.tile_count : main_end;
         p.queue[2] = 0;
         __threadfence();
       }

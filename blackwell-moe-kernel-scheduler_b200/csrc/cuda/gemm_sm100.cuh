@@ -90,6 +90,10 @@ struct GemmParams {
   // ragged edge then also loads rows of the next expert; they only feed accumulator
   // rows beyond valid_m, which are never written.
   const unsigned long long* a_row_offsets;
+  // Optional: the tile total lives in device memory (written by the worklist builder of
+  // the same stream; the host never saw the counts). tile_count is then only the
+  // capacity of `tiles`, and the queue's chunked part ends at the tile total.
+  const uint32_t* tile_count_dev;
 };
 
 // Words per CTA of GemmParams::trace (SM cycles):

@@ -12,6 +12,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <cstddef>
 #include <cstdint>
 #include <cstring>
 #include <new>
@@ -248,9 +249,18 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
   // ---- argument checks, in the reference's order ----
   const bool packed = a.packed_a != nullptr;
   const bool pushed = a.results_pushed != 0;
+  const bool dev_counts = a.tokens_per_expert_dev != nullptr;
   if ((a.a == nullptr && !packed) || a.b == nullptr || (a.d == nullptr && !pushed) ||
-      a.tokens_per_expert == nullptr || a.experts == 0 || a.n == 0 || a.k == 0 ||
-      a.n % 8 != 0 || a.k % 8 != 0) {
+      (a.tokens_per_expert == nullptr && !dev_counts) || a.experts == 0 || a.n == 0 ||
+      a.k == 0 || a.n % 8 != 0 || a.k % 8 != 0) {
+    return BMOE_INVALID_ARGUMENT;
+  }
+  // counts that the host never sees: everything that is sized from them uses capacities
+  if (dev_counts && (!packed || !pushed || a.hybrid_tail_tiles != 0 ||
+                     (a.scheduler != BMOE_SCHED_EXPERT_ORDER &&
+                      a.scheduler != BMOE_SCHED_STATIC_PERSISTENT &&
+                      a.scheduler != BMOE_SCHED_COMPACTED &&
+                      a.scheduler != BMOE_SCHED_DYNAMIC_QUEUE))) {
     return BMOE_INVALID_ARGUMENT;
   }
   if (packed && (misaligned16(a.packed_a) || a.packed_rows == 0)) return BMOE_INVALID_ARGUMENT;
@@ -281,16 +291,20 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
 
   uint32_t active = 0;
   uint64_t routed_rows = 0;
+  // with device-side counts every expert may turn out active: each needs its weights
+  std::vector<uint32_t> assumed_rows;
+  if (dev_counts) assumed_rows.assign(a.experts, 1u);
+  const uint32_t* const host_counts = dev_counts ? assumed_rows.data() : a.tokens_per_expert;
   for (uint32_t e = 0; e < a.experts; ++e) {
-    if (a.tokens_per_expert[e] == 0) continue;
+    if (host_counts[e] == 0) continue;
     if ((!packed && (a.a[e] == nullptr || misaligned16(a.a[e]))) || a.b[e] == nullptr ||
         misaligned16(a.b[e]) || (!pushed && (a.d[e] == nullptr || misaligned16(a.d[e])))) {
       return BMOE_INVALID_ARGUMENT;
     }
-    routed_rows += a.tokens_per_expert[e];
+    routed_rows += host_counts[e];
     ++active;
   }
-  if (packed && routed_rows > a.packed_rows) return BMOE_INVALID_ARGUMENT;
+  if (packed && !dev_counts && routed_rows > a.packed_rows) return BMOE_INVALID_ARGUMENT;
   plan->stats.active_experts = active;
   plan->default_stream = static_cast<cudaStream_t>(a.stream);
   plan->setup_stream = plan->default_stream;
@@ -309,6 +323,7 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
   // per FLOP) unless 256-row tiles would pad the routed rows by more than 10 %
   // over 128-row tiles, as they do for small-M (decode-like) routing.
   uint32_t cta_group = a.cta_group;
+  if (cta_group == 0 && dev_counts) cta_group = a.n > 128 ? 2u : 1u;
   if (cta_group == 0) {
     uint64_t padded128 = 0, padded256 = 0;
     for (uint32_t e = 0; e < a.experts; ++e) {
@@ -324,21 +339,19 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
   if (cta_group == 1 && !out_f32) {
     if (a.tile_n != 0) {
       tile_n = a.tile_n;
-    } else {
+    } else if (!dev_counts) {
       // More tiles than SMs: 256-column tiles (fewest operand bytes per FLOP). Fewer:
       // the launch is one wave and is bound by how many bytes of the weight stream
-      // each CTA keeps in flight, so the tiles are narrowed (128, then 64 columns) as
-      // long as they still fit one wave. The k order of a tile does not depend on its
-      // width, so results do not change.
+      // each CTA keeps in flight, so 128-column tiles are used as long as they still
+      // fit one wave (twice the CTAs pulling on memory). 64-column tiles (tile_n = 64,
+      // explicit only) measured no faster: twice the CTAs again, but each keeps less in
+      // flight. The k order of a tile does not depend on its width, so results do not
+      // change.
       const uint32_t wave = a.cta_count != 0 ? a.cta_count : static_cast<uint32_t>(sm_count);
       tile_n = 256u;
-      if (bmoe_host_tile_count(a.tokens_per_expert, a.experts, a.n, tile_m, 256u) < wave) {
-        for (uint32_t width = 128u; width >= 64u; width /= 2) {
-          if (bmoe_host_tile_count(a.tokens_per_expert, a.experts, a.n, tile_m, width) > wave) {
-            break;
-          }
-          tile_n = width;
-        }
+      if (bmoe_host_tile_count(a.tokens_per_expert, a.experts, a.n, tile_m, 256u) < wave &&
+          bmoe_host_tile_count(a.tokens_per_expert, a.experts, a.n, tile_m, 128u) <= wave) {
+        tile_n = 128u;
       }
       if (a.n <= 64) tile_n = 64u;
     }
@@ -352,8 +365,10 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
   const uint32_t unit_budget = a.cta_count != 0 ? a.cta_count : (sm_units ? sm_units : 1u);
   const Resolved policy = resolve_policy(a, tile_m, tile_n, unit_budget);
 
+  // device-side counts: sum(ceil(M_e / tile_m)) <= floor(rows / tile_m) + experts
   const uint64_t tile_total =
-      bmoe_host_tile_count(a.tokens_per_expert, a.experts, a.n, tile_m, tile_n);
+      dev_counts ? (a.packed_rows / tile_m + a.experts) * ((a.n + tile_n - 1) / tile_n)
+                 : bmoe_host_tile_count(a.tokens_per_expert, a.experts, a.n, tile_m, tile_n);
   if (tile_total == 0 || tile_total > 0x7fffffffull) return BMOE_INVALID_ARGUMENT;
   const uint32_t tiles = static_cast<uint32_t>(tile_total);
 
@@ -390,7 +405,9 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
   const uint32_t main_end = tiles - tail;
   std::memset(stage, 0, off_counts);
   reinterpret_cast<uint32_t*>(stage)[1] = main_end;  // tail counter starts after the main part
-  std::memcpy(stage + off_counts, a.tokens_per_expert, sizeof(uint32_t) * a.experts);
+  if (!dev_counts) {
+    std::memcpy(stage + off_counts, a.tokens_per_expert, sizeof(uint32_t) * a.experts);
+  }
   CUtensorMap* const maps_a = reinterpret_cast<CUtensorMap*>(stage + off_maps);
   CUtensorMap* const maps_b = maps_a + a.experts;
   CUtensorMap* const maps_d = maps_b + a.experts;
@@ -411,7 +428,7 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
     return BMOE_CUDA_ERROR;
   }
   for (uint32_t e = 0; e < a.experts; ++e) {
-    const uint64_t rows = a.tokens_per_expert[e];
+    const uint64_t rows = host_counts[e];
     if (rows == 0) {
       if (!packed || e != 0) std::memset(&maps_a[e], 0, sizeof(CUtensorMap));
       std::memset(&maps_b[e], 0, sizeof(CUtensorMap));
@@ -442,7 +459,9 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
   request.tile_n = tile_n;
   request.order = policy.order;
   request.raster = raster;
-  int rc = bmoe_worklist_build(reinterpret_cast<const uint32_t*>(meta + off_counts), &request,
+  int rc = bmoe_worklist_build(dev_counts ? a.tokens_per_expert_dev
+                                          : reinterpret_cast<const uint32_t*>(meta + off_counts),
+                               &request,
                                static_cast<bmoe_tile*>(plan->worklist.ptr), tiles,
                                plan->workspace.ptr, stream);
   if (rc != BMOE_OK) return rc;
@@ -474,12 +493,18 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
         static_cast<const uint8_t*>(plan->workspace.ptr) + layout.off_row_offsets);
   }
   plan->needs_push = pushed;
+  if (dev_counts) {
+    p.tile_count_dev = reinterpret_cast<const uint32_t*>(
+        static_cast<const uint8_t*>(plan->workspace.ptr) + layout.off_totals +
+        offsetof(bmoe_worklist_totals, total_tiles));
+  }
 
   plan->tile_n = tile_n;
   plan->stats_n = a.n;
   plan->cta_group = cta_group;
   plan->out_f32 = out_f32;
   plan->units = policy.one_cta_per_tile ? tiles : (tiles < unit_budget ? tiles : unit_budget);
+  if (dev_counts) plan->units = unit_budget;   // the tile total is not known here
 
   plan->stats.threadblock_count = plan->units * cta_group;
   plan->stats.workspace_bytes =

@@ -88,6 +88,7 @@ class GroupedGemmPlan:
         packed_a: int = 0,
         packed_rows: int = 0,
         results_pushed: bool = False,
+        tokens_per_expert_dev: int = 0,
     ) -> int:
         """Pointer-array form of the reference arguments. Returns a status.
         ``packed_a`` / ``packed_rows``: base and row capacity of ONE buffer holding all
@@ -129,6 +130,7 @@ class GroupedGemmPlan:
             packed_rows=int(packed_rows),
             results_pushed=1 if results_pushed else 0,
             reserved0=0,
+            tokens_per_expert_dev=int(tokens_per_expert_dev) or None,
         )
         return int(self._lib.bmoe_plan_initialize(self._handle, C.byref(args)))
 
@@ -162,6 +164,25 @@ class GroupedGemmPlan:
         if single_a_map:
             options.update(packed_a=a.data_ptr(), packed_rows=int(a.shape[0]))
         return self.initialize(a_ptrs, b_ptrs, d_ptrs, counts, n, k, **options)
+
+    def initialize_packed_device_counts(self, a, w, counts_dev_ptr: int, **options) -> int:
+        """Packed form whose counts exist only on the device: ``counts_dev_ptr`` points at
+        uint32 [E] rows per expert, written by work that precedes this call in the stream
+        (for example ``bmoe_ep_plan``). Nothing is read back: the worklist is built from
+        the device counts, the kernel takes the tile total from device memory, the grid is
+        the full persistent grid, and the results leave through ``set_push``. ``a`` is
+        the packed row buffer (its row count is the capacity)."""
+        experts = int(w.shape[0])
+        n, k = int(w.shape[1]), int(w.shape[2])
+        if experts == 0 or int(a.shape[1]) != k or not (a.is_contiguous() and w.is_contiguous()):
+            return _capi.INVALID_ARGUMENT
+        b_ptrs = np.uint64(w.data_ptr()) + np.arange(experts, dtype=np.uint64) * np.uint64(n * k * 2)
+        zeros = np.zeros(experts, dtype=np.uint64)
+        self._keep = (a, w)
+        return self.initialize(zeros, b_ptrs, zeros, np.zeros(experts, dtype=np.uint32), n, k,
+                               packed_a=a.data_ptr(), packed_rows=int(a.shape[0]),
+                               results_pushed=True, tokens_per_expert_dev=counts_dev_ptr,
+                               **options)
 
     # --------------------------------------------------------------- run --
     def run(self, stream=None) -> int:

@@ -218,7 +218,7 @@ class FusedExpertParallelLayer:
                  exchange_groups: int = 4, dispatch_ctas: int = 0, wait_budget_ns: int = 0,
                  push_results: bool = True, exchange_sms: int = 16,
                  expert_parts: Sequence[int] | None = None, bulk_copies: bool = False,
-                 copy_engine_min_bytes: int = 0, **plan_options):
+                 copy_engine_min_bytes: int = 0, device_plan: bool = True, **plan_options):
         """``rows_cap``: packed rows this rank can own; ``assignments_cap``: local
         assignments (tokens x top_k) per step; ``exchange_groups``: groups the
         experts of a rank are split into for the overlap (1 = no overlap).
@@ -235,6 +235,12 @@ class FusedExpertParallelLayer:
         GEMM must then be a persistent policy (its grid is what leaves the SMs free).
         0 = share: ``dispatch_ctas`` 256-thread CTAs (default 7/16 of the SMs) that fit
         beside resident GEMM CTAs; any policy.
+
+        ``device_plan``: derive the step's tables from the all-gathered counts with one small
+        kernel (``bmoe_ep_plan``) and hand the grouped GEMM its counts in device memory, so
+        that a step has no host synchronisation at all (the host only enqueues). Needs
+        ``push_results`` and no copy-engine blocks; otherwise the host plans with numpy after
+        reading the counts back.
 
         ``copy_engine_min_bytes`` (multi-rank only): an (expert, source) block of at least
         this size travels as one peer copy issued by the host (copy engines, no SMs)
@@ -310,7 +316,10 @@ class FusedExpertParallelLayer:
         self._off_buckets = self._off_expert_row + 4 * self.experts
         self._off_copy_mask = self._off_buckets + 4 * (_capi.EP_MAX_GROUPS + 3)
         self._off_staging = (self._off_copy_mask + 4 * _capi.EP_MAX_GROUPS + 7) // 8 * 8
-        self._table_bytes = self._off_staging + 8 * self.experts
+        # | uint32 rows per local expert [E] | uint32 totals [2] (device planner only)
+        self._off_local_rows = self._off_staging + 8 * self.experts
+        self._off_totals = self._off_local_rows + 4 * self.experts
+        self._table_bytes = self._off_totals + 8
         self._stage = torch.empty(self._table_bytes, dtype=torch.uint8).pin_memory()
         self._tables = torch.empty(self._table_bytes, dtype=torch.uint8, device=dev)
         self._owner_dev = torch.tensor(self.owner, dtype=torch.int32, device=dev)
@@ -331,6 +340,18 @@ class FusedExpertParallelLayer:
         self._ev_start = torch.cuda.Event()
         self._ev_comm = torch.cuda.Event()
         self.routes = None
+        persistent = str(scheduler) in ("expert_order", "baseline", "static_persistent", "static",
+                                        "sorted_static", "compacted", "dynamic_queue", "dynamic",
+                                        "0", "1", "2", "3")
+        self.device_plan = bool(device_plan) and self.push_results and not self.copy_min_rows \
+            and persistent and self.experts <= 4096 and len(self.local_shards) > 0 \
+            and not self.plan_options.get("hybrid_tail_tiles")
+        if self.device_plan:
+            order = np.lexsort((np.arange(self.experts), np.asarray(self.owner)))
+            self._order_dev = torch.tensor(order, dtype=torch.int32, device=dev)
+            self._counts_all_dev = torch.zeros(world * self.experts, dtype=torch.int64, device=dev)
+            self._tables.zero_()
+        self._last_local_m = None
         self.copy_bytes = 0      # bytes of the last step that went as peer copies
         self._copy_streams_used = []
         if self.copy_min_rows:
@@ -526,29 +547,52 @@ class FusedExpertParallelLayer:
         self._scratch.zero_()          # cursors and counters of the step; before the host waits
         if sharded:
             flat_ids = shard_ids
-        if self.world > 1:
-            flat = torch.empty(self.world * self.experts, dtype=torch.int64, device=dev)
-            dist.all_gather_into_tensor(flat, local_counts, group=self.group)
-            counts_all = flat.reshape(self.world, self.experts).cpu().numpy()
-        else:
-            counts_all = local_counts.reshape(1, -1).cpu().numpy()
-        step = self._planner.step(counts_all, self.copy_min_rows)
-        if step["total_local"] > self.rows_cap:
-            raise RuntimeError("routed rows exceed the packed buffer capacity")
-        stage = self._stage.numpy()
         e = self.experts
-        stage[:8 * e].view(np.int64)[:] = step["row_base"]
-        stage[8 * e:9 * e] = step["group_of"]
-        stage[9 * e:9 * e + len(step["group_local"])] = step["group_local"]
-        local_m = step["local_m"]
-        stage[self._off_expert_row:self._off_expert_row + 4 * len(local_m)].view(np.uint32)[:] = \
-            np.cumsum(local_m) - local_m
-        buckets = step["bucket_offset"]
-        stage[self._off_buckets:self._off_buckets + 4 * len(buckets)].view(np.uint32)[:] = buckets
-        mask = step["copy_mask"]
-        stage[self._off_copy_mask:self._off_copy_mask + 4 * len(mask)].view(np.uint32)[:] = mask
-        stage[self._off_staging:self._off_staging + 8 * e].view(np.int64)[:] = step["staging_row_base"]
-        self._tables.copy_(self._stage, non_blocking=True)
+        step = None
+        if self.device_plan:
+            # counts stay on the device: all-gather, one planning launch, no read-back
+            flat = self._counts_all_dev
+            if self.world > 1:
+                dist.all_gather_into_tensor(flat, local_counts, group=self.group)
+            else:
+                flat = local_counts
+            t = self._tables.data_ptr()
+            args = _capi.EpPlanArgs(
+                counts_all_dev=flat.data_ptr(), owner_dev=self._owner_dev.data_ptr(),
+                order_dev=self._order_dev.data_ptr(), row_base_dev=t, group_of_dev=t + 8 * e,
+                group_local_dev=t + 9 * e, expert_row_dev=t + self._off_expert_row,
+                local_rows_dev=t + self._off_local_rows,
+                bucket_offset_dev=t + self._off_buckets, totals_dev=t + self._off_totals,
+                rows_cap=self.rows_cap, experts=e, ranks=self.world, self=self.rank,
+                groups=self.groups, tile_m=self.tile_m, stream=main.cuda_stream or None)
+            _capi.check(self._lib.bmoe_ep_plan(C.byref(args)), "bmoe_ep_plan")
+            self.launches += 1
+            self._last_local_m = None
+        else:
+            if self.world > 1:
+                flat = torch.empty(self.world * self.experts, dtype=torch.int64, device=dev)
+                dist.all_gather_into_tensor(flat, local_counts, group=self.group)
+                counts_all = flat.reshape(self.world, self.experts).cpu().numpy()
+            else:
+                counts_all = local_counts.reshape(1, -1).cpu().numpy()
+            step = self._planner.step(counts_all, self.copy_min_rows)
+            if step["total_local"] > self.rows_cap:
+                raise RuntimeError("routed rows exceed the packed buffer capacity")
+            stage = self._stage.numpy()
+            stage[:8 * e].view(np.int64)[:] = step["row_base"]
+            stage[8 * e:9 * e] = step["group_of"]
+            stage[9 * e:9 * e + len(step["group_local"])] = step["group_local"]
+            local_m = step["local_m"]
+            stage[self._off_expert_row:self._off_expert_row + 4 * len(local_m)].view(np.uint32)[:] = \
+                np.cumsum(local_m) - local_m
+            buckets = step["bucket_offset"]
+            stage[self._off_buckets:self._off_buckets + 4 * len(buckets)].view(np.uint32)[:] = buckets
+            mask = step["copy_mask"]
+            stage[self._off_copy_mask:self._off_copy_mask + 4 * len(mask)].view(np.uint32)[:] = mask
+            stage[self._off_staging:self._off_staging + 8 * e].view(np.int64)[:] = \
+                step["staging_row_base"]
+            self._tables.copy_(self._stage, non_blocking=True)
+            self._last_local_m = step["local_m"].tolist()
         self.epoch += 1
         routes = None
         if record_routes:
@@ -583,20 +627,27 @@ class FusedExpertParallelLayer:
         self._dispatch(x, assignments, _capi.EP_LOCAL, main)
         if self.copy_min_rows:
             self._send_copies(x, step, counts_all[self.rank], assignments)
+
         if self.world > 1 and not self.exchange_sms:
             push_remote()
         mark("local_rows")
 
-        total_local = step["total_local"]
+        total_local = step["total_local"] if step is not None else -1
         if total_local:
             # one A descriptor over the packed buffer, cached B descriptors and (when the
             # epilogue pushes the rows) no D descriptors: a re-plan encodes next to nothing
-            _capi.check(self.plan.initialize_packed(self.a, w_local, self.d, step["local_m"],
-                                                    scheduler=self.scheduler, stream=main,
-                                                    single_a_map=True,
-                                                    results_pushed=self.push_results,
-                                                    **self.plan_options),
-                        "bmoe_plan_initialize")
+            if step is None:
+                _capi.check(self.plan.initialize_packed_device_counts(
+                    self.a, w_local, self._tables.data_ptr() + self._off_local_rows,
+                    scheduler=self.scheduler, stream=main, **self.plan_options),
+                    "bmoe_plan_initialize")
+            else:
+                _capi.check(self.plan.initialize_packed(self.a, w_local, self.d, step["local_m"],
+                                                        scheduler=self.scheduler, stream=main,
+                                                        single_a_map=True,
+                                                        results_pushed=self.push_results,
+                                                        **self.plan_options),
+                            "bmoe_plan_initialize")
             if self.world > 1:
                 _capi.check(self.plan.set_gate(self.shared.local["flags"].data_ptr(), self.epoch,
                                                self.world, self.rank,
@@ -652,8 +703,19 @@ class FusedExpertParallelLayer:
             y = out
             mark("weighted_sum")
         self._marks = marks
-        self.last_local_m = step["local_m"].tolist()
         return y
+
+    @property
+    def last_local_m(self):
+        """Rows per local expert of the last step (read back on demand when the step was
+        planned on the device)."""
+        if self._last_local_m is None:
+            import torch
+
+            rows = self._tables[self._off_local_rows:self._off_local_rows
+                                + 4 * len(self.local_shards)].cpu().numpy().view(np.uint32)
+            self._last_local_m = [int(r) for r in rows]
+        return self._last_local_m
 
     def poll(self):
         status, report = self.plan.poll()
@@ -661,6 +723,11 @@ class FusedExpertParallelLayer:
             raise _capi.EngineError(
                 status, f"grouped GEMM (site {report.code}, cta {report.cta}, "
                         f"group {report.stage}, rank {report.aux})")
+        if self.device_plan:
+            totals = self._tables[self._off_totals:self._off_totals + 8].cpu().numpy().view(np.uint32)
+            if int(totals[1]) != 0:
+                raise RuntimeError(f"routed rows ({int(totals[0])}) exceed the packed buffer "
+                                   f"capacity ({self.rows_cap})")
         word = int(self._wait_status.item()) & 0xffffffff
         if word:
             self._wait_status.zero_()   # reported once; the layer stays usable

@@ -312,8 +312,8 @@ typedef struct bmoe_gemm_args {
   uint32_t claim_size;
   uint32_t hybrid_tail_tiles;
   uint32_t cta_count;
-  uint32_t tile_n;    /* 64, 128 or 256 output columns per tile; 0 = the widest of them
-                         that still yields at least one tile per SM (single-CTA tiles) */
+  uint32_t tile_n;    /* 64, 128 or 256 output columns per tile; 0 = 256, or 128 when the
+                         problem is a single wave either way (single-CTA tiles) */
   uint32_t cta_group; /* 1 = 128-row tiles, 2 = CTA pairs computing 256 x 256 tiles,
                          0 = chosen from the routing (pairs unless they pad > 10 % more) */
   int32_t raster_along_m;
@@ -333,6 +333,17 @@ typedef struct bmoe_gemm_args {
    * which must then be set before run); d[] is ignored and no D descriptor is made. */
   uint32_t results_pushed;
   uint32_t reserved0;
+  /* Counts that only exist on the device (appended; NULL = the host array above). When
+   * set, uint32 [experts] in device memory holds the rows per expert, written by work
+   * that precedes initialize in `stream`; the host never reads it, so a step needs no
+   * host synchronisation between routing and the GEMM launch. The worklist is built from
+   * it on the device, the kernel reads the tile total from device memory and the grid is
+   * the full persistent grid. Requires packed_a (packed_rows = row capacity of the
+   * buffer, an upper bound of the routed rows), results_pushed = 1, cta_group 1 or 2
+   * (0 = 2 when n > 128), tile_n 0 (= 256) or explicit, a persistent policy
+   * (expert_order, static_persistent, compacted, dynamic_queue; no hybrid tail).
+   * tokens_per_expert is then ignored; stats report capacities. */
+  const uint32_t* tokens_per_expert_dev;
 } bmoe_gemm_args;
 
 /* blackwell_moe::GroupedGemmPlanStats (grouped_gemm.cuh:42-46) + extensions. */
@@ -524,6 +535,37 @@ int bmoe_combine_topk(const void* const* src_bases_dev, uint32_t n_src,
 int bmoe_ep_count(const int64_t* expert_ids_dev, uint64_t assignments, uint32_t experts,
                   const int64_t* parts_dev, const int64_t* shard_base_dev, uint32_t bins,
                   int64_t* ids_out_dev, int64_t* counts_dev, void* stream);
+
+typedef struct bmoe_ep_plan_args {
+  const int64_t* counts_all_dev;   /* [ranks, experts] routed rows per (source rank, expert),
+                                      the all-gathered result of bmoe_ep_count */
+  const int32_t* owner_dev;        /* [experts] owning rank */
+  const int32_t* order_dev;        /* [experts] expert ids sorted by (owner, id) */
+  int64_t* row_base_dev;           /* out [experts]: first row of (expert, this rank) in the
+                                      owner's packed A */
+  uint8_t* group_of_dev;           /* out [experts]: exchange group of the expert on its owner */
+  uint8_t* group_local_dev;        /* out [experts of this rank], in packed order */
+  uint32_t* expert_row_dev;        /* out [experts of this rank]: first packed row */
+  uint32_t* local_rows_dev;        /* out [experts of this rank]: rows (the GEMM's counts) */
+  uint32_t* bucket_offset_dev;     /* out [groups + 3], as bmoe_ep_route reads it */
+  uint32_t* totals_dev;            /* out [2]: rows this rank owns in this step; 1 if that
+                                      exceeds rows_cap (the step's results are then invalid) */
+  uint64_t rows_cap;
+  uint32_t experts;                /* <= 4096 */
+  uint32_t ranks;
+  uint32_t self;
+  uint32_t groups;
+  uint32_t tile_m;                 /* rows per tile of the grouped GEMM (group balance) */
+  void* stream;
+} bmoe_ep_plan_args;
+
+/* Tables of one exchange step, derived on the device from the count matrix (one small
+ * launch): where every (expert, source) block starts in its owner's packed A, the
+ * exchange groups (contiguous runs of an owner's experts with about equal tile counts),
+ * this rank's bucket sizes, and the rows per local expert. Same integer arithmetic as
+ * the host planner of the Python layer; with it a step needs no host synchronisation.
+ * No counterpart in the reference (it has no multi-GPU path). */
+int bmoe_ep_plan(const bmoe_ep_plan_args* args);
 
 typedef struct bmoe_ep_route_args {
   const int64_t* expert_ids_dev;   /* [assignments] expert of assignment i (token i / top_k);

@@ -178,7 +178,8 @@ def test_single_rank_fused_layer_and_gate(engine):
 
     ids, x, w = make_problem()
     want = reference_output(engine, x, ids, w, 4)
-    for push, opts in ((False, {}), (True, {"cta_group": 1}), (True, {"scheduler": "clc"})):
+    for push, opts in ((False, {}), (True, {"cta_group": 1}), (True, {"scheduler": "clc"}),
+                       (True, {"device_plan": False})):
         plain = ep_fused.FusedExpertParallelLayer([0] * 40, 512, 320, rank=0, world=1,
                                                   rows_cap=2400, assignments_cap=2400,
                                                   push_results=push, **opts)
@@ -309,6 +310,73 @@ def test_single_rank_fused_layer_and_gate(engine):
         plan.close()
 
 
+def test_device_planner_equals_host_planner(engine):
+    """bmoe_ep_plan (the step tables derived on the device, so that a step needs no host
+    synchronisation) against the numpy planner, table for table, over random count
+    matrices, owner maps, group counts and tile heights - including owners without
+    experts, empty experts and a single rank."""
+    import ctypes as C
+
+    import torch
+
+    from bmoe_b200 import ep_fused
+
+    cap = engine._capi
+    lib = cap.load()
+    rng = np.random.default_rng(77)
+    for trial in range(40):
+        world = int(rng.integers(1, 9))
+        experts = int(rng.integers(1, 300)) if trial % 5 else int(rng.integers(1000, 4097))
+        groups = int(rng.integers(1, cap.EP_MAX_GROUPS + 1))
+        tile_m = int(rng.choice([128, 256, 16]))
+        owner = rng.integers(0, world, size=experts)
+        if world > 2:
+            owner[owner == 1] = 0                      # a rank that owns nothing
+        counts_all = (rng.integers(0, 900, size=(world, experts)) *
+                      (rng.random((world, experts)) > 0.3)).astype(np.int64)
+        order = np.lexsort((np.arange(experts), owner))
+        dev = "cuda"
+        counts_dev = torch.from_numpy(counts_all).to(dev)
+        owner_dev = torch.from_numpy(owner.astype(np.int32)).to(dev)
+        order_dev = torch.from_numpy(order.astype(np.int32)).to(dev)
+        for rank in sorted(set([0, world - 1, int(rng.integers(0, world))])):
+            want = ep_fused.plan_step(counts_all, owner.tolist(), rank, groups, tile_m)
+            n_local = len(want["local_experts"])
+            row_base = torch.full((experts,), -7, dtype=torch.int64, device=dev)
+            group_of = torch.full((experts,), 255, dtype=torch.uint8, device=dev)
+            group_local = torch.full((max(1, experts),), 255, dtype=torch.uint8, device=dev)
+            expert_row = torch.zeros(max(1, experts), dtype=torch.int32, device=dev)
+            local_rows = torch.zeros(max(1, experts), dtype=torch.int32, device=dev)
+            buckets = torch.zeros(cap.EP_MAX_GROUPS + 3, dtype=torch.int32, device=dev)
+            totals = torch.zeros(2, dtype=torch.int32, device=dev)
+            rows_cap = int(sum(want["local_m"])) + (0 if trial % 7 else -1)
+            args = cap.EpPlanArgs(
+                counts_all_dev=counts_dev.data_ptr(), owner_dev=owner_dev.data_ptr(),
+                order_dev=order_dev.data_ptr(), row_base_dev=row_base.data_ptr(),
+                group_of_dev=group_of.data_ptr(), group_local_dev=group_local.data_ptr(),
+                expert_row_dev=expert_row.data_ptr(), local_rows_dev=local_rows.data_ptr(),
+                bucket_offset_dev=buckets.data_ptr(), totals_dev=totals.data_ptr(),
+                rows_cap=max(0, rows_cap), experts=experts, ranks=world, self=rank,
+                groups=groups, tile_m=tile_m, stream=None)
+            assert lib.bmoe_ep_plan(C.byref(args)) == 0
+            torch.cuda.synchronize()
+            key = (trial, world, experts, groups, tile_m, rank)
+            assert np.array_equal(row_base.cpu().numpy(), want["row_base"]), key
+            assert np.array_equal(group_of.cpu().numpy(), want["group_of"]), key
+            assert np.array_equal(group_local.cpu().numpy()[:n_local], want["group_local"]), key
+            local_m = np.asarray(want["local_m"], dtype=np.int64)
+            assert np.array_equal(local_rows.cpu().numpy()[:n_local], local_m), key
+            assert np.array_equal(expert_row.cpu().numpy()[:n_local],
+                                  np.cumsum(local_m) - local_m), key
+            assert np.array_equal(buckets.cpu().numpy()[:groups + 3],
+                                  want["bucket_offset"].astype(np.int64)), key
+            got_totals = totals.cpu().numpy()
+            assert int(got_totals[0]) == int(local_m.sum()), key
+            assert int(got_totals[1]) == (1 if local_m.sum() > max(0, rows_cap) else 0), key
+    bad = cap.EpPlanArgs(experts=5000, ranks=1, groups=1, tile_m=128)
+    assert lib.bmoe_ep_plan(C.byref(bad)) == cap.INVALID_ARGUMENT
+
+
 def _ep_worker(rank, world, port, tmpdir):
     for p in (ROOT, ROOT / "tests", ROOT / "oracle"):
         sys.path.insert(0, str(p))
@@ -377,6 +445,23 @@ def _ep_worker(rank, world, port, tmpdir):
         fused.close()
         # blocks of 8 rows and more travel as peer copies (copy engines), the rest as SM
         # stores; both kinds of flags gate the GEMM
+        hosted = ep_fused.FusedExpertParallelLayer(owner, 512, 320, rank=rank, world=world,
+                                                   rows_cap=2400, assignments_cap=(hi - lo) * 4,
+                                                   exchange_groups=4, device_plan=False)
+        planned = ep_fused.FusedExpertParallelLayer(owner, 512, 320, rank=rank, world=world,
+                                                    rows_cap=2400, assignments_cap=(hi - lo) * 4,
+                                                    exchange_groups=4)
+        same = same and planned.device_plan and not hosted.device_plan
+        for layer_ in (hosted, planned):
+            for _ in range(3):
+                y = layer_.forward(x[lo:hi].cuda(), ids[lo:hi].cuda(),
+                                   w[layer_.local_experts].cuda())
+            layer_.poll()
+            same = same and torch.equal(y.view(torch.int16), want.view(torch.int16))
+        same = same and hosted.last_local_m == planned.last_local_m
+        dist.barrier()
+        hosted.close()
+        planned.close()
         copied = ep_fused.FusedExpertParallelLayer(owner, 512, 320, rank=rank, world=world,
                                                    rows_cap=2400, assignments_cap=(hi - lo) * 4,
                                                    exchange_groups=3, scheduler="dynamic_queue",
