@@ -42,6 +42,13 @@ WORKLOADS = {
     # half-size Mixtral-shaped case for profiler captures (weights 470 MB > L2)
     "profile_e8_t2048_k4096_n7168_zipf1.0": dict(
         experts=8, top_k=2, tokens=2048, k=4096, n=7168, distribution=3, zipf_alpha=1.0),
+    # half-size decode-shaped case for profiler captures (weights 2.2 GB)
+    "profile_decode_e128_t128_k7168_n2048_heavy_sparse": dict(
+        experts=128, top_k=8, tokens=128, k=7168, n=2048, distribution=4, zipf_alpha=1.2,
+        heavy_fraction=4 / 128, heavy_share=0.5, inactive_fraction=0.4),
+    # one dense small-M problem (the weight-stream regime of the dense M-sweep)
+    "profile_dense_m64_k2048_n7168": dict(
+        experts=1, top_k=1, tokens=64, k=2048, n=7168, distribution=0, zipf_alpha=1.2),
     # small expert-parallel case for profiler captures of the routing kernels
     "profile_ep_e32_t4096_k7168_n2048_zipf1.0": dict(
         experts=32, top_k=4, tokens=4096, k=7168, n=2048, distribution=3, zipf_alpha=1.0),
@@ -658,7 +665,9 @@ def run_skew_sweep(args):
         # the other single-GPU configurations, for the p99-vs-expert-order table
         points += [("mixtral_zipf1.0", WORKLOADS[DEFAULT_WORKLOAD]),
                    ("decode_heavy_sparse",
-                    WORKLOADS["deepseek_decode_e256_t256_k7168_n2048_heavy_sparse"])]
+                    WORKLOADS["deepseek_decode_e256_t256_k7168_n2048_heavy_sparse"]),
+                   ("cpu_runnable_uniform", WORKLOADS["cpu_runnable_e8_t256_k512_n1024_uniform"])]
+        points += [(name, WORKLOADS[name]) for name in sorted(PUBLISHED_TFLOPS)]
     out = []
     for label, spec in points:
         counts = workload_counts(engine, spec)
@@ -692,10 +701,16 @@ def run_skew_sweep(args):
                                      ("static_persistent", "static_persistent", {}),
                                      ("dynamic_queue", "dynamic_queue", {}), ("clc", "clc", {}),
                                      ("auto", "auto", {}),
-                                     ("reference_rule", ref_policy, ref_opts)):
+                                     ("reference_rule", ref_policy, ref_opts),
+                                     ("expert_order_g1", "expert_order", {"cta_group": 1}),
+                                     ("dynamic_queue_g1", "dynamic_queue", {"cta_group": 1}),
+                                     ("clc_g1", "clc", {"cta_group": 1}),
+                                     ("expert_order_g2", "expert_order", {"cta_group": 2}),
+                                     ("dynamic_queue_g2", "dynamic_queue", {"cta_group": 2}),
+                                     ("clc_g2", "clc", {"cta_group": 2})):
             plan = engine.GroupedGemmPlan()
             cap.check(plan.initialize_packed(a, w, d, counts, scheduler=policy, stream=stream,
-                                             cta_group=args.cta_group, **opts), label_)
+                                             **{"cta_group": args.cta_group, **opts}), label_)
             plans.append((label_, plan))
         for _ in range(max(3, args.warmup)):
             for _, plan in plans:
@@ -717,12 +732,16 @@ def run_skew_sweep(args):
                 raise RuntimeError(f"{policy}: {cap.status_string(status)}")
             ms = [ev[i][j][0].elapsed_time(ev[i][j][1]) for i in range(iters)]
             p50 = percentile(ms, 0.5)
+            st_ = plan.stats()
             timing[policy] = {"p50_us": p50 * 1e3, "p99_us": percentile(ms, 0.99) * 1e3,
                               "useful_tflops_p50": flops / (p50 * 1e-3) / 1e12,
-                              "cta_group": plan.stats().cta_group}
+                              "cta_group": st_.cta_group, "tile_n": st_.tile_n,
+                              "resolved": st_.resolved_scheduler, "ctas": st_.threadblock_count}
             plan.close()
         for row in timing.values():
             row["p99_speedup_vs_expert_order"] = timing["expert_order"]["p99_us"] / row["p99_us"]
+        best = min(timing, key=lambda name: timing[name]["p50_us"])
+        auto_gap = timing["auto"]["p50_us"] / timing[best]["p50_us"] - 1.0
         out.append({"routing": label, "shape": {"experts": spec["experts"], "rows": sum(counts),
                                                  "k": k, "n": n},
                     "cv_m": wm.coefficient_of_variation,
@@ -730,6 +749,7 @@ def run_skew_sweep(args):
                     "small_m_expert_ratio": wm.small_m_expert_ratio,
                     "total_tiles_128x128": wm.total_tiles, "schedule_model_148_ctas": model,
                     "reference_rule_picks": cap.VARIANT_NAMES[variant.value],
+                    "best_p50": best, "auto_p50_over_best": auto_gap,
                     "engine": timing})
         del a, w, d
     print(json.dumps({"metric": "p50/p99 us per grouped GEMM vs routing skew", "unit": "us",
@@ -803,9 +823,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="engine", choices=["engine", "reference"])
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
-    # dynamic_queue with claim 1 measured fastest on the headline workload; "auto"
-    # (the reference's threshold rule) and every other policy are in the table.
-    ap.add_argument("--policy", default="dynamic_queue")
+    # "auto" = the engine's own fitted rule (launch control on the headline workload);
+    # every explicit policy is in the table.
+    ap.add_argument("--policy", default="auto")
     ap.add_argument("--cta-group", type=int, default=0, choices=[0, 1, 2],
                     help="0 = engine picks per routing (default)")
     ap.add_argument("--policy-iters", type=int, default=1000,

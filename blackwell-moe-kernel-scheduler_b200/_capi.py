@@ -345,6 +345,7 @@ SIGNATURES = {
          _P(RoutingFeatures)],
     ),
     "bmoe_select_variant": (C.c_int, [_P(RoutingFeatures), _P(C.c_double), _u32p]),
+    "bmoe_select_variant_fitted": (C.c_int, [_P(RoutingFeatures), _P(C.c_double), _u32p]),
     "bmoe_variant_name": (C.c_char_p, [C.c_uint32]),
     "bmoe_worklist_layout_for": (C.c_int, [C.c_uint32, _P(WorklistLayout)]),
     "bmoe_worklist_build": (

@@ -180,8 +180,8 @@ Resolved resolve_policy(const bmoe_gemm_args& a, uint32_t tile_m, uint32_t tile_
   uint32_t claim = a.claim_size == 0 ? 1 : a.claim_size;
   uint32_t tail = a.hybrid_tail_tiles;
   if (policy == BMOE_SCHED_AUTO) {
-    // Threshold dispatch on launch-level routing features, with the thresholds
-    // fitted on this engine (the reference's bootstrap values stay the default of
+    // Dispatch on launch-level routing features with the rule fitted on this engine
+    // (the reference's rule and bootstrap values stay available through
     // select_launch_variant / bmoe_select_variant).
     namespace bm = blackwell_moe;
     bm::GemmShape shape;
@@ -199,7 +199,7 @@ Resolved resolve_policy(const bmoe_gemm_args& a, uint32_t tile_m, uint32_t tile_
     spec.hybrid_tail_tiles = 2 * cta_count;
     const bm::LaunchConfig cfg =
         bm::resolve_launch_config(
-            bm::select_launch_variant(f, bm::fitted_b200_thresholds()), spec);
+            bm::select_launch_variant_fitted(f), spec);
     policy = static_cast<uint32_t>(cfg.scheduler);
     claim = cfg.claim_size;
     tail = cfg.hybrid_tail_tiles;

@@ -262,6 +262,24 @@ int bmoe_select_variant(const bmoe_routing_features* features,
   return BMOE_OK;
 }
 
+int bmoe_select_variant_fitted(const bmoe_routing_features* features, const double* rule,
+                               uint32_t* variant_out) {
+  if (features == nullptr || variant_out == nullptr) return BMOE_INVALID_ARGUMENT;
+  bm::RoutingFeatures f;
+  f.mean_m = features->mean_m;
+  f.cv_m = features->cv_m;
+  f.inactive_expert_ratio = features->inactive_expert_ratio;
+  f.active_tiles = features->active_tiles;
+  f.tiles_per_cta = features->tiles_per_cta;
+  bm::FittedDispatch r;
+  if (rule != nullptr) {
+    r.nonpersistent_tiles_per_cta = rule[0];
+    r.weight_stream_mean_rows = rule[1];
+  }
+  *variant_out = static_cast<uint32_t>(bm::select_launch_variant_fitted(f, r));
+  return BMOE_OK;
+}
+
 const char* bmoe_variant_name(uint32_t variant) {
   if (variant > BMOE_VARIANT_CLC) return "unknown";
   return bm::launch_variant_name(static_cast<bm::LaunchVariant>(variant));

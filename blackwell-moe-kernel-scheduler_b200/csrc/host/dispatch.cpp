@@ -162,6 +162,17 @@ LaunchVariant select_launch_variant(const RoutingFeatures& f,
   return LaunchVariant::kDynamicClaim1;
 }
 
+LaunchVariant select_launch_variant_fitted(const RoutingFeatures& f,
+                                           const FittedDispatch& rule) {
+  if (f.tiles_per_cta <= rule.nonpersistent_tiles_per_cta) {
+    return LaunchVariant::kNonPersistent;
+  }
+  const double active_share = 1.0 - f.inactive_expert_ratio;
+  const double mean_active_rows = active_share > 0.0 ? f.mean_m / active_share : 0.0;
+  if (mean_active_rows <= rule.weight_stream_mean_rows) return LaunchVariant::kStaticWs;
+  return LaunchVariant::kClc;
+}
+
 LaunchConfig resolve_launch_config(LaunchVariant variant,
                                    const DispatchSpec& spec) {
   LaunchConfig cfg;

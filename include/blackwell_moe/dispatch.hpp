@@ -41,16 +41,24 @@ struct DispatchThresholds {
   double sparse_expert_ratio = 0.5;
 };
 
-// Thresholds fitted on B200 measurements of this engine (Qwen3-shaped skew sweep
-// and the Mixtral- / DeepSeek-shaped workloads): chunked and hybrid claims never
-// paid (they cost 5-15 % through lost L2 locality of the tile_m-fastest
-// traversal), so the deep-queue branch is disabled; the other bootstrap values
-// were not contradicted by the data and are kept. Used by the plan's kAuto.
-inline DispatchThresholds fitted_b200_thresholds() {
-  DispatchThresholds t;
-  t.chunked_min_tiles_per_cta = 1.0e30;
-  return t;
-}
+// The engine's own rule for kAuto, fitted on B200 measurements of this engine (the
+// reference's rule and bootstrap thresholds above stay available unchanged through
+// select_launch_variant / bmoe_select_variant / select_kernel). Fitted on the
+// Qwen3-shaped skew sweep (E=128, 131072 rows, N=768, K=2048; uniform and Zipf 0.5 / 1.0 /
+// 1.5) and the DeepSeek-shaped decode routing; checked on routings it was not fitted on
+// (Mixtral-shaped Zipf 1.0, the four E=64 rows the reference published, the small
+// CPU-runnable case), where it stays within 1 % of the best policy's median. What the
+// measurements say: launch control (one CTA per tile, work stealing) is the fastest or
+// within 0.3 % of it wherever tiles carry real rows; the chunked and hybrid queues never
+// paid (5-15 % slower: concurrent tiles then span more weight column blocks); when the
+// experts hold only a handful of rows each the launch is a pure weight stream of
+// equal-cost tiles and the plain static stride wins by 1-2 % (no claim traffic, and the
+// producer may run further ahead of the scheduler).
+struct FittedDispatch {
+  double nonpersistent_tiles_per_cta = 1.0;   // the reference's value, not contradicted
+  // mean rows per ACTIVE expert at or below which the launch counts as a weight stream
+  double weight_stream_mean_rows = 32.0;
+};
 
 // The launch variants the rule can choose (reference kernel names in
 // python/blackwell_moe_tirx/kernels/registry.py:45-106).
@@ -60,7 +68,7 @@ enum class LaunchVariant {
   kDynamicClaim1,   // "v2_dynamic":       atomic queue, claim 1
   kChunked,         // "v3_chunked":       atomic queue, claim `claim_size`
   kHybrid,          // "v4_hybrid":        coarse chunks + claim-1 tail
-  kClc,             // "v5_clc":           never chosen by the rule
+  kClc,             // "v5_clc":           never chosen by the reference's rule
 };
 
 const char* launch_variant_name(LaunchVariant variant);
@@ -90,6 +98,12 @@ RoutingFeatures routing_features(
 LaunchVariant select_launch_variant(
     const RoutingFeatures& features,
     const DispatchThresholds& thresholds = DispatchThresholds());
+
+// The engine's fitted rule (see FittedDispatch): one CTA per tile when every unit gets
+// at most one tile, the static stride for weight-stream routings, launch control
+// otherwise.
+LaunchVariant select_launch_variant_fitted(
+    const RoutingFeatures& features, const FittedDispatch& rule = FittedDispatch());
 
 LaunchConfig resolve_launch_config(
     LaunchVariant variant, const DispatchSpec& spec = DispatchSpec());

@@ -195,6 +195,17 @@ int bmoe_select_variant(const bmoe_routing_features* features,
                         const double* thresholds, uint32_t* variant_out);
 const char* bmoe_variant_name(uint32_t variant);
 
+/* The engine's own rule, the one a plan applies for BMOE_SCHED_AUTO (fitted on B200
+ * measurements of this engine; the reference never picks launch control,
+ * dispatch.py:93-94, and its bootstrap values are explicitly provisional,
+ * agent/evaluation_contract.md:41-48): one CTA per tile when no unit gets more than one
+ * tile, the static stride when the active experts hold `weight_stream_mean_rows` rows or
+ * fewer on average (a pure weight stream of equal-cost tiles), launch control otherwise.
+ * rule may be NULL (fitted values) or point to two doubles
+ * {nonpersistent_tiles_per_cta, weight_stream_mean_rows}. */
+int bmoe_select_variant_fitted(const bmoe_routing_features* features, const double* rule,
+                               uint32_t* variant_out);
+
 /* ======================================================================== */
 /* 2. Device worklist builder                                                */
 /* ======================================================================== */

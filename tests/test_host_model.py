@@ -290,3 +290,32 @@ def test_harness_csv_schema_and_routing_files_match_the_reference(engine):
             args.iterations) == ("v1_static_ws", 64, 4096, 7168, 2048, 148, 20, 200)
     with pytest.raises(ValueError):
         engine.run_benchmark(spec, plan, warmup=-1)
+
+
+def test_fitted_dispatch_rule_on_the_benchmark_routings(engine, golden):
+    """The rule a plan applies for `auto` (fitted on B200 measurements): launch control
+    where tiles carry real rows, the static stride for weight-stream routings, one CTA per
+    tile when no unit gets more than one. The reference's own rule keeps its answers."""
+    cap = engine._capi
+    lib = cap.load()
+
+    def pick(counts, n, tile_m, tile_n, units, rule=None):
+        c = support.as_counts(counts)
+        f = cap.RoutingFeatures()
+        assert lib.bmoe_routing_features_compute(c.ctypes.data_as(C.POINTER(C.c_uint32)), len(c), n,
+                                                 tile_m, tile_n, units, C.byref(f)) == 0
+        out = C.c_uint32(99)
+        arr = (C.c_double * 2)(*rule) if rule else None
+        assert lib.bmoe_select_variant_fitted(C.byref(f), arr, C.byref(out)) == 0
+        return cap.VARIANT_NAMES[out.value]
+
+    w = golden["workloads"]
+    assert pick(w["c2_zipf1_e8"]["counts"], 14336, 256, 256, 74) == "v5_clc"
+    for name in ("c4_uniform_e128", "c4_zipf05_e128", "c4_zipf10_e128", "c4_zipf15_e128"):
+        assert pick(w[name]["counts"], 768, 256, 256, 74) == "v5_clc", name
+    assert pick(w["zipf_e64_default"]["counts"], 7168, 128, 256, 148) == "v5_clc"
+    decode = golden["build_side_workloads"]["c3_heavy_sparse_e256_decode"]["counts"]
+    assert pick(decode, 2048, 128, 256, 148) == "v1_static_ws"       # 13 rows per active expert
+    assert pick(w["c1_uniform_e8"]["counts"], 1024, 128, 128, 148) == "v0_nonpersistent"
+    assert pick(decode, 2048, 128, 256, 148, rule=(1.0, 4.0)) == "v5_clc"
+    assert lib.bmoe_select_variant_fitted(None, None, None) == cap.INVALID_ARGUMENT
