@@ -104,12 +104,15 @@ def run(args, spec, workload):
         pair = args.cta_group != 1
         plan_options = {"cta_group": 2 if pair else 1,
                         "cta_count": max(1, (sms - args.comm_sms) // (2 if pair else 1))}
+    # The overlapped exchange needs a persistent grid (it keeps SMs free for the pushes and
+    # plans the step on the device): "auto" means the claim-1 queue here.
+    fused_policy = "dynamic_queue" if args.policy == "auto" else args.policy
     if args.exchange == "fused":
         from bmoe_b200 import ep_fused
 
         layer = ep_fused.FusedExpertParallelLayer(
             owner, n, k, rank=rank, world=world, rows_cap=tokens * top_k,
-            assignments_cap=(hi - lo) * top_k, scheduler=args.policy,
+            assignments_cap=(hi - lo) * top_k, scheduler=fused_policy,
             exchange_groups=ep_groups, cta_group=args.cta_group,
             dispatch_ctas=args.dispatch_ctas, push_results=not args.no_push,
             exchange_sms=args.exchange_sms, expert_parts=parts,
@@ -136,6 +139,7 @@ def run(args, spec, workload):
             owner, n, k, rank=rank, world=world,
             ops=ep.CudaOps(scheduler=args.policy, cta_group=args.cta_group))
     exchange_sms_used = getattr(layer, "exchange_sms", 0)
+    layer_info = type("LayerInfo", (), {"device_plan": getattr(layer, "device_plan", False)})
     copy_bytes = 0
     w_local = _expert_weights(torch, layer.local_experts, n, k, dev)
     total_flops = 2.0 * tokens * top_k * n * k
@@ -301,7 +305,9 @@ def run(args, spec, workload):
         "p50_us": bench.percentile(step_samples, 0.5) * 1e3,
         "p99_us": bench.percentile(step_samples, 0.99) * 1e3,
         "config": {"workload": workload, "experts": spec["experts"], "top_k": top_k,
-                   "tokens": tokens, "k": k, "n": n, "policy": args.policy,
+                   "tokens": tokens, "k": k, "n": n,
+                   "policy": fused_policy if args.exchange == "fused" else args.policy,
+                   "device_planned": bool(getattr(layer_info, "device_plan", False)),
                    "parallelism": f"ep{world}",
                    "placement": ("tile-count LPT" if parts is None else
                                  "tile-count LPT over row shards: %d of %d experts split, %d shards"
