@@ -145,15 +145,13 @@ def run(args, spec, workload):
     total_flops = 2.0 * tokens * top_k * n * k
     stream = torch.cuda.current_stream()
 
+    sampler = bench.ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()      # runs through the warm-up; the region's samples are picked by time
     for _ in range(args.warmup):
         layer.forward(x_local, ids_local, w_local, **extra)
     ops.poll()
     barrier()
-
-    sampler = bench.ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-        time.sleep(0.2)
     launches_before = ops.launches
     barrier()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
