@@ -424,6 +424,8 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     uint32_t stage = 0, stage_round = 0;
     uint32_t last_expert = 0xffffffffu;
     uint64_t t_info = 0, t_stage = 0;
+    // bytes that land per stage: the A box (possibly fewer than 128 rows) and the B box
+    const uint32_t tx_bytes = (p.a_box_bytes + Cfg::kBBytes) * Cfg::kGroup;
     while (true) {
       const uint32_t slot = reads % kSchedSlots;
       const uint32_t round = (reads / kSchedSlots) & 1u;
@@ -473,12 +475,12 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         if (ptx::elect_one()) {
           if constexpr (PAIR) {
             // Both CTAs' bytes are counted on the leader's barrier.
-            if (leader) ptx::mbar_arrive_expect_tx(bar_full(stage), Cfg::kTxBytes);
+            if (leader) ptx::mbar_arrive_expect_tx(bar_full(stage), tx_bytes);
             const uint32_t full = ptx::map_to_cta(bar_full(stage), 0);
             ptx::tma_load_2d_pair(dst_a, map_a, full, k0, static_cast<int32_t>(a_row0));
             ptx::tma_load_2d_pair(dst_b, map_b, full, k0, static_cast<int32_t>(col0));
           } else {
-            ptx::mbar_arrive_expect_tx(bar_full(stage), Cfg::kTxBytes);
+            ptx::mbar_arrive_expect_tx(bar_full(stage), tx_bytes);
             ptx::tma_load_2d(dst_a, map_a, bar_full(stage), k0, static_cast<int32_t>(a_row0));
             ptx::tma_load_2d(dst_b, map_b, bar_full(stage), k0, static_cast<int32_t>(col0));
           }

@@ -45,7 +45,7 @@ struct DeviceStatus {
 };
 
 struct GemmParams {
-  const CUtensorMap* tmap_a;  // [experts] A_e as {k, M_e}, box {64, 128}
+  const CUtensorMap* tmap_a;  // [experts] A_e as {k, M_e}, box {64, a_box_bytes / 128}
   const CUtensorMap* tmap_b;  // [experts] B_e as {k, n},   box {64, TILE_N / cta_group}
   const CUtensorMap* tmap_d;  // [experts] D_e as {n, M_e}, box {64, 32} BF16 / {32, 32} FP32
   const bmoe_tile* tiles;     // device worklist
@@ -94,6 +94,13 @@ struct GemmParams {
   // the same stream; the host never saw the counts). tile_count is then only the
   // capacity of `tiles`, and the queue's chunked part ends at the tile total.
   const uint32_t* tile_count_dev;
+  // Bytes of one A box: rows of the box x 128. 128 rows unless no expert has that many:
+  // then the box only covers the rows that can be valid (rounded up to 8). The MMA still
+  // reads 128 rows of the stage; the rows the box does not write feed accumulator rows
+  // that are never stored. What it saves is shared-memory fill bandwidth: a CTA takes in
+  // about 64 bytes per cycle, zero-filled rows included, and that - not HBM or the tensor
+  // pipe - bounds a one-wave launch over a small-M problem.
+  uint32_t a_box_bytes;
 };
 
 // Words per CTA of GemmParams::trace (SM cycles):

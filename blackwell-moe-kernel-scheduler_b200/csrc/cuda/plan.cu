@@ -424,7 +424,17 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
   plan->b_key_n = a.n;
   plan->b_key_k = a.k;
   plan->b_key_box = b_box;
-  if (packed && !encode_matrix(&maps_a[0], a.packed_a, a.packed_rows, a.k, 128, false)) {
+  // Rows of the A box: 128, or fewer when no expert has that many rows (single-CTA tiles
+  // only; see GemmParams::a_box_bytes).
+  uint32_t a_box_rows = 128;
+  if (cta_group == 1 && !dev_counts) {
+    uint32_t most = 0;
+    for (uint32_t e = 0; e < a.experts; ++e) {
+      if (a.tokens_per_expert[e] > most) most = a.tokens_per_expert[e];
+    }
+    if (most < 128) a_box_rows = most < 8 ? 8u : (most + 7u) / 8u * 8u;
+  }
+  if (packed && !encode_matrix(&maps_a[0], a.packed_a, a.packed_rows, a.k, a_box_rows, false)) {
     return BMOE_CUDA_ERROR;
   }
   for (uint32_t e = 0; e < a.experts; ++e) {
@@ -436,7 +446,7 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
       plan->b_encoded_for[e] = nullptr;
       continue;
     }
-    if (!packed && !encode_matrix(&maps_a[e], a.a[e], rows, a.k, 128, false)) {
+    if (!packed && !encode_matrix(&maps_a[e], a.a[e], rows, a.k, a_box_rows, false)) {
       return BMOE_CUDA_ERROR;
     }
     if (plan->b_encoded_for[e] != a.b[e]) {
@@ -487,6 +497,7 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
   p.tile_visits = nullptr;
   p.cta_tiles = nullptr;
   p.wait_budget_ns = 1000000000ull;  // 1 s per wait, then the kernel gives up
+  p.a_box_bytes = a_box_rows * 128u;
   if (packed) {
     // first row of every expert in the packed buffer, as the worklist builder left it
     p.a_row_offsets = reinterpret_cast<const unsigned long long*>(
