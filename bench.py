@@ -391,6 +391,10 @@ def run_single_gpu(args, spec, workload):
     torch.cuda.set_device(0)
     dev = torch.device("cuda:0")
     stream = torch.cuda.current_stream()
+    # the clock sampler needs a moment to come up: it starts before the inputs are made and
+    # runs through the warm-up; the timed region's samples are picked by their time stamps
+    sampler = ClockSampler(0)
+    sampler.start()
     counts = workload_counts(engine, spec)
     n, k = spec["n"], spec["k"]
     total = sum(counts)
@@ -416,8 +420,7 @@ def run_single_gpu(args, spec, workload):
     # ---------------- headline: K timed steps of the chosen policy ----------
     plan = make_plan(args.policy, cta_group=args.cta_group)
     stats = plan.stats()
-    sampler = ClockSampler(0)
-    sampler.start()          # runs through the warm-up; the region's samples are picked by time
+    load_start = time.time()   # the GPU is under this load from the first warm-up launch on
     for _ in range(args.warmup):
         plan.run(stream)
     check(plan, "warm-up")
@@ -431,7 +434,9 @@ def run_single_gpu(args, spec, workload):
         plan.run(stream)
     t1.record(stream)
     torch.cuda.synchronize()
-    sampler.mark_region(wall0, time.time())
+    # clock samples: warm-up and timed region together (the region alone can be shorter than
+    # one sampling interval at small K)
+    sampler.mark_region(min(load_start, wall0), time.time())
     region_ms = t0.elapsed_time(t1)
     launches = plan.stats().launches - launches_before
     clocks = sampler.stop()

@@ -72,6 +72,11 @@ def run(args, spec, workload):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    # the clock sampler needs a moment to come up: it starts before the set-up and runs
+    # through the warm-up; the timed region's samples are picked by their time stamps
+    sampler = bench.ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     n, k, top_k, tokens = spec["n"], spec["k"], spec["top_k"], spec["tokens"]
     ids_all = _routing(torch, spec)
     global_counts = torch.bincount(ids_all.reshape(-1), minlength=spec["experts"]).tolist()
@@ -145,9 +150,6 @@ def run(args, spec, workload):
     total_flops = 2.0 * tokens * top_k * n * k
     stream = torch.cuda.current_stream()
 
-    sampler = bench.ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()      # runs through the warm-up; the region's samples are picked by time
     for _ in range(args.warmup):
         layer.forward(x_local, ids_local, w_local, **extra)
     ops.poll()
