@@ -84,10 +84,13 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
         objs = list(pool.map(lambda s: _compile_one(s, newest_header, verbose), srcs))
     if LIB_PATH.exists() and all(LIB_PATH.stat().st_mtime >= o.stat().st_mtime for o in objs):
         return LIB_PATH
-    cmd = [_nvcc(), *ARCH_FLAGS, "-shared", "-o", str(LIB_PATH), *map(str, objs)]
+    # link beside the target, then rename: a reader never sees a half-written library
+    staged = LIB_PATH.with_suffix(".so.tmp")
+    cmd = [_nvcc(), *ARCH_FLAGS, "-shared", "-o", str(staged), *map(str, objs)]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
         raise RuntimeError(f"link failed:\n{proc.stdout}\n{proc.stderr}")
+    os.replace(staged, LIB_PATH)
     return LIB_PATH
 
 

@@ -505,7 +505,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       uint32_t reads = 0;
       uint32_t stage = 0, stage_round = 0;
       uint32_t buf = 0, buf_round = 0;
-      uint64_t t_info = 0, t_accum = 0, t_operands = 0;
+      uint64_t t_info = 0, t_accum = 0, t_operands = 0, t_issue = 0;
       while (true) {
         const uint32_t slot = reads % kSchedSlots;
         const uint32_t round = (reads / kSchedSlots) & 1u;
@@ -540,6 +540,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
               ptx::make_kmajor_sw128_desc(base + Cfg::kOffA + stage * kABytes);
           const uint64_t b_desc =
               ptx::make_kmajor_sw128_desc(base + Cfg::kOffB + stage * Cfg::kBBytes);
+          const long long issue_t0 = tracing ? clock64() : 0;
           if (ptx::elect_one()) {
 #pragma unroll
             for (uint32_t ks = 0; ks < kBlockK / 16; ++ks) {
@@ -568,6 +569,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
               }
             }
           }
+          if (tracing) t_issue += static_cast<uint64_t>(clock64() - issue_t0);
           if (++stage == Cfg::kStages) { stage = 0; stage_round ^= 1u; }
         }
         if (!ok) break;
@@ -577,6 +579,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         p.trace[blockIdx.x * kTraceWords + 2] = t_info;
         p.trace[blockIdx.x * kTraceWords + 3] = t_accum;
         p.trace[blockIdx.x * kTraceWords + 4] = t_operands;
+        p.trace[blockIdx.x * kTraceWords + 10] = t_issue;
       }
     }
     __syncwarp();

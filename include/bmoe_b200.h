@@ -688,7 +688,16 @@ int bmoe_ep_wait_flags(const uint32_t* flags_dev, uint32_t first_slot, uint32_t 
  * local flag array reached `epoch` (bounded by the plan's wait budget; running out
  * reports BMOE_DEVICE_TIMEOUT through bmoe_plan_poll). flags_dev == NULL removes
  * the gate, and so does every bmoe_plan_initialize.
- * group_of_expert_dev: [experts of the plan] uint8, values < 32. */
+ * group_of_expert_dev: [experts of the plan] uint8, values < 32.
+ * Forward progress: the flags must be raised by OTHER GPUs (or by copies, see below),
+ * never by a kernel of this GPU that is launched separately: a persistent gated launch
+ * may occupy every SM it is given, and nothing guarantees that another launch of the same
+ * GPU runs beside it. Work of this GPU that the launch depends on (the rows that stay on
+ * the rank) precedes it in stream order instead. A rank that pushes rows to its peers
+ * from a kernel of its own while its gated GEMM runs should leave that kernel SMs the
+ * GEMM's grid does not cover (cta_count below the SM count), otherwise every rank can end
+ * up with a resident GEMM waiting for pushes that no peer has room to run; the wait is
+ * bounded either way and reports BMOE_DEVICE_TIMEOUT. */
 int bmoe_plan_set_gate(bmoe_plan* plan, const uint32_t* flags_dev, uint32_t epoch,
                        uint32_t ranks, uint32_t self, const uint8_t* group_of_expert_dev);
 
