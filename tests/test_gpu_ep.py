@@ -310,6 +310,74 @@ def test_single_rank_fused_layer_and_gate(engine):
         plan.close()
 
 
+def test_route_planning_leaves_no_stale_entry_when_a_row_does_not_fit(engine):
+    """A packed buffer that is too short for the routed rows (an inconsistent table): the
+    assignments that do not fit reserve their bucket slot all the same, and that slot must
+    then hold an entry no rank owns, not whatever an earlier step left there - the copy
+    kernels skip such entries, so nothing is written outside the buffer."""
+    import ctypes as C
+
+    import torch
+
+    from bmoe_b200 import ep_fused
+
+    cap = engine._capi
+    lib = cap.load()
+    experts, top_k, tokens, groups = 6, 2, 40, 2
+    gen = torch.Generator().manual_seed(3)
+    ids = torch.multinomial(torch.ones(experts).expand(tokens, -1), top_k, generator=gen)
+    flat = ids.reshape(-1).contiguous().cuda()
+    counts = torch.bincount(flat.cpu(), minlength=experts).numpy().reshape(1, -1)
+    step = ep_fused.plan_step(counts, [0] * experts, 0, groups)
+    assignments = tokens * top_k
+    rows_cap = assignments - 25                       # 25 rows do not fit
+    row_base = torch.from_numpy(step["row_base"]).cuda()
+    owner = torch.zeros(experts, dtype=torch.int32, device="cuda")
+    group_of = torch.from_numpy(step["group_of"]).cuda()
+    cursor = torch.zeros(experts, dtype=torch.int32, device="cuda")
+    origin = torch.full((assignments,), -1, dtype=torch.int64, device="cuda")
+    origin_bases = torch.tensor([origin.data_ptr()], dtype=torch.int64, device="cuda")
+    stale = np.zeros(assignments, dtype=[("token", "<u4"), ("to", "<u4"), ("row", "<u4"), ("pad", "<u4")])
+    stale["row"] = 7                                   # a valid-looking entry from "last step"
+    entries = torch.from_numpy(stale.view(np.uint8).copy()).cuda()
+    buckets = torch.from_numpy(step["bucket_offset"].astype(np.int32)).cuda()
+    fill = torch.zeros(groups + 2, dtype=torch.int32, device="cuda")
+    args = cap.EpRouteArgs(
+        expert_ids_dev=flat.data_ptr(), row_base_dev=row_base.data_ptr(), owner_dev=owner.data_ptr(),
+        group_of_dev=group_of.data_ptr(), cursor_dev=cursor.data_ptr(),
+        origin_bases_dev=origin_bases.data_ptr(), entries_dev=entries.data_ptr(),
+        bucket_offset_dev=buckets.data_ptr(), bucket_fill_dev=fill.data_ptr(),
+        dst_rank_out_dev=None, dst_row_out_dev=None, assignments=assignments, rows_cap=rows_cap,
+        top_k=top_k, experts=experts, ranks=1, self=0, groups=groups, stream=None,
+        staging_row_base_dev=None, staging_rows_cap=0)
+    assert lib.bmoe_ep_route(C.byref(args)) == 0
+    torch.cuda.synchronize()
+    got = entries.cpu().numpy().view(stale.dtype)
+    fits = got["to"] == 0
+    assert int(fits.sum()) == rows_cap and np.all(got["row"][fits] < rows_cap)
+    assert sorted(got["row"][fits].tolist()) == list(range(rows_cap))
+    assert np.all(got["to"][~fits] == 0xFFFFFFFF) and int((~fits).sum()) == 25
+    # the copy kernel walks all entries and touches nothing beyond the short buffer
+    k = 64
+    x = torch.randn(tokens, k, generator=gen).to(torch.bfloat16).cuda()
+    a = torch.zeros(assignments, k, dtype=torch.bfloat16, device="cuda")
+    a_bases = torch.tensor([a.data_ptr()], dtype=torch.int64, device="cuda")
+    claims = torch.zeros(groups + 2, dtype=torch.int32, device="cuda")
+    dargs = cap.EpDispatchArgs(
+        x_dev=x.data_ptr(), entries_dev=entries.data_ptr(), bucket_offset_dev=buckets.data_ptr(),
+        a_bases_dev=a_bases.data_ptr(), flag_bases_dev=None, group_done_dev=None,
+        chunk_next_dev=claims.data_ptr(), assignments=assignments, tokens=tokens,
+        rows_cap=rows_cap, row_bytes=k * 2, ranks=1, self=0, groups=groups, mode=cap.EP_LOCAL,
+        epoch=1, max_ctas=0, block_threads=0, cluster=0, bulk_copies=0, status_dev=None,
+        stream=None)
+    assert lib.bmoe_ep_dispatch(C.byref(dargs)) == 0
+    torch.cuda.synchronize()
+    assert a[rows_cap:].eq(0).all()
+    want = x[torch.from_numpy(got["token"][fits].astype(np.int64)).cuda()]
+    assert torch.equal(a[torch.from_numpy(got["row"][fits].astype(np.int64)).cuda()].view(torch.int16),
+                       want.view(torch.int16))
+
+
 def test_device_planner_equals_host_planner(engine):
     """bmoe_ep_plan (the step tables derived on the device, so that a step needs no host
     synchronisation) against the numpy planner, table for table, over random count
