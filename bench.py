@@ -595,8 +595,6 @@ def run_single_gpu(args, spec, workload):
     if bound_is_tensor:
         roofline = {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"],
                     "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
-                    "frac_of_sustained": (achieved / peaks["bf16_tflops_sustained"]
-                                          if peaks.get("bf16_tflops_sustained") else None),
                     # sustained loop against the sustained cuBLAS figure
                     "achieved_sustained": value_sustained,
                     "peak_sustained": peaks.get("bf16_tflops_sustained"),
