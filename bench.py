@@ -861,6 +861,10 @@ def main():
                     help="fused exchange: (expert, source) blocks of at least this many KiB "
                          "travel as peer copies issued by the host (copy engines) instead of "
                          "SM stores; 0 = all rows through the SMs")
+    ap.add_argument("--send-once", type=int, default=-1, choices=[-1, 0, 1],
+                    help="fused exchange: a token routed to several experts of one other rank "
+                         "crosses NVLink once and the owner's GEMM kernel copies the row onto "
+                         "the other packed rows (-1 = the layer's default)")
     ap.add_argument("--split-hot", action="store_true",
                     help="fused exchange: cut experts above half a rank's fair share of the "
                          "tiles into row shards placed on several ranks")

@@ -144,6 +144,19 @@ class EpRouteArgs(C.Structure):
         ("self", C.c_uint32), ("groups", C.c_uint32),
         ("stream", C.c_void_p),
         ("staging_row_base_dev", C.c_void_p), ("staging_rows_cap", C.c_uint64),
+        ("primary_out_dev", C.c_void_p),
+    ]
+
+
+class EpDuplicatesArgs(C.Structure):
+    _fields_ = [
+        ("expert_ids_dev", C.c_void_p), ("owner_dev", C.c_void_p), ("group_of_dev", C.c_void_p),
+        ("primary_dev", C.c_void_p), ("row_of_dev", C.c_void_p),
+        ("record_bases_dev", C.c_void_p), ("count_bases_dev", C.c_void_p),
+        ("fill_dev", C.c_void_p), ("done_counter_dev", C.c_void_p),
+        ("assignments", C.c_uint64), ("record_cap", C.c_uint32), ("experts", C.c_uint32),
+        ("ranks", C.c_uint32), ("self", C.c_uint32), ("groups", C.c_uint32),
+        ("stream", C.c_void_p),
     ]
 
 
@@ -180,6 +193,7 @@ class EpDispatchArgs(C.Structure):
         ("max_ctas", C.c_uint32), ("block_threads", C.c_uint32), ("cluster", C.c_uint32),
         ("bulk_copies", C.c_uint32), ("status_dev", C.c_void_p),
         ("stream", C.c_void_p),
+        ("bucket_fill_dev", C.c_void_p),
     ]
 
 
@@ -394,6 +408,7 @@ SIGNATURES = {
     ),
     "bmoe_ep_plan": (C.c_int, [C.c_void_p]),
     "bmoe_ep_route": (C.c_int, [C.c_void_p]),
+    "bmoe_ep_duplicates": (C.c_int, [C.c_void_p]),
     "bmoe_ep_dispatch": (C.c_int, [C.c_void_p]),
     "bmoe_ep_return": (C.c_int, [C.c_void_p]),
     "bmoe_ep_wait_flags": (
@@ -404,6 +419,9 @@ SIGNATURES = {
     "bmoe_plan_set_gate": (
         C.c_int, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p]),
     "bmoe_plan_set_gate_copies": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "bmoe_plan_set_expand": (
+        C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                  C.c_uint64, C.c_uint32, C.c_uint32, C.c_uint32]),
     "bmoe_peer_copy_batch": (C.c_int, [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32]),
     "bmoe_plan_set_push": (
         C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint64]),

@@ -119,6 +119,7 @@ struct RouteArgs {
   uint64_t staging_rows_cap;
   int32_t* dst_rank_out;       // [assignments] or nullptr: where each assignment went
   int64_t* dst_row_out;        // [assignments] or nullptr
+  int32_t* primary_out;        // [assignments] or nullptr: send-once mode (see below)
   uint64_t assignments;
   uint64_t rows_cap;
   uint32_t top_k;
@@ -127,6 +128,34 @@ struct RouteArgs {
   uint32_t self;
   uint32_t groups;
 };
+
+// Send-once mode (primary_out != nullptr): a token routed to several experts of ONE other
+// rank crosses NVLink once. Of its assignments to that rank the one with the smallest
+// (exchange group, position in the token's top-k list) is the PRIMARY and travels as
+// before; the others still get their packed row and origin record, but no route entry:
+// primary_out[i] names the primary's assignment and ep_duplicates_kernel tells the owner
+// to copy the primary's row (already in its A) into the duplicate's row. -1 = not a
+// duplicate.
+__device__ __forceinline__ int32_t primary_of(const RouteArgs& a, uint64_t i, int32_t to,
+                                              uint32_t group) {
+  const uint64_t token = i / a.top_k;
+  const uint32_t mine = static_cast<uint32_t>(i - token * a.top_k);
+  uint32_t best_group = group, best_j = mine;
+  for (uint32_t j = 0; j < a.top_k; ++j) {
+    if (j == mine) continue;
+    const int64_t e = a.expert_ids[token * a.top_k + j];
+    if (e < 0 || e >= static_cast<int64_t>(a.experts) || a.owner[e] != to) continue;
+    const uint32_t g = a.group_of[e];
+    if (g >= a.groups) continue;
+    if (g < best_group || (g == best_group && j < best_j)) {
+      best_group = g;
+      best_j = j;
+    }
+  }
+  return best_j == mine ? -1 : static_cast<int32_t>(token * a.top_k + best_j);
+}
+
+constexpr uint32_t kDuplicateBucket = 0xfffffffeu;   // takes a row, but no route entry
 
 // Route planning, one thread per assignment: destination row from the expert's cursor
 // (the order of rows inside an expert changes no result row, only where it sits), the
@@ -159,7 +188,13 @@ __global__ void __launch_bounds__(256) ep_route_kernel(RouteArgs a) {
         }
       }
     }
+    int32_t primary = -1;
+    if (a.primary_out != nullptr && bucket < a.groups) {
+      primary = primary_of(a, i, to, bucket);
+      if (primary >= 0) bucket = kDuplicateBucket;
+    }
     const bool live = bucket != 0xffffffffu;
+    const bool has_entry = live && bucket != kDuplicateBucket;
     // one cursor atomic per distinct expert in the warp
     const uint32_t key_e = live ? static_cast<uint32_t>(e) : 0xffffffffu;
     const uint32_t same_e = __match_any_sync(0xffffffffu, key_e);
@@ -171,12 +206,33 @@ __global__ void __launch_bounds__(256) ep_route_kernel(RouteArgs a) {
     const uint32_t same_b = __match_any_sync(0xffffffffu, bucket);
     uint32_t first_slot = 0;
     const uint32_t lead_b = __ffs(same_b) - 1;
-    if (live && lane == lead_b) first_slot = atomicAdd(&a.bucket_fill[bucket], __popc(same_b));
+    if (has_entry && lane == lead_b) {
+      first_slot = atomicAdd(&a.bucket_fill[bucket], __popc(same_b));
+    }
     first_slot = __shfl_sync(0xffffffffu, first_slot, lead_b);
-    if (!live) continue;
+    if (!live) {
+      if (a.primary_out != nullptr && i < a.assignments) a.primary_out[i] = -1;
+      continue;
+    }
     const int64_t row = a.row_base[e] + first_pos + __popc(same_e & lanes_below);
+    if (!has_entry) {
+      // a duplicate: its row and origin record, no entry; the owner fills the row itself
+      const bool fits = row >= 0 && static_cast<uint64_t>(row) < a.rows_cap;
+      if (fits) {
+        a.origin_bases[to][row] =
+            static_cast<long long>((static_cast<uint64_t>(a.self) << kOriginRankShift) | i);
+      }
+      a.primary_out[i] = fits ? primary : -1;
+      if (a.dst_rank_out != nullptr) a.dst_rank_out[i] = to;
+      if (a.dst_row_out != nullptr) a.dst_row_out[i] = fits ? row : -1;
+      continue;
+    }
+    if (a.primary_out != nullptr) a.primary_out[i] = -1;
     const uint32_t slot = a.bucket_offset[bucket] + first_slot + __popc(same_b & lanes_below);
-    if (slot >= a.bucket_offset[bucket + 1] || slot >= a.assignments) continue;
+    if (slot >= a.bucket_offset[bucket + 1] || slot >= a.assignments) {
+      if (a.dst_row_out != nullptr) a.dst_row_out[i] = -1;   // nothing was sent for it
+      continue;
+    }
     // A bad table must never become a stray access to another GPU's memory: the slot
     // this assignment reserved gets an entry no rank owns (the copy kernels skip it)
     // instead of keeping whatever an earlier step left there.
@@ -187,6 +243,7 @@ __global__ void __launch_bounds__(256) ep_route_kernel(RouteArgs a) {
       none.row = 0xffffffffu;
       none.pad = 0;
       a.entries[slot] = none;
+      if (a.dst_row_out != nullptr) a.dst_row_out[i] = -1;
       continue;
     }
     a.origin_bases[to][row] =
@@ -212,6 +269,69 @@ __global__ void __launch_bounds__(256) ep_route_kernel(RouteArgs a) {
   }
 }
 
+// Send-once mode, second pass: one record {row of the primary, row of the duplicate} per
+// duplicate assignment, appended to the list of (exchange group of the duplicate, this
+// source) in the OWNER's memory; when the whole grid is done the last CTA publishes the list
+// lengths there. The owner's GEMM kernel copies primary -> duplicate once this source's
+// flag for the group is up (the primary belongs to the same or an earlier group of the same
+// source, so it has landed by then). Runs after ep_route_kernel and before the launch that
+// pushes the rows and raises the flags, in one stream.
+struct DuplicateArgs {
+  const int64_t* expert_ids;     // [assignments]
+  const int32_t* owner;          // [experts]
+  const uint8_t* group_of;       // [experts]
+  const int32_t* primary;        // [assignments] from ep_route_kernel
+  const int64_t* row_of;         // [assignments] packed row of every assignment (-1: none)
+  uint2* const* record_bases;    // [ranks] record lists: [groups][ranks][record_cap]
+  uint32_t* const* count_bases;  // [ranks] list lengths: [groups][ranks]
+  uint32_t* fill;                // [ranks][groups] zero at step start
+  uint32_t* done_counter;        // zero at step start
+  uint64_t assignments;
+  uint32_t record_cap;
+  uint32_t experts;
+  uint32_t ranks;
+  uint32_t self;
+  uint32_t groups;
+};
+
+__global__ void __launch_bounds__(256) ep_duplicates_kernel(DuplicateArgs a) {
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+  for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < a.assignments;
+       i += stride) {
+    const int32_t first = a.primary[i];
+    if (first < 0 || static_cast<uint64_t>(first) >= a.assignments) continue;
+    const int64_t e = a.expert_ids[i];
+    if (e < 0 || e >= static_cast<int64_t>(a.experts)) continue;
+    const int32_t to = a.owner[e];
+    const uint32_t g = a.group_of[e];
+    const int64_t from_row = a.row_of[first], to_row = a.row_of[i];
+    if (to < 0 || static_cast<uint32_t>(to) >= a.ranks || static_cast<uint32_t>(to) == a.self ||
+        g >= a.groups || from_row < 0 || to_row < 0) {
+      continue;
+    }
+    const uint32_t at = atomicAdd(&a.fill[static_cast<uint32_t>(to) * a.groups + g], 1u);
+    if (at >= a.record_cap) continue;   // cannot happen with record_cap >= assignments
+    a.record_bases[to][(static_cast<size_t>(g) * a.ranks + a.self) * a.record_cap + at] =
+        make_uint2(static_cast<uint32_t>(from_row), static_cast<uint32_t>(to_row));
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t arrived = atomicAdd(a.done_counter, 1u);
+    if (arrived == gridDim.x - 1) {
+      __threadfence_system();
+      for (uint32_t r = 0; r < a.ranks; ++r) {
+        if (r == a.self) continue;
+        for (uint32_t g = 0; g < a.groups; ++g) {
+          const uint32_t n = a.fill[r * a.groups + g];
+          a.count_bases[r][g * a.ranks + a.self] = n < a.record_cap ? n : a.record_cap;
+        }
+      }
+      __threadfence_system();
+    }
+  }
+}
+
 struct DispatchArgs {
   const uint4* x;              // [tokens, k] BF16 token rows of this rank
   const RouteEntry* entries;   // bucketed route entries (ep_route_kernel)
@@ -231,6 +351,8 @@ struct DispatchArgs {
   uint32_t span;               // entries per claim: 1..32
   uint32_t row_bytes;
   uint32_t* status;            // optional: set when a bulk-copy wait ran out
+  const uint32_t* bucket_fill; // optional [groups + 2]: entries really written per bucket
+                               // (send-once mode leaves gaps at the end of a bucket)
 };
 
 // Bucket by bucket (exchange groups in order, then - or only - the local bucket), a
@@ -250,7 +372,8 @@ __global__ void __launch_bounds__(1024) ep_dispatch_kernel(DispatchArgs a) {
                                                        : a.groups + 1u;
   for (uint32_t b = first_bucket; b < end_bucket; ++b) {
     const uint32_t begin = a.bucket_offset[b];
-    const uint32_t count = a.bucket_offset[b + 1] - begin;
+    uint32_t count = a.bucket_offset[b + 1] - begin;
+    if (a.bucket_fill != nullptr && a.bucket_fill[b] < count) count = a.bucket_fill[b];
     while (true) {
       uint32_t at = 0;
       if (lane == 0) at = atomicAdd(&a.chunk_next[b], span);
@@ -315,7 +438,8 @@ __global__ void __launch_bounds__(kBulkMaxWarps * 32) ep_dispatch_bulk_kernel(Di
   const uint8_t* const x = reinterpret_cast<const uint8_t*>(a.x);
   for (uint32_t b = first_bucket; b < end_bucket; ++b) {
     const uint32_t begin = a.bucket_offset[b];
-    const uint32_t count = a.bucket_offset[b + 1] - begin;
+    uint32_t count = a.bucket_offset[b + 1] - begin;
+    if (a.bucket_fill != nullptr && a.bucket_fill[b] < count) count = a.bucket_fill[b];
     while (alive) {
       uint32_t at = 0;
       if (lane == 0) at = atomicAdd(&a.chunk_next[b], span);
@@ -718,10 +842,49 @@ extern "C" int bmoe_ep_route(const bmoe_ep_route_args* args) {
   a.groups = c.groups;
   a.staging_row_base = c.staging_row_base_dev;
   a.staging_rows_cap = c.staging_rows_cap;
+  a.primary_out = c.primary_out_dev;
+  if (c.primary_out_dev != nullptr &&
+      (c.dst_row_out_dev == nullptr || c.staging_row_base_dev != nullptr)) {
+    return BMOE_INVALID_ARGUMENT;   // send-once needs the row of every assignment
+  }
   const uint64_t want = (c.assignments + 255) / 256;
   const uint64_t cap = 4ull * bmoe::device_sms();
   const uint32_t grid = static_cast<uint32_t>(want < cap ? want : cap);
   bmoe::ep_route_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(c.stream)>>>(a);
+  return cudaPeekAtLastError() == cudaSuccess ? BMOE_OK : BMOE_CUDA_ERROR;
+}
+
+extern "C" int bmoe_ep_duplicates(const bmoe_ep_duplicates_args* args) {
+  if (args == nullptr) return BMOE_INVALID_ARGUMENT;
+  const bmoe_ep_duplicates_args& c = *args;
+  if (c.ranks == 0 || c.self >= c.ranks || c.groups == 0 || c.groups > BMOE_EP_MAX_GROUPS ||
+      c.record_cap == 0 || c.owner_dev == nullptr || c.group_of_dev == nullptr ||
+      c.primary_dev == nullptr || c.row_of_dev == nullptr || c.record_bases_dev == nullptr ||
+      c.count_bases_dev == nullptr || c.fill_dev == nullptr || c.done_counter_dev == nullptr ||
+      (c.assignments != 0 && c.expert_ids_dev == nullptr)) {
+    return BMOE_INVALID_ARGUMENT;
+  }
+  bmoe::DuplicateArgs a;
+  a.expert_ids = c.expert_ids_dev;
+  a.owner = c.owner_dev;
+  a.group_of = c.group_of_dev;
+  a.primary = c.primary_dev;
+  a.row_of = c.row_of_dev;
+  a.record_bases = reinterpret_cast<uint2* const*>(c.record_bases_dev);
+  a.count_bases = reinterpret_cast<uint32_t* const*>(c.count_bases_dev);
+  a.fill = c.fill_dev;
+  a.done_counter = c.done_counter_dev;
+  a.assignments = c.assignments;
+  a.record_cap = c.record_cap;
+  a.experts = c.experts;
+  a.ranks = c.ranks;
+  a.self = c.self;
+  a.groups = c.groups;
+  const uint64_t want = (c.assignments + 255) / 256;
+  const uint64_t cap = 2ull * bmoe::device_sms();
+  uint32_t grid = static_cast<uint32_t>(want < cap ? want : cap);
+  if (grid == 0) grid = 1;   // the list lengths are published even when there is nothing
+  bmoe::ep_duplicates_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(c.stream)>>>(a);
   return cudaPeekAtLastError() == cudaSuccess ? BMOE_OK : BMOE_CUDA_ERROR;
 }
 
@@ -797,6 +960,7 @@ extern "C" int bmoe_ep_dispatch(const bmoe_ep_dispatch_args* args) {
   config.gridDim = dim3(grid, 1, 1);
   a.row_bytes = c.row_bytes;
   a.status = c.status_dev;
+  a.bucket_fill = c.bucket_fill_dev;
   if (c.bulk_copies != 0) {
     // one row-sized stage per warp, as many warps as fit (the bytes in flight per SM
     // bound its push rate: a row stays in its stage until NVLink has taken it)
@@ -890,6 +1054,7 @@ cudaError_t preload_exchange_kernels() {
   cudaError_t rc = preload_one(ep_count_kernel);
   if (rc == cudaSuccess) rc = preload_one(ep_plan_kernel);
   if (rc == cudaSuccess) rc = preload_one(ep_route_kernel);
+  if (rc == cudaSuccess) rc = preload_one(ep_duplicates_kernel);
   if (rc == cudaSuccess) rc = preload_one(ep_dispatch_kernel);
   if (rc == cudaSuccess) rc = preload_one(ep_dispatch_bulk_kernel);
   if (rc == cudaSuccess) rc = preload_one(ep_return_kernel);

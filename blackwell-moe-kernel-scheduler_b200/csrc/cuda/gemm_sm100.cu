@@ -291,6 +291,29 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             }
           }
         }
+        if (p.expand_records != nullptr && g < p.expand_groups) {
+          // rows of this group that the sources did not send: copied here, by warp 3 of
+          // the CTAs of this launch, from the rows that did arrive
+          uint32_t want = 0;
+          for (uint32_t r = 0; r < p.gate_ranks; ++r) {
+            if (r != p.gate_self) want += p.expand_count[g * p.gate_ranks + r];
+          }
+          for (uint32_t spin = 1;; ++spin) {
+            if (ptx::ld_acquire_gpu_u32(p.expand_done + g) >= want) break;
+            if ((spin & 0xf) == 0) {
+              if (*abort_word != 0) return false;
+              const uint64_t now = ptx::global_timer_ns();
+              if (start == 0) {
+                start = now;
+              } else if (now - start > budget) {
+                *abort_word = 1;
+                report(p, kSiteSchedExpand, 0, expert, g, want);
+                return false;
+              }
+            }
+            __nanosleep(100);
+          }
+        }
         // The rows were written by other GPUs' ordinary stores; the TMA loads that
         // follow (async proxy) must observe them.
         ptx::fence_proxy_async_all();
@@ -580,6 +603,82 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         p.trace[blockIdx.x * kTraceWords + 3] = t_accum;
         p.trace[blockIdx.x * kTraceWords + 4] = t_operands;
         p.trace[blockIdx.x * kTraceWords + 10] = t_issue;
+      }
+    }
+    __syncwarp();
+  }
+
+  // ------------------------------------------------------- row expansion --
+  // Send-once exchange: group by group and source by source, wait for the source's flag,
+  // then copy primary rows onto the rows of the duplicates, a few records per claim, in
+  // competition with warp 3 of every other CTA of the launch.
+  else if (warp == 3) {
+    if (p.expand_records != nullptr && p.gate_flags != nullptr) {
+      constexpr uint32_t kClaim = 2;
+      bool alive = true;
+      for (uint32_t g = 0; alive && g < p.expand_groups; ++g) {
+        for (uint32_t r = 0; alive && r < p.gate_ranks; ++r) {
+          if (r == p.gate_self) continue;
+          const uint32_t list = g * p.gate_ranks + r;
+          uint32_t ok = 1;
+          if (lane == 0) {
+            const uint32_t* flag = p.gate_flags + list;
+            uint64_t start = 0;
+            for (uint32_t spin = 1;; ++spin) {
+              if (static_cast<int32_t>(ptx::ld_acquire_sys_u32(flag) - p.gate_epoch) >= 0) break;
+              if ((spin & 0xf) == 0) {
+                if (*abort_word != 0) { ok = 0; break; }
+                const uint64_t now = ptx::global_timer_ns();
+                if (start == 0) {
+                  start = now;
+                } else if (now - start > budget) {
+                  *abort_word = 1;
+                  report(p, kSiteExpandFlag, 4, 0, g, r);
+                  ok = 0;
+                  break;
+                }
+              }
+              __nanosleep(500);
+            }
+          }
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (ok == 0) { alive = false; break; }
+          uint32_t count = lane == 0 ? p.expand_count[list] : 0u;
+          count = __shfl_sync(0xffffffffu, count, 0);
+          if (count > p.expand_cap) count = p.expand_cap;
+          const uint2* const records = p.expand_records + static_cast<size_t>(list) * p.expand_cap;
+          while (true) {
+            uint32_t at = 0;
+            if (lane == 0) at = atomicAdd(&p.expand_next[list], kClaim);
+            at = __shfl_sync(0xffffffffu, at, 0);
+            if (at >= count) break;
+            const uint32_t end = min(at + kClaim, count);
+            for (uint32_t i = at; i < end; ++i) {
+              const uint2 rec = records[i];
+              if (rec.x < p.expand_rows_cap && rec.y < p.expand_rows_cap) {
+                const uint4* src = p.expand_a + static_cast<size_t>(rec.x) * p.expand_vec_per_row;
+                uint4* dst = p.expand_a + static_cast<size_t>(rec.y) * p.expand_vec_per_row;
+                for (uint32_t v0 = 0; v0 < p.expand_vec_per_row; v0 += 32 * 8) {
+                  uint4 regs[8];
+#pragma unroll
+                  for (uint32_t u = 0; u < 8; ++u) {
+                    const uint32_t v = v0 + u * 32 + lane;
+                    if (v < p.expand_vec_per_row) regs[u] = src[v];
+                  }
+#pragma unroll
+                  for (uint32_t u = 0; u < 8; ++u) {
+                    const uint32_t v = v0 + u * 32 + lane;
+                    if (v < p.expand_vec_per_row) dst[v] = regs[u];
+                  }
+                }
+              }
+            }
+            // the copies are visible device-wide before they are counted
+            __threadfence();
+            __syncwarp();
+            if (lane == 0) atomicAdd(&p.expand_done[g], end - at);
+          }
+        }
       }
     }
     __syncwarp();

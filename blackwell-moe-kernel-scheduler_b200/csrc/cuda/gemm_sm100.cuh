@@ -30,6 +30,8 @@ enum DeviceSite : uint32_t {
   kSiteEpiInfo = 9,
   kSiteEpiAccum = 10,     // epilogue waiting for a finished accumulator
   kSiteSchedGate = 11,    // scheduler waiting for another rank's rows (stage = group, aux = rank)
+  kSiteExpandFlag = 12,   // row expansion waiting for a source's flag (stage = group, aux = rank)
+  kSiteSchedExpand = 13,  // scheduler waiting for a group's row expansion (stage = group)
 };
 
 // Device-side error record; zero-initialised by the host.
@@ -94,6 +96,19 @@ struct GemmParams {
   // the same stream; the host never saw the counts). tile_count is then only the
   // capacity of `tiles`, and the queue's chunked part ends at the tile total.
   const uint32_t* tile_count_dev;
+  // Optional row expansion (send-once exchange): record lists {from row, to row} per
+  // (exchange group, source rank), written by the sources. Warp 3 of every CTA copies
+  // A[from] -> A[to] for a list once that source's flag for the group is up; the gate
+  // waits until expand_done[group] has reached the sum of the group's list lengths.
+  const uint2* expand_records;    // [groups][gate_ranks][expand_cap]; nullptr = off
+  const uint32_t* expand_count;   // [groups][gate_ranks] list lengths (valid once flagged)
+  uint32_t* expand_next;          // [groups][gate_ranks] claim counters, zero at step start
+  uint32_t* expand_done;          // [groups] records carried out, zero at step start
+  uint4* expand_a;                // packed A
+  uint64_t expand_rows_cap;
+  uint32_t expand_vec_per_row;    // k / 8
+  uint32_t expand_cap;
+  uint32_t expand_groups;
   // Bytes of one A box: rows of the box x 128. 128 rows unless no expert has that many:
   // then the box only covers the rows that can be valid (rounded up to 8). The MMA still
   // reads 128 rows of the stage; the rows the box does not write feed accumulator rows

@@ -550,6 +550,7 @@ int bmoe_plan_set_gate(bmoe_plan* plan, const uint32_t* flags_dev, uint32_t epoc
   bmoe::GemmParams& p = plan->params;
   p.gate_copy_mask = nullptr;
   p.gate_copy_plane = 0;
+  p.expand_records = nullptr;
   if (flags_dev == nullptr || ranks <= 1) {
     p.gate_flags = nullptr;
     p.gate_group_of = nullptr;
@@ -570,6 +571,34 @@ int bmoe_plan_set_gate_copies(bmoe_plan* plan, const uint32_t* copy_mask_dev) {
   if (copy_mask_dev != nullptr && p.gate_flags == nullptr) return BMOE_INVALID_ARGUMENT;
   p.gate_copy_mask = copy_mask_dev;
   p.gate_copy_plane = copy_mask_dev != nullptr ? BMOE_EP_COPY_FLAGS(p.gate_ranks) : 0u;
+  return BMOE_OK;
+}
+
+int bmoe_plan_set_expand(bmoe_plan* plan, const void* records_dev, const uint32_t* counts_dev,
+                         uint32_t* next_dev, uint32_t* done_dev, void* a_dev,
+                         uint64_t rows_cap, uint32_t row_bytes, uint32_t record_cap,
+                         uint32_t groups) {
+  if (plan == nullptr || !plan->ready) return BMOE_INVALID_ARGUMENT;
+  bmoe::GemmParams& p = plan->params;
+  if (records_dev == nullptr) {
+    p.expand_records = nullptr;
+    return BMOE_OK;
+  }
+  if (p.gate_flags == nullptr || counts_dev == nullptr || next_dev == nullptr ||
+      done_dev == nullptr || a_dev == nullptr || rows_cap == 0 || row_bytes == 0 ||
+      row_bytes % 16 != 0 || record_cap == 0 || groups == 0 || groups > BMOE_EP_MAX_GROUPS ||
+      misaligned16(a_dev)) {
+    return BMOE_INVALID_ARGUMENT;
+  }
+  p.expand_records = static_cast<const uint2*>(records_dev);
+  p.expand_count = counts_dev;
+  p.expand_next = next_dev;
+  p.expand_done = done_dev;
+  p.expand_a = static_cast<uint4*>(a_dev);
+  p.expand_rows_cap = rows_cap;
+  p.expand_vec_per_row = row_bytes / 16;
+  p.expand_cap = record_cap;
+  p.expand_groups = groups;
   return BMOE_OK;
 }
 

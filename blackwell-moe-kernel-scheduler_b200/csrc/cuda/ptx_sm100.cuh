@@ -93,6 +93,13 @@ __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* addr) {
   return v;
 }
 
+// Counter advanced by other CTAs of this GPU.
+__device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* addr) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }

@@ -199,6 +199,14 @@ class GroupedGemmPlan:
         raised the flags of their peer copies (``bmoe_plan_set_gate_copies``)."""
         return int(self._lib.bmoe_plan_set_gate_copies(self._handle, copy_mask_ptr or None))
 
+    def set_expand(self, records_ptr, counts_ptr, next_ptr, done_ptr, a_ptr, rows_cap: int,
+                   row_bytes: int, record_cap: int, groups: int) -> int:
+        """Let the launch copy duplicate rows inside the packed A buffer itself (send-once
+        exchange, ``bmoe_plan_set_expand``); ``records_ptr`` None switches it off."""
+        return int(self._lib.bmoe_plan_set_expand(self._handle, records_ptr or None, counts_ptr,
+                                                  next_ptr, done_ptr, a_ptr, rows_cap, row_bytes,
+                                                  record_cap, groups))
+
     def set_push(self, origin_ptr, expert_row_ptr, y_bases_ptr, ranks: int, y_rows_cap: int) -> int:
         """Send result rows straight to their origin ranks' buffers instead of D (see
         ``bmoe_plan_set_push``); ``origin_ptr`` None switches back."""

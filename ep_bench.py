@@ -121,7 +121,8 @@ def run(args, spec, workload):
             exchange_groups=ep_groups, cta_group=args.cta_group,
             dispatch_ctas=args.dispatch_ctas, push_results=not args.no_push,
             exchange_sms=args.exchange_sms, expert_parts=parts,
-            bulk_copies=args.bulk_copies, copy_engine_min_bytes=args.copy_engine_kb * 1024)
+            bulk_copies=args.bulk_copies, copy_engine_min_bytes=args.copy_engine_kb * 1024,
+            **({} if args.send_once < 0 else {"send_once": bool(args.send_once)}))
         ops = layer
         plain = layer
         groups = layer.groups
@@ -144,7 +145,8 @@ def run(args, spec, workload):
             owner, n, k, rank=rank, world=world,
             ops=ep.CudaOps(scheduler=args.policy, cta_group=args.cta_group))
     exchange_sms_used = getattr(layer, "exchange_sms", 0)
-    layer_info = type("LayerInfo", (), {"device_plan": getattr(layer, "device_plan", False)})
+    layer_info = type("LayerInfo", (), {"device_plan": getattr(layer, "device_plan", False),
+                                        "send_once": getattr(layer, "send_once", False)})
     copy_bytes = 0
     w_local = _expert_weights(torch, layer.local_experts, n, k, dev)
     total_flops = 2.0 * tokens * top_k * n * k
@@ -308,6 +310,7 @@ def run(args, spec, workload):
                    "tokens": tokens, "k": k, "n": n,
                    "policy": fused_policy if args.exchange == "fused" else args.policy,
                    "device_planned": bool(getattr(layer_info, "device_plan", False)),
+                   "send_once": bool(getattr(layer_info, "send_once", False)),
                    "parallelism": f"ep{world}",
                    "placement": ("tile-count LPT" if parts is None else
                                  "tile-count LPT over row shards: %d of %d experts split, %d shards"

@@ -610,6 +610,14 @@ typedef struct bmoe_ep_route_args {
    * bmoe_peer_copy_batch sends it). The origin record is written as for any row. */
   const int64_t* staging_row_base_dev;  /* [experts] or NULL */
   uint64_t staging_rows_cap;
+  /* Send-once mode (appended; NULL = every assignment sends its row). A token routed to
+   * several experts of ONE other rank then crosses NVLink once: of its assignments to
+   * that rank the one with the smallest (exchange group, position in the top-k list) is
+   * the primary and is routed as before; the others get their row and origin record but
+   * no route entry, and primary_out_dev[i] names the primary's assignment (-1: not a
+   * duplicate). bmoe_ep_duplicates then tells the owner which rows to copy. Needs
+   * dst_row_out_dev; excludes staging_row_base_dev. */
+  int32_t* primary_out_dev;             /* [assignments] or NULL */
 } bmoe_ep_route_args;
 
 /* Route planning of one step: the destination row of every assignment (the row inside
@@ -619,6 +627,33 @@ typedef struct bmoe_ep_route_args {
  * routed row in the bucket of its exchange group. Precedes bmoe_ep_dispatch in stream
  * order. */
 int bmoe_ep_route(const bmoe_ep_route_args* args);
+
+typedef struct bmoe_ep_duplicates_args {
+  const int64_t* expert_ids_dev;   /* [assignments], as given to bmoe_ep_route */
+  const int32_t* owner_dev;        /* [experts] */
+  const uint8_t* group_of_dev;     /* [experts] */
+  const int32_t* primary_dev;      /* [assignments] written by bmoe_ep_route */
+  const int64_t* row_of_dev;       /* [assignments] bmoe_ep_route's dst_row_out_dev */
+  void* const* record_bases_dev;   /* [ranks] record lists of every rank:
+                                      uint32 pairs [groups][ranks][record_cap] */
+  void* const* count_bases_dev;    /* [ranks] list lengths of every rank: uint32 [groups][ranks] */
+  uint32_t* fill_dev;              /* [ranks * groups] zero at step start */
+  uint32_t* done_counter_dev;      /* zero at step start */
+  uint64_t assignments;
+  uint32_t record_cap;             /* records one (group, source) list holds */
+  uint32_t experts;
+  uint32_t ranks;
+  uint32_t self;
+  uint32_t groups;
+  void* stream;
+} bmoe_ep_duplicates_args;
+
+/* Send-once mode, after bmoe_ep_route and before the bmoe_ep_dispatch launch that raises
+ * the flags, same stream: appends one record {packed row of the primary, packed row of the
+ * duplicate} per duplicate assignment to list (group of the duplicate, this rank) in the
+ * OWNER's memory and publishes the list lengths there. The owner's grouped GEMM copies
+ * the rows itself (bmoe_plan_set_expand). No counterpart in the reference. */
+int bmoe_ep_duplicates(const bmoe_ep_duplicates_args* args);
 
 typedef struct bmoe_ep_dispatch_args {
   const void* x_dev;               /* [tokens, row_bytes] token rows of this rank */
@@ -647,6 +682,9 @@ typedef struct bmoe_ep_dispatch_args {
                                       at most 16): for CTAs on SMs of their own */
   uint32_t* status_dev;            /* optional: 0x40000000 | bucket if a bulk-copy wait ran out */
   void* stream;
+  const uint32_t* bucket_fill_dev; /* appended, optional [groups + 2]: entries bmoe_ep_route
+                                      really wrote per bucket (its bucket_fill_dev); needed in
+                                      send-once mode, where buckets are not filled to the end */
 } bmoe_ep_dispatch_args;
 
 /* Copies the routed token rows into the owners' packed A, bucket by bucket: REMOTE
@@ -708,6 +746,23 @@ int bmoe_plan_set_gate(bmoe_plan* plan, const uint32_t* flags_dev, uint32_t epoc
  * this rank], NULL switches the extension off. Call after bmoe_plan_set_gate. No
  * counterpart in the reference (it has no multi-GPU path). */
 int bmoe_plan_set_gate_copies(bmoe_plan* plan, const uint32_t* copy_mask_dev);
+
+/* Send-once mode on the owner's side: the grouped GEMM itself copies duplicate rows.
+ * One spare warp of every CTA walks, group by group, the record lists that the sources
+ * wrote (bmoe_ep_duplicates) as soon as a source's flag for the group is up, copies
+ * A[from] -> A[to] (both rows of this rank's packed A) and counts the copies in
+ * done_dev[group]; the gate publishes a tile of a group only when all of the group's
+ * records have been carried out. One launch, so no kernel of this GPU waits for another.
+ *   records_dev  uint32 pairs [groups][ranks][record_cap]   (written by the peers)
+ *   counts_dev   uint32 [groups][ranks]                     (written by the peers)
+ *   next_dev     uint32 [groups][ranks]  claim counters, zero at step start
+ *   done_dev     uint32 [groups]         zero at step start
+ * Call after bmoe_plan_set_gate (same flags, epoch, ranks); records_dev == NULL switches
+ * it off. a_dev / rows_cap / row_bytes describe the packed A buffer. */
+int bmoe_plan_set_expand(bmoe_plan* plan, const void* records_dev, const uint32_t* counts_dev,
+                         uint32_t* next_dev, uint32_t* done_dev, void* a_dev,
+                         uint64_t rows_cap, uint32_t row_bytes, uint32_t record_cap,
+                         uint32_t groups);
 
 /* One device-to-device copy of a batch (bmoe_peer_copy_batch). */
 typedef struct bmoe_copy_item {

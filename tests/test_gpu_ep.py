@@ -378,6 +378,86 @@ def test_route_planning_leaves_no_stale_entry_when_a_row_does_not_fit(engine):
                        want.view(torch.int16))
 
 
+def test_gemm_copies_duplicate_rows_before_their_group_starts(engine):
+    """Send-once exchange, owner's side, on one GPU with the flags already up: the record
+    lists name rows that did not travel (here: left as NaN) and the rows to copy them from;
+    warp 3 of the launch's CTAs fills them and the gate holds every group back until its
+    list has been carried out. Output and the packed buffer must equal the run on the fully
+    populated buffer."""
+    import torch
+
+    counts = [300, 40, 0, 260, 129]
+    n, k, ranks, groups, cap = 256, 192, 2, 2, 64
+    gen = torch.Generator().manual_seed(12)
+    a_full = torch.randn(sum(counts), k, generator=gen).to(torch.bfloat16)
+    wt = (torch.randn(len(counts), n, k, generator=gen) * k ** -0.5).to(torch.bfloat16).cuda()
+    group_of = torch.tensor([0, 0, 0, 1, 1], dtype=torch.uint8, device="cuda")
+    first_row = np.cumsum([0] + counts[:-1])
+    # duplicates: rows of group-1 experts copied from group-0 rows, and inside a group; a
+    # source row is always one that travelled (never itself a duplicate)
+    pairs = {0: [(5, 310), (7, 9), (299, 320)], 1: [(5, 345), (7, 600), (400, 401), (8, 728)]}
+    for g in (0, 1):
+        for src, dst in pairs[g]:
+            a_full[dst] = a_full[src]
+    gapped = a_full.clone()
+    for g in (0, 1):
+        for _, dst in pairs[g]:
+            gapped[dst] = float("nan")
+    d_want = torch.zeros(sum(counts), n, dtype=torch.bfloat16, device="cuda")
+    engine.grouped_gemm(a_full.cuda(), wt, d_want, counts, scheduler="dynamic_queue")
+    records = np.zeros((groups, ranks, cap, 2), dtype=np.uint32)
+    lengths = np.zeros((groups, ranks), dtype=np.uint32)
+    for g in (0, 1):
+        records[g, 1, :len(pairs[g])] = pairs[g]
+        lengths[g, 1] = len(pairs[g])
+    records_dev = torch.from_numpy(records.view(np.int32)).cuda()
+    lengths_dev = torch.from_numpy(lengths.view(np.int32)).cuda()
+    flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+    flags[0 * ranks + 1] = 9
+    flags[1 * ranks + 1] = 9
+    for cta_group, policy in ((1, "dynamic_queue"), (2, "expert_order"), (2, "dynamic_queue")):
+        a_dev = gapped.clone().cuda()
+        d = torch.zeros_like(d_want)
+        claims = torch.zeros(groups * ranks, dtype=torch.int32, device="cuda")
+        done = torch.zeros(groups, dtype=torch.int32, device="cuda")
+        plan = engine.GroupedGemmPlan()
+        try:
+            assert plan.initialize_packed(a_dev, wt, d, counts, scheduler=policy,
+                                          cta_group=cta_group) == 0
+            assert plan.set_gate(flags.data_ptr(), 9, ranks, 0, group_of.data_ptr()) == 0
+            assert plan.set_expand(records_dev.data_ptr(), lengths_dev.data_ptr(),
+                                   claims.data_ptr(), done.data_ptr(), a_dev.data_ptr(),
+                                   a_dev.shape[0], k * 2, cap, groups) == 0
+            assert plan.run() == 0
+            status, report = plan.poll()
+            assert status == 0, (report.code, report.stage, report.aux)
+        finally:
+            plan.close()
+        assert done.cpu().tolist() == [len(pairs[0]), len(pairs[1])]
+        assert torch.equal(a_dev.cpu().view(torch.int16), a_full.view(torch.int16))
+        assert torch.equal(d.view(torch.int16), d_want.view(torch.int16)), (cta_group, policy)
+    # a list that claims more records than were ever written for it: bounded wait, status
+    lengths_dev[1, 1] = 50
+    records_dev[1, 1, 4:50] = 0x7fffffff            # rows out of range: skipped, still counted
+    a_dev = gapped.clone().cuda()
+    d = torch.zeros_like(d_want)
+    claims = torch.zeros(groups * ranks, dtype=torch.int32, device="cuda")
+    done = torch.zeros(groups, dtype=torch.int32, device="cuda")
+    plan = engine.GroupedGemmPlan()
+    try:
+        assert plan.initialize_packed(a_dev, wt, d, counts, scheduler="dynamic_queue") == 0
+        assert plan.set_gate(flags.data_ptr(), 9, ranks, 0, group_of.data_ptr()) == 0
+        assert plan.set_expand(records_dev.data_ptr(), lengths_dev.data_ptr(), claims.data_ptr(),
+                               done.data_ptr(), a_dev.data_ptr(), a_dev.shape[0], k * 2, cap,
+                               groups) == 0
+        assert plan.run() == 0 and plan.poll()[0] == 0
+        assert done.cpu().tolist() == [len(pairs[0]), 50]
+        assert torch.equal(d.view(torch.int16), d_want.view(torch.int16))
+        assert plan.set_expand(None, None, None, None, None, 0, 0, 0, 0) == 0
+    finally:
+        plan.close()
+
+
 def test_device_planner_equals_host_planner(engine):
     """bmoe_ep_plan (the step tables derived on the device, so that a step needs no host
     synchronisation) against the numpy planner, table for table, over random count
@@ -530,6 +610,27 @@ def _ep_worker(rank, world, port, tmpdir):
         dist.barrier()
         hosted.close()
         planned.close()
+        once = ep_fused.FusedExpertParallelLayer(owner, 512, 320, rank=rank, world=world,
+                                                 rows_cap=2400, assignments_cap=(hi - lo) * 4,
+                                                 exchange_groups=4, send_once=True)
+        once_hosted = ep_fused.FusedExpertParallelLayer(owner, 512, 320, rank=rank, world=world,
+                                                        rows_cap=2400,
+                                                        assignments_cap=(hi - lo) * 4,
+                                                        exchange_groups=3, send_once=True,
+                                                        device_plan=False, cta_group=1)
+        for layer_ in (once, once_hosted):
+            same = same and layer_.send_once
+            for i in range(4):
+                y = layer_.forward(x[lo:hi].cuda(), ids[lo:hi].cuda(),
+                                   w[layer_.local_experts].cuda(),
+                                   topk_weights=gates.cuda() if i == 3 else None)
+                if i == 2:
+                    same = same and torch.equal(y.view(torch.int16), want.view(torch.int16))
+            layer_.poll()
+            same = same and torch.equal(y.cpu().view(torch.int16), want_z.view(torch.int16))
+        dist.barrier()
+        once.close()
+        once_hosted.close()
         copied = ep_fused.FusedExpertParallelLayer(owner, 512, 320, rank=rank, world=world,
                                                    rows_cap=2400, assignments_cap=(hi - lo) * 4,
                                                    exchange_groups=3, scheduler="dynamic_queue",
