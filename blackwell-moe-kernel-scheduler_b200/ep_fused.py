@@ -307,7 +307,12 @@ class FusedExpertParallelLayer:
         # every rank loads its kernels before the first step: the step's bounded waits
         # assume that all ranks launch within the wait budget
         _capi.check(self._lib.bmoe_preload_kernels(), "bmoe_preload_kernels")
-        self.send_once = bool(send_once) and world > 1 and not self.copy_min_rows
+        # (a persistent grid only: the warps that copy the rows stay until the last group's
+        # flags are up, which one-CTA-per-tile launches cannot afford)
+        self.send_once = bool(send_once) and world > 1 and not self.copy_min_rows and \
+            str(scheduler) in ("expert_order", "baseline", "static_persistent", "static",
+                               "sorted_static", "compacted", "dynamic_queue", "dynamic",
+                               "0", "1", "2", "3")
         self._record_cap = max(1, self.assignments_cap)
         sizes = {"a": self.rows_cap * k * 2, "d": self.rows_cap * n * 2, "origin": self.rows_cap * 8,
                  "y": self.assignments_cap * n * 2, "flags": flag_slots * 4}
