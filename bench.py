@@ -74,16 +74,14 @@ for _name, _dist, _alpha in (("uniform", 0, 1.2), ("heavy_hitter", 1, 1.2), ("sp
 DEFAULT_WORKLOAD = "mixtral_e8_t4096_k4096_n14336_zipf1.0"
 EP_WORKLOAD = "ep_deepseek_e256_t32768_k7168_n2048_zipf1.0"
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the GEMM kernel from
-# the ncu captures summarised under profiles/. The full-size launches are scaled from
-# half-size captures of the same kernel and routing family, where traffic grows in
-# proportion to the operand bytes: Mixtral-shaped, CTA-pair kernel: 561.5 MB measured for
-# 562.0 MB of algorithmic bytes; decode-shaped, single-CTA kernel: 2283.9 MB for 2279.6 MB.
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the GEMM kernel, measured with
+# ncu on the benchmarked configurations themselves (one launch each, DRAM counters and
+# duration only) and on the small cases summarised under profiles/.
 NCU_TRAFFIC_BYTES = {
+    DEFAULT_WORKLOAD: 1242.6e6,                      # algorithmic 1241.5 MB
+    "deepseek_decode_e256_t256_k7168_n2048_heavy_sparse": 4534.9e6,   # algorithmic 4529.8 MB
     "profile_e8_t2048_k4096_n7168_zipf1.0": 561.5e6,
-    DEFAULT_WORKLOAD: 1241.5e6 * (561.5 / 562.0),
     "profile_decode_e128_t128_k7168_n2048_heavy_sparse": 2283.9e6,
-    "deepseek_decode_e256_t256_k7168_n2048_heavy_sparse": 4529.8e6 * (2283.9 / 2279.6),
     "profile_dense_m64_k2048_n7168": 29.7e6,
 }
 
