@@ -852,9 +852,9 @@ def main():
                     help="SMs the pipelined GEMM leaves to the exchange kernels")
     ap.add_argument("--dispatch-ctas", type=int, default=0,
                     help="fused exchange: CTAs of the remote-row kernel (0 = one per SM)")
-    ap.add_argument("--exchange-sms", type=int, default=16,
+    ap.add_argument("--exchange-sms", type=int, default=-1,
                     help="fused exchange: SMs the GEMM leaves to the remote-row kernel "
-                         "(0 = share SMs, see --dispatch-ctas)")
+                         "(0 = share SMs, see --dispatch-ctas; -1 = 16)")
     ap.add_argument("--copy-engine-kb", type=int, default=0,
                     help="fused exchange: (expert, source) blocks of at least this many KiB "
                          "travel as peer copies issued by the host (copy engines) instead of "
@@ -862,7 +862,7 @@ def main():
     ap.add_argument("--send-once", type=int, default=-1, choices=[-1, 0, 1],
                     help="fused exchange: a token routed to several experts of one other rank "
                          "crosses NVLink once and the owner's GEMM kernel copies the row onto "
-                         "the other packed rows (-1 = the layer's default)")
+                         "the other packed rows (-1 = off)")
     ap.add_argument("--split-hot", action="store_true",
                     help="fused exchange: cut experts above half a rank's fair share of the "
                          "tiles into row shards placed on several ranks")

@@ -112,6 +112,13 @@ def run(args, spec, workload):
     # The overlapped exchange needs a persistent grid (it keeps SMs free for the pushes and
     # plans the step on the device): "auto" means the claim-1 queue here.
     fused_policy = "dynamic_queue" if args.policy == "auto" else args.policy
+    # Defaults of the overlapped exchange: 16 SMs set aside for the pushes, every
+    # assignment sends its own row. The send-once exchange (--send-once 1) cuts the NVLink
+    # bytes 1.4-4x; at two and four GPUs, where the gated GEMM and not the pushes bounds the
+    # step, it changed the step by less than the run-to-run spread (3 %), with SMs set aside
+    # or shared.
+    send_once = max(0, args.send_once)
+    exchange_sms = args.exchange_sms if args.exchange_sms >= 0 else 16
     if args.exchange == "fused":
         from bmoe_b200 import ep_fused
 
@@ -120,9 +127,9 @@ def run(args, spec, workload):
             assignments_cap=(hi - lo) * top_k, scheduler=fused_policy,
             exchange_groups=ep_groups, cta_group=args.cta_group,
             dispatch_ctas=args.dispatch_ctas, push_results=not args.no_push,
-            exchange_sms=args.exchange_sms, expert_parts=parts,
+            exchange_sms=exchange_sms, expert_parts=parts,
             bulk_copies=args.bulk_copies, copy_engine_min_bytes=args.copy_engine_kb * 1024,
-            **({} if args.send_once < 0 else {"send_once": bool(args.send_once)}))
+            send_once=bool(send_once))
         ops = layer
         plain = layer
         groups = layer.groups
