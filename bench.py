@@ -398,9 +398,20 @@ def run_single_gpu(args, spec, workload):
     total = sum(counts)
     flops = 2.0 * total * n * k
     a, w = synth_inputs(torch, counts, n, k, dev)
+    fp8 = args.dtype == "fp8"
+    if fp8:
+        # E4M3 bit patterns of the same draws (weights x 8: out of the subnormal range);
+        # operands are one byte per element, D stays BF16
+        a = a.to(torch.float8_e4m3fn).view(torch.uint8)
+        w8 = torch.empty(w.shape, dtype=torch.uint8, device=dev)
+        for e in range(len(counts)):
+            w8[e] = (w[e].float() * 8.0).to(torch.float8_e4m3fn).view(torch.uint8)
+        w = w8
+        del w8
+    operand_bytes = 1 if fp8 else 2
     d = torch.zeros(total, n, dtype=torch.bfloat16, device=dev)
     active = sum(c > 0 for c in counts)
-    algorithmic_bytes = 2.0 * (total * k + active * n * k + total * n)
+    algorithmic_bytes = operand_bytes * (total * k + active * n * k) + 2.0 * total * n
 
     def make_plan(policy, **opts):
         plan = engine.GroupedGemmPlan()
@@ -520,7 +531,7 @@ def run_single_gpu(args, spec, workload):
     # ---------------- end to end through the public API, host buffers --------
     e2e, e2e_plan = None, None
     if not args.no_e2e:
-        a_host = torch.empty(a.shape, dtype=torch.bfloat16).pin_memory()
+        a_host = torch.empty(a.shape, dtype=a.dtype).pin_memory()
         a_host.copy_(a)
         d_host = torch.empty(d.shape, dtype=torch.bfloat16).pin_memory()
         # Two result buffers and two plans: while step i's D travels to the host on
@@ -568,7 +579,7 @@ def run_single_gpu(args, spec, workload):
             check(p_, "e2e")
         e2e_ms = e0.elapsed_time(e1) / e2e_steps
         e2e = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-               "h2d_bytes_per_step": a_host.numel() * 2 + 4 * len(counts)
+               "h2d_bytes_per_step": a_host.numel() * operand_bytes + 4 * len(counts)
                + 3 * 128 * len(counts) + 512,
                "d2h_bytes_per_step": d_host.numel() * 2, "ms_per_step": e2e_ms,
                "note": "weights stay resident on the device (plan state); every step uploads "
@@ -580,8 +591,22 @@ def run_single_gpu(args, spec, workload):
     cpu = None
     if not args.no_cpu_baseline:
         lib = load_oracle()
-        cpu = cpu_sample(lib, bits(torch, a), bits(torch, w), counts, n, k,
-                         target_s=args.cpu_seconds)
+        if fp8:
+            # the oracle's FP8 definition: operands decoded exactly to BF16, then the same loop
+            def decoded(t):
+                import ctypes as C
+
+                import numpy as np
+
+                codes = np.ascontiguousarray(t.cpu().numpy())
+                out = np.zeros(codes.shape, dtype=np.uint16)
+                lib.orc_e4m3_to_bf16(codes.ctypes.data_as(C.c_void_p), C.c_uint64(codes.size),
+                                     out.ctypes.data_as(C.c_void_p))
+                return out
+            cpu = cpu_sample(lib, decoded(a), decoded(w), counts, n, k, target_s=args.cpu_seconds)
+        else:
+            cpu = cpu_sample(lib, bits(torch, a), bits(torch, w), counts, n, k,
+                             target_s=args.cpu_seconds)
 
     peaks = measured_peaks()
     achieved = flops / (avg_launch_ms * 1e-3) / 1e12
@@ -589,29 +614,39 @@ def run_single_gpu(args, spec, workload):
     # cap has settled the clocks
     sustained_ms = percentile(samples, 0.5)
     value_sustained = flops / (sustained_ms * 1e-3) / 1e12
-    bound_is_tensor = flops / algorithmic_bytes > peaks["bf16_tflops"] * 1e12 / (peaks["hbm_gbs"] * 1e9)
+    # FP8: no measured FP8 GEMM figure exists for this pool; the tensor pipe's FP8 rate is
+    # nominally twice its BF16 rate, so the denominators are twice the measured BF16 ones
+    tensor_scale = 2.0 if fp8 else 1.0
+    tensor_peak = peaks["bf16_tflops"] * tensor_scale
+    tensor_sustained = (peaks["bf16_tflops_sustained"] * tensor_scale
+                        if peaks.get("bf16_tflops_sustained") else None)
+    bound_is_tensor = flops / algorithmic_bytes > tensor_peak * 1e12 / (peaks["hbm_gbs"] * 1e9)
     if bound_is_tensor:
-        roofline = {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"],
-                    "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
+        roofline = {"bound": "tensor", "achieved": achieved, "peak": tensor_peak,
+                    "unit": "TFLOP/s", "frac": achieved / tensor_peak,
                     # sustained loop against the sustained cuBLAS figure
                     "achieved_sustained": value_sustained,
-                    "peak_sustained": peaks.get("bf16_tflops_sustained"),
-                    "frac_sustained": (value_sustained / peaks["bf16_tflops_sustained"]
-                                       if peaks.get("bf16_tflops_sustained") else None)}
+                    "peak_sustained": tensor_sustained,
+                    "frac_sustained": (value_sustained / tensor_sustained
+                                       if tensor_sustained else None)}
     else:
         gbs = algorithmic_bytes / (avg_launch_ms * 1e-3) / 1e9
         gbs_sustained = algorithmic_bytes / (sustained_ms * 1e-3) / 1e9
         roofline = {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                     "frac": gbs / peaks["hbm_gbs"], "achieved_sustained": gbs_sustained,
                     "frac_sustained": gbs_sustained / peaks["hbm_gbs"]}
-    roofline.update({"traffic": NCU_TRAFFIC_BYTES.get(workload), "peak_source": peaks["source"],
+    roofline.update({"traffic": None if fp8 else NCU_TRAFFIC_BYTES.get(workload),
+                     "peak_source": peaks["source"] + (
+                         "; tensor peak = 2 x the measured BF16 figure (no FP8 measurement)"
+                         if fp8 else ""),
                      "kernel": "grouped_gemm_kernel<%d, %s>" % (stats.tile_n, "pair" if stats.cta_group == 2 else "single"),
                      "algorithmic_flops_per_launch": flops,
                      "algorithmic_bytes_per_launch": algorithmic_bytes,
                      "avg_launch_ms": avg_launch_ms})
 
     line = {
-        "metric": "useful BF16 TFLOP/s per grouped GEMM", "value": value, "unit": "TFLOP/s",
+        "metric": "useful %s TFLOP/s per grouped GEMM" % ("FP8" if fp8 else "BF16"),
+        "value": value, "unit": "TFLOP/s",
         "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
         "higher_is_better": True, "scaling": "weak",
         # `value` is the K-step region right after the warm-up (a burst of a few ms at the
@@ -622,15 +657,16 @@ def run_single_gpu(args, spec, workload):
         # value / the reference's published TFLOP/s, only where that exact row exists
         # (there the comparable figure is the median: useful_tflops_p50).
         "vs_baseline": (flops / (percentile(samples, 0.5) * 1e-3) / 1e12 / PUBLISHED_TFLOPS[workload]
-                        if workload in PUBLISHED_TFLOPS else None),
-        "dtype": "bf16", "data": "synthetic",
+                        if workload in PUBLISHED_TFLOPS and not fp8 else None),
+        "dtype": "fp8_e4m3" if fp8 else "bf16", "data": "synthetic",
         "config": {"workload": workload, "experts": spec["experts"], "top_k": spec["top_k"],
                    "tokens": spec["tokens"], "k": k, "n": n, "policy": args.policy,
-                   "resolved_policy": stats.resolved_scheduler, "tile": [stats.tile_m, stats.tile_n, 64],
+                   "resolved_policy": stats.resolved_scheduler,
+                   "tile": [stats.tile_m, stats.tile_n, 128 if fp8 else 64],
                    "cta_group": stats.cta_group, "stages": stats.stages,
                    "ctas": stats.threadblock_count, "tiles": stats.total_tiles,
                    "l2": "weights (%.0f MB) exceed the 126 MB L2; no flush between steps"
-                         % (active * n * k * 2 / 1e6)},
+                         % (active * n * k * operand_bytes / 1e6)},
         "latency_samples": len(samples),
         "p50_us_with_replan": percentile(replan_ms, 0.5) * 1e3,
         "p99_us_with_replan": percentile(replan_ms, 0.99) * 1e3,
@@ -831,6 +867,9 @@ def main():
     # "auto" = the engine's own fitted rule (launch control on the headline workload);
     # every explicit policy is in the table.
     ap.add_argument("--policy", default="auto")
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8"],
+                    help="operand type of the single-GPU run: bf16 (the reference's contract) "
+                         "or fp8 (E4M3 operands, an engine extension; D stays BF16)")
     ap.add_argument("--cta-group", type=int, default=0, choices=[0, 1, 2],
                     help="0 = engine picks per routing (default)")
     ap.add_argument("--policy-iters", type=int, default=1000,

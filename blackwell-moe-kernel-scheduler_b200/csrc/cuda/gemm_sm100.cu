@@ -1,4 +1,4 @@
-// Persistent, warp-specialised BF16 grouped GEMM for sm_100a.
+// Persistent, warp-specialised BF16 (and FP8 E4M3) grouped GEMM for sm_100a.
 //
 // One CTA (256 threads) per SM walks a device worklist of 20-byte tile records
 // and computes, per record, a 128 x TILE_N block (one CTA) or a 256 x TILE_N
@@ -449,6 +449,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     uint64_t t_info = 0, t_stage = 0;
     // bytes that land per stage: the A box (possibly fewer than 128 rows) and the B box
     const uint32_t tx_bytes = (p.a_box_bytes + Cfg::kBBytes) * Cfg::kGroup;
+    const uint32_t k_block_elems = p.fp8 != 0 ? 2 * kBlockK : kBlockK;   // 128 bytes of a row
     while (true) {
       const uint32_t slot = reads % kSchedSlots;
       const uint32_t round = (reads / kSchedSlots) & 1u;
@@ -494,7 +495,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         }
         const uint32_t dst_a = base + Cfg::kOffA + stage * kABytes;
         const uint32_t dst_b = base + Cfg::kOffB + stage * Cfg::kBBytes;
-        const int32_t k0 = static_cast<int32_t>(kb * kBlockK);
+        const int32_t k0 = static_cast<int32_t>(kb * k_block_elems);   // element coordinate
         if (ptx::elect_one()) {
           if constexpr (PAIR) {
             // Both CTAs' bytes are counted on the leader's barrier.
@@ -525,6 +526,8 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   else if (warp == 1) {
     if (leader) {
       constexpr uint32_t idesc = ptx::make_bf16_idesc(kCtaRows * Cfg::kGroup, TILE_N);
+      constexpr uint32_t idesc_fp8 = ptx::make_e4m3_idesc(kCtaRows * Cfg::kGroup, TILE_N);
+      const bool fp8 = p.fp8 != 0;
       uint32_t reads = 0;
       uint32_t stage = 0, stage_round = 0;
       uint32_t buf = 0, buf_round = 0;
@@ -565,14 +568,28 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
               ptx::make_kmajor_sw128_desc(base + Cfg::kOffB + stage * Cfg::kBBytes);
           const long long issue_t0 = tracing ? clock64() : 0;
           if (ptx::elect_one()) {
+            if (!fp8) {
 #pragma unroll
-            for (uint32_t ks = 0; ks < kBlockK / 16; ++ks) {
-              // 16 BF16 = 32 bytes along k inside the 128-byte swizzle row.
-              const uint32_t acc = (kb | ks) != 0 ? 1u : 0u;
-              if constexpr (PAIR) {
-                ptx::umma_bf16_ss_pair(d_tmem, a_desc + 2 * ks, b_desc + 2 * ks, idesc, acc);
-              } else {
-                ptx::umma_bf16_ss(d_tmem, a_desc + 2 * ks, b_desc + 2 * ks, idesc, acc);
+              for (uint32_t ks = 0; ks < kBlockK / 16; ++ks) {
+                // 16 BF16 = 32 bytes along k inside the 128-byte swizzle row.
+                const uint32_t acc = (kb | ks) != 0 ? 1u : 0u;
+                if constexpr (PAIR) {
+                  ptx::umma_bf16_ss_pair(d_tmem, a_desc + 2 * ks, b_desc + 2 * ks, idesc, acc);
+                } else {
+                  ptx::umma_bf16_ss(d_tmem, a_desc + 2 * ks, b_desc + 2 * ks, idesc, acc);
+                }
+              }
+            } else {
+#pragma unroll
+              for (uint32_t ks = 0; ks < kBlockK / 16; ++ks) {
+                // 32 FP8 = the same 32 bytes.
+                const uint32_t acc = (kb | ks) != 0 ? 1u : 0u;
+                if constexpr (PAIR) {
+                  ptx::umma_e4m3_ss_pair(d_tmem, a_desc + 2 * ks, b_desc + 2 * ks, idesc_fp8,
+                                         acc);
+                } else {
+                  ptx::umma_e4m3_ss(d_tmem, a_desc + 2 * ks, b_desc + 2 * ks, idesc_fp8, acc);
+                }
               }
             }
             // The stage is reusable (in both CTAs) once these MMAs retire.

@@ -47,12 +47,12 @@ struct DeviceStatus {
 };
 
 struct GemmParams {
-  const CUtensorMap* tmap_a;  // [experts] A_e as {k, M_e}, box {64, a_box_bytes / 128}
-  const CUtensorMap* tmap_b;  // [experts] B_e as {k, n},   box {64, TILE_N / cta_group}
+  const CUtensorMap* tmap_a;  // [experts] A_e as {k, M_e}, box {128 B, a_box_bytes / 128}
+  const CUtensorMap* tmap_b;  // [experts] B_e as {k, n},   box {128 B, TILE_N / cta_group}
   const CUtensorMap* tmap_d;  // [experts] D_e as {n, M_e}, box {64, 32} BF16 / {32, 32} FP32
   const bmoe_tile* tiles;     // device worklist
   uint32_t tile_count;
-  uint32_t k_blocks;          // ceil(k / 64)
+  uint32_t k_blocks;          // ceil(k bytes of a row / 128)
   uint32_t sched_mode;        // SchedMode
   uint32_t claim_size;        // queue: tiles per claim in the main part
   uint32_t main_end;          // queue: [0, main_end) chunked, [main_end, T) singly
@@ -116,6 +116,11 @@ struct GemmParams {
   // about 64 bytes per cycle, zero-filled rows included, and that - not HBM or the tensor
   // pipe - bounds a one-wave launch over a small-M problem.
   uint32_t a_box_bytes;
+  // Operand type: 0 = BF16 (k-block = 64 elements, kind::f16), 1 = FP8 E4M3 (k-block =
+  // 128 elements, kind::f8f6f4). A k-block is 128 bytes of a row either way and one MMA
+  // instruction covers 32 of them, so the shared-memory layout, the descriptors and the
+  // pipeline are the same; only the tensor maps, k_blocks and the instruction differ.
+  uint32_t fp8;
 };
 
 // Words per CTA of GemmParams::trace (SM cycles):

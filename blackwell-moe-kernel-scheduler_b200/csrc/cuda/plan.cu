@@ -47,21 +47,26 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-// Row-major matrix [rows, cols] of BF16 (or FP32) viewed as a 2-D tensor
-// {cols, rows} with a SWIZZLE_128B box of 128 bytes (64 BF16 / 32 FP32 columns)
-// x box_rows rows.
+// Element type of a matrix a tensor map describes.
+enum class Elem : uint32_t { kBf16, kF32, kByte };
+
+// Row-major matrix [rows, cols] viewed as a 2-D tensor {cols, rows} with a SWIZZLE_128B
+// box of 128 bytes (64 BF16 / 32 FP32 / 128 one-byte columns) x box_rows rows.
 bool encode_matrix(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
-                   uint32_t box_rows, bool fp32) {
+                   uint32_t box_rows, Elem type) {
   EncodeTiledFn encode = encode_tiled_fn();
   if (encode == nullptr) return false;
-  const uint32_t elem = fp32 ? 4u : 2u;
+  const uint32_t elem = type == Elem::kF32 ? 4u : (type == Elem::kBf16 ? 2u : 1u);
+  const CUtensorMapDataType kind =
+      type == Elem::kF32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                         : (type == Elem::kBf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                : CU_TENSOR_MAP_DATA_TYPE_UINT8);
   const cuuint64_t dims[2] = {cols, rows};
   const cuuint64_t strides[1] = {cols * elem};
   const cuuint32_t box[2] = {128u / elem, box_rows};
   const cuuint32_t elem_strides[2] = {1, 1};
   const CUresult rc = encode(
-      map, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
-      const_cast<void*>(base), dims, strides,
+      map, kind, 2, const_cast<void*>(base), dims, strides,
       box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return rc == CUDA_SUCCESS;
@@ -133,7 +138,7 @@ struct bmoe_plan {
   // What the B descriptors in the staging area were encoded for (reused while the
   // expert's weight pointer, the shape and the box do not change).
   std::vector<const void*> b_encoded_for;
-  uint32_t b_key_n = 0, b_key_k = 0, b_key_box = 0, b_key_experts = 0;
+  uint32_t b_key_n = 0, b_key_k = 0, b_key_box = 0, b_key_experts = 0, b_key_type = 0;
   bool needs_push = false;   // results_pushed: run() only after set_push
 
   bmoe::GemmParams params{};
@@ -265,7 +270,11 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
   }
   if (packed && (misaligned16(a.packed_a) || a.packed_rows == 0)) return BMOE_INVALID_ARGUMENT;
   if (pushed && a.output_f32 != 0) return BMOE_INVALID_ARGUMENT;
-  if (a.data_type != 0) return BMOE_UNSUPPORTED_DATA_TYPE;
+  if (a.data_type > 1) return BMOE_UNSUPPORTED_DATA_TYPE;
+  // FP8 E4M3 operands: a row is k bytes, and a tensor map wants row strides of 16 bytes
+  const bool fp8 = a.data_type == 1;
+  if (fp8 && a.k % 16 != 0) return BMOE_INVALID_ARGUMENT;
+  const Elem operand = fp8 ? Elem::kByte : Elem::kBf16;
   if (a.scheduler > BMOE_SCHED_CLC) return BMOE_UNSUPPORTED_SCHEDULER;
   if (a.experts > BMOE_WORKLIST_MAX_EXPERTS) return BMOE_INVALID_ARGUMENT;
   if (a.tile_n != 0 && a.tile_n != 64 && a.tile_n != 128 && a.tile_n != 256) {
@@ -417,13 +426,14 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
   const uint32_t b_box = tile_n / cta_group;
   const bool b_cache_valid = !staging_moved && plan->b_key_experts == a.experts &&
                              plan->b_key_n == a.n && plan->b_key_k == a.k &&
-                             plan->b_key_box == b_box &&
+                             plan->b_key_box == b_box && plan->b_key_type == a.data_type &&
                              plan->b_encoded_for.size() == a.experts;
   if (!b_cache_valid) plan->b_encoded_for.assign(a.experts, nullptr);
   plan->b_key_experts = a.experts;
   plan->b_key_n = a.n;
   plan->b_key_k = a.k;
   plan->b_key_box = b_box;
+  plan->b_key_type = a.data_type;
   // Rows of the A box: 128, or fewer when no expert has that many rows (single-CTA tiles
   // only; see GemmParams::a_box_bytes).
   uint32_t a_box_rows = 128;
@@ -434,7 +444,7 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
     }
     if (most < 128) a_box_rows = most < 8 ? 8u : (most + 7u) / 8u * 8u;
   }
-  if (packed && !encode_matrix(&maps_a[0], a.packed_a, a.packed_rows, a.k, a_box_rows, false)) {
+  if (packed && !encode_matrix(&maps_a[0], a.packed_a, a.packed_rows, a.k, a_box_rows, operand)) {
     return BMOE_CUDA_ERROR;
   }
   for (uint32_t e = 0; e < a.experts; ++e) {
@@ -446,14 +456,15 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
       plan->b_encoded_for[e] = nullptr;
       continue;
     }
-    if (!packed && !encode_matrix(&maps_a[e], a.a[e], rows, a.k, a_box_rows, false)) {
+    if (!packed && !encode_matrix(&maps_a[e], a.a[e], rows, a.k, a_box_rows, operand)) {
       return BMOE_CUDA_ERROR;
     }
     if (plan->b_encoded_for[e] != a.b[e]) {
-      if (!encode_matrix(&maps_b[e], a.b[e], a.n, a.k, b_box, false)) return BMOE_CUDA_ERROR;
+      if (!encode_matrix(&maps_b[e], a.b[e], a.n, a.k, b_box, operand)) return BMOE_CUDA_ERROR;
       plan->b_encoded_for[e] = a.b[e];
     }
-    if (!pushed && !encode_matrix(&maps_d[e], a.d[e], rows, a.n, 32, out_f32)) {
+    if (!pushed && !encode_matrix(&maps_d[e], a.d[e], rows, a.n, 32,
+                                  out_f32 ? Elem::kF32 : Elem::kBf16)) {
       return BMOE_CUDA_ERROR;
     }
   }
@@ -486,7 +497,8 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
   p.tmap_d = dev_maps + 2 * static_cast<size_t>(a.experts);
   p.tiles = static_cast<const bmoe_tile*>(plan->worklist.ptr);
   p.tile_count = tiles;
-  p.k_blocks = (a.k + 63) / 64;
+  p.k_blocks = fp8 ? (a.k + 127) / 128 : (a.k + 63) / 64;   // 128 bytes of a row each
+  p.fp8 = fp8 ? 1u : 0u;
   p.sched_mode = policy.sched_mode;
   p.claim_size = policy.claim_size;
   p.main_end = main_end;

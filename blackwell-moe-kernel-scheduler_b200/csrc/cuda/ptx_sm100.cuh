@@ -292,6 +292,27 @@ __device__ __forceinline__ void umma_bf16_ss(uint32_t d_tmem, uint64_t a_desc,
       : "memory");
 }
 
+// Instruction descriptor for kind::f8f6f4 with both operands FP8 E4M3 (format code 0),
+// FP32 accumulation; the other fields as for kind::f16. One instruction covers K = 32
+// elements (the same 32 bytes of a swizzle row as 16 BF16).
+__host__ __device__ constexpr uint32_t make_e4m3_idesc(uint32_t m, uint32_t n) {
+  return (1u << 4) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+// D[tmem] (+)= A[smem] * B[smem]^T for one K=32 slice of FP8 E4M3 operands.
+__device__ __forceinline__ void umma_e4m3_ss(uint32_t d_tmem, uint64_t a_desc,
+                                             uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+      "}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // Arrives on `bar` once all tcgen05.mma issued so far by this thread finished.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile(
@@ -440,6 +461,20 @@ __device__ __forceinline__ void umma_bf16_ss_pair(uint32_t d_tmem, uint64_t a_de
       ".reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// The same for FP8 E4M3 operands (K = 32 per instruction).
+__device__ __forceinline__ void umma_e4m3_ss_pair(uint32_t d_tmem, uint64_t a_desc,
+                                                  uint64_t b_desc, uint32_t idesc,
+                                                  uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
       "}" ::"r"(d_tmem),
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");

@@ -61,6 +61,26 @@ Bf16GroupedGemmPlan& Bf16GroupedGemmPlan::operator=(
 }
 
 KernelStatus Bf16GroupedGemmPlan::initialize(const GroupedGemmArguments& args) {
+  // The BF16 plan takes BF16 only, as the reference's does (after its argument checks:
+  // cutlass_baseline.cu:206-213). The engine checks arguments first, then the type.
+  if (args.data_type != DataType::kBf16) {
+    GroupedGemmArguments probe = args;
+    probe.data_type = static_cast<DataType>(0x7fffffff);
+    return initialize_typed(probe);
+  }
+  return initialize_typed(args);
+}
+
+KernelStatus Fp8E4m3GroupedGemmPlan::initialize(const GroupedGemmArguments& args) {
+  if (args.data_type != DataType::kFp8E4M3) {
+    GroupedGemmArguments probe = args;
+    probe.data_type = static_cast<DataType>(0x7fffffff);
+    return plan_.initialize_typed(probe);
+  }
+  return plan_.initialize_typed(args);
+}
+
+KernelStatus Bf16GroupedGemmPlan::initialize_typed(const GroupedGemmArguments& args) {
   if (impl_ == nullptr) impl_ = new Impl;
   if (impl_->handle == nullptr) impl_->handle = bmoe_plan_create();
   if (impl_->handle == nullptr) return KernelStatus::kCudaError;
@@ -122,7 +142,8 @@ void* Bf16GroupedGemmPlan::native_handle() const {
 }
 
 KernelStatus launch_grouped_gemm_baseline(const GroupedGemmArguments& args) {
-  const bmoe_gemm_args c = to_c_args(args);
+  bmoe_gemm_args c = to_c_args(args);
+  if (args.data_type != DataType::kBf16) c.data_type = 0x7fffffffu;  // BF16 only, as above
   return static_cast<KernelStatus>(bmoe_grouped_gemm(&c));
 }
 

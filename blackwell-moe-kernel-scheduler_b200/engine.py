@@ -136,8 +136,10 @@ class GroupedGemmPlan:
 
     def initialize_packed(self, a, w, d, tokens_per_expert: Sequence[int], *,
                           single_a_map: bool = False, **options) -> int:
-        """Packed form: ``a`` [sum M, k], ``w`` [E, n, k], ``d`` [sum M, n] CUDA BF16
-        tensors, rows of expert 0 first. Row offsets are the exclusive prefix sum
+        """Packed form: ``a`` [sum M, k], ``w`` [E, n, k], ``d`` [sum M, n] CUDA
+        tensors, rows of expert 0 first; ``a`` and ``w`` BF16, or both one byte per element
+        (FP8 E4M3 bit patterns; k then a multiple of 16), ``d`` BF16 (FP32 with
+        ``output_f32``). Row offsets are the exclusive prefix sum
         of the counts; every expert's slice starts on a 16-byte boundary because
         k and n are multiples of 8. ``single_a_map``: one tensor map over the whole of
         ``a`` instead of one per expert (cheaper to re-plan; tiles at an expert's ragged
@@ -157,8 +159,14 @@ class GroupedGemmPlan:
         if int(a.shape[0]) < total or int(d.shape[0]) < total:
             return _capi.INVALID_ARGUMENT
         first_row = (np.cumsum(counts) - counts).astype(np.uint64)
-        a_ptrs = np.uint64(a.data_ptr()) + first_row * np.uint64(k * 2)
-        b_ptrs = np.uint64(w.data_ptr()) + np.arange(experts, dtype=np.uint64) * np.uint64(n * k * 2)
+        elem = int(a.element_size())
+        if elem != int(w.element_size()) or elem not in (1, 2):
+            return _capi.INVALID_ARGUMENT
+        if elem == 1:
+            options["data_type"] = 1          # FP8 E4M3 bytes (torch.float8_e4m3fn or uint8)
+        a_ptrs = np.uint64(a.data_ptr()) + first_row * np.uint64(k * elem)
+        b_ptrs = (np.uint64(w.data_ptr()) +
+                  np.arange(experts, dtype=np.uint64) * np.uint64(n * k * elem))
         d_ptrs = np.uint64(d.data_ptr()) + first_row * np.uint64(n * d_elem)
         self._keep = (a, w, d)
         if single_a_map:

@@ -120,8 +120,28 @@ class Bf16GroupedGemmPlan {
                                std::uint64_t y_rows_cap);
 
  private:
+  friend class Fp8E4m3GroupedGemmPlan;
+  KernelStatus initialize_typed(const GroupedGemmArguments& args);
   struct Impl;
   Impl* impl_ = nullptr;
+};
+
+// Extension: the same plan over FP8 E4M3 operands (one byte per element, no scales):
+//   D_e[M_e, n] = float(A_e)[M_e, k] * float(B_e)[n, k]^T    (FP32 accumulate, BF16 out)
+// The reference declares DataType::kFp8E4M3 (grouped_gemm.cuh:10) and rejects it
+// everywhere (baselines/cutlass/cutlass_baseline.cu:211-213); Bf16GroupedGemmPlan keeps
+// that behaviour, this class is where the type is accepted. args.data_type must be
+// kFp8E4M3 (anything else: kUnsupportedDataType) and k a multiple of 16.
+class Fp8E4m3GroupedGemmPlan {
+ public:
+  KernelStatus initialize(const GroupedGemmArguments& args);
+  KernelStatus run(void* stream = nullptr) { return plan_.run(stream); }
+  GroupedGemmPlanStats stats() const { return plan_.stats(); }
+  KernelStatus poll() { return plan_.poll(); }
+  void* native_handle() const { return plan_.native_handle(); }
+
+ private:
+  Bf16GroupedGemmPlan plan_;
 };
 
 // One-shot convenience path (plan, initialize, run). Benchmarks reuse a plan.

@@ -318,7 +318,12 @@ typedef struct bmoe_gemm_args {
   uint32_t experts;
   uint32_t n;
   uint32_t k;
-  uint32_t data_type; /* 0 = BF16 (only supported), 1 = FP8 E4M3 */
+  uint32_t data_type; /* 0 = BF16; 1 = FP8 E4M3: a[] and b[] hold one byte per element
+                         (no scales), FP32 accumulation, D as for BF16; k must then be a
+                         multiple of 16. The reference declares the type and rejects it
+                         (grouped_gemm.cuh:10, cutlass_baseline.cu:211-213); so do the
+                         C++ Bf16GroupedGemmPlan and the one-shot launcher. Other values:
+                         BMOE_UNSUPPORTED_DATA_TYPE. */
   uint32_t scheduler; /* bmoe_scheduler */
   uint32_t claim_size;
   uint32_t hybrid_tail_tiles;

@@ -663,5 +663,57 @@ ORC_EXPORT int orc_max_threads(void) {
 #endif
 }
 
+/* ------------------------------------------------------------------------ */
+/* FP8 E4M3 operands                                                         */
+/* ------------------------------------------------------------------------ */
+/* The reference declares DataType::kFp8E4M3 (include/blackwell_moe/kernels/
+ * grouped_gemm.cuh:10) and implements nothing for it, so there is nothing of the
+ * reference's to follow here: these state the OCP 8-bit floating point format E4M3
+ * (1 sign, 4 exponent bits with bias 7, 3 mantissa bits; no infinities, S.1111.111 is
+ * NaN, largest finite value 448) and the engine's definition of the FP8 grouped GEMM:
+ * every operand byte decoded exactly, then the BF16 contract's loop. Every E4M3 value is
+ * exactly representable in BF16, so decoding to BF16 bit patterns and calling
+ * orc_grouped_gemm IS the FP8 oracle. */
+static inline float e4m3_to_f32(uint8_t v) {
+  const uint32_t sign = v >> 7, exponent = (v >> 3) & 15u, mantissa = v & 7u;
+  float magnitude;
+  if (exponent == 15u && mantissa == 7u) {
+    magnitude = NAN;
+  } else if (exponent == 0u) {
+    magnitude = ldexpf((float)mantissa, -9);             /* subnormal: m/8 * 2^-6 */
+  } else {
+    magnitude = ldexpf((float)(8u + mantissa), (int)exponent - 10);   /* (1 + m/8) * 2^(e-7) */
+  }
+  return sign ? -magnitude : magnitude;
+}
+
+ORC_EXPORT void orc_e4m3_to_bf16(const uint8_t* src, uint64_t count, uint16_t* dst) {
+  for (uint64_t i = 0; i < count; ++i) dst[i] = f32_to_bf16(e4m3_to_f32(src[i]));
+}
+
+ORC_EXPORT float orc_e4m3_to_f32(uint8_t v) { return e4m3_to_f32(v); }
+
+/* Round to nearest, ties to even, saturating to +-448 (NaN stays NaN). */
+ORC_EXPORT uint8_t orc_f32_to_e4m3(float f) {
+  uint32_t bits;
+  memcpy(&bits, &f, 4);
+  const uint8_t sign = (uint8_t)((bits >> 24) & 0x80u);
+  const float a = fabsf(f);
+  if (a != a) return (uint8_t)(sign | 0x7fu);
+  if (a >= 448.0f) return (uint8_t)(sign | 0x7eu);
+  if (a < ldexpf(1.0f, -6)) {
+    /* subnormal range: multiples of 2^-9 */
+    const float q = nearbyintf(ldexpf(a, 9));            /* 0 .. 8, ties to even */
+    return (uint8_t)(sign | (uint8_t)q);                 /* 8 = smallest normal, 0x08 */
+  }
+  int e;
+  const float frac = frexpf(a, &e);                      /* a = frac * 2^e, frac in [0.5, 1) */
+  float q = nearbyintf(ldexpf(frac, 4));                 /* 8 .. 16 */
+  if (q == 16.0f) { q = 8.0f; ++e; }
+  const uint32_t exponent = (uint32_t)(e - 1 + 7);
+  const uint32_t code = (exponent << 3) | ((uint32_t)q - 8u);
+  return (uint8_t)(sign | (code > 0x7eu ? 0x7eu : code));
+}
+
 ORC_EXPORT uint16_t orc_f32_to_bf16(float f) { return f32_to_bf16(f); }
 ORC_EXPORT float orc_bf16_to_f32(uint16_t h) { return bf16_to_f32(h); }

@@ -6,8 +6,10 @@
 //   pair     tests/test_sm100_2sm_correctness.cu:55-128     256 x 128 x 64
 //   direct   tests/test_direct_cute_correctness.cu:55-126   128 x 256 x 64, FP32 out
 //   probe    tests/test_scheduler_probe.cu:100-128          37 tiles, 8 CTAs
+// plus one case of the FP8 E4M3 plan, which the reference does not have.
 // Prints "SKIP" and exits 0 on a device that is not compute capability 10.0.
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime_api.h>
 
 #include <cmath>
@@ -128,6 +130,84 @@ void grouped_kat() {
   for (uint32_t e = 0; e < 4; ++e) { delete da[e]; delete db[e]; delete dd[e]; }
 }
 
+// FP8 E4M3 plan (an extension: the reference only declares the type). Operands are
+// multiples of 1/8 of magnitude <= 5/8, which E4M3 holds exactly; every product is a
+// multiple of 1/64 and the sums of k = 160 of them are exact in FP32, so the expected
+// output is the exact sum rounded once to BF16 and the comparison is bitwise.
+void fp8_kat() {
+  const std::vector<uint32_t> tokens{7, 0, 13, 131};
+  const uint32_t n = 40, k = 160;
+  auto fill8 = [](size_t count, int mul, int add, int mod, int off) {
+    std::vector<__nv_fp8_e4m3> v(count);
+    for (size_t i = 0; i < count; ++i) {
+      v[i] = __nv_fp8_e4m3(static_cast<float>(static_cast<int>((i * mul + add) % mod) - off) / 8.0f);
+    }
+    return v;
+  };
+  std::vector<std::vector<__nv_fp8_e4m3>> ha(4), hb(4);
+  std::vector<Dev<__nv_fp8_e4m3>*> da(4, nullptr), db(4, nullptr);
+  std::vector<Dev<__nv_bfloat16>*> dd(4, nullptr);
+  std::vector<const void*> pa(4, nullptr), pb(4, nullptr);
+  std::vector<void*> pd(4, nullptr);
+  for (uint32_t e = 0; e < 4; ++e) {
+    if (tokens[e] == 0) continue;
+    ha[e] = fill8(static_cast<size_t>(tokens[e]) * k, 1, 3 * e, 11, 5);
+    hb[e] = fill8(static_cast<size_t>(n) * k, 3, e, 9, 4);
+    da[e] = new Dev<__nv_fp8_e4m3>(ha[e].size());
+    db[e] = new Dev<__nv_fp8_e4m3>(hb[e].size());
+    dd[e] = new Dev<__nv_bfloat16>(static_cast<size_t>(tokens[e]) * n);
+    da[e]->upload(ha[e]);
+    db[e]->upload(hb[e]);
+    pa[e] = da[e]->p; pb[e] = db[e]->p; pd[e] = dd[e]->p;
+  }
+  GroupedGemmArguments args;
+  args.a = pa.data(); args.b = pb.data(); args.d = pd.data();
+  args.tokens_per_expert = tokens.data();
+  args.experts = 4; args.n = n; args.k = k;
+  args.data_type = DataType::kFp8E4M3;
+  for (SchedulerKind policy : {SchedulerKind::kExpertOrder, SchedulerKind::kDynamicQueue,
+                               SchedulerKind::kClc}) {
+    for (uint32_t group : {1u, 2u}) {
+      args.scheduler = policy;
+      args.cta_group = group;
+      for (uint32_t e = 0; e < 4; ++e) {
+        if (tokens[e] != 0) {
+          cuda_ok(cudaMemset(dd[e]->p, 0xff, static_cast<size_t>(tokens[e]) * n * 2), "memset");
+        }
+      }
+      Fp8E4m3GroupedGemmPlan plan;
+      KernelStatus st = plan.initialize(args);
+      require(st == KernelStatus::kSuccess, std::string("FP8: ") + kernel_status_string(st));
+      require(plan.run() == KernelStatus::kSuccess, "FP8 run");
+      require(plan.poll() == KernelStatus::kSuccess, "FP8 device status");
+      for (uint32_t e = 0; e < 4; ++e) {
+        if (tokens[e] == 0) continue;
+        const auto out = dd[e]->download(static_cast<size_t>(tokens[e]) * n);
+        for (uint32_t r = 0; r < tokens[e]; ++r) {
+          for (uint32_t c = 0; c < n; ++c) {
+            float acc = 0.0f;
+            for (uint32_t i = 0; i < k; ++i) {
+              acc += static_cast<float>(ha[e][static_cast<size_t>(r) * k + i]) *
+                     static_cast<float>(hb[e][static_cast<size_t>(c) * k + i]);
+            }
+            const __nv_bfloat16 want = __float2bfloat16(acc);
+            const __nv_bfloat16 got = out[r * n + c];
+            require(__bfloat162float(got) == __bfloat162float(want),
+                    "FP8 grouped GEMM differs from the exact result");
+          }
+        }
+      }
+    }
+  }
+  Fp8E4m3GroupedGemmPlan plan;
+  GroupedGemmArguments bad = args;
+  bad.data_type = DataType::kBf16;
+  require(plan.initialize(bad) == KernelStatus::kUnsupportedDataType, "FP8 plan takes FP8 only");
+  bad = args; bad.k = 40;
+  require(plan.initialize(bad) == KernelStatus::kInvalidArgument, "k % 16 must be rejected");
+  for (uint32_t e = 0; e < 4; ++e) { delete da[e]; delete db[e]; delete dd[e]; }
+}
+
 template <class Plan>
 void dense_kat(uint32_t m, uint32_t n, uint32_t k, int a_mod, int a_off, int b_mul, int b_mod,
                int b_off, const char* what) {
@@ -231,6 +311,7 @@ int main() {
       return 0;
     }
     grouped_kat();
+    fp8_kat();
     dense_kat<Sm100DenseGemmPlan>(128, 128, 64, 9, 4, 3, 11, 5, "1-CTA dense plan");
     dense_kat<Sm100TwoSmGemmPlan>(256, 128, 64, 7, 3, 5, 13, 6, "CTA-pair dense plan");
     dense_kat<Sm100DenseGemmPlan>(1000, 520, 264, 9, 4, 3, 11, 5, "1-CTA dense plan, ragged");

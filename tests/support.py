@@ -121,6 +121,20 @@ class Oracle:
         assert rc == 0
         return out
 
+    def e4m3_to_bf16(self, codes):
+        """FP8 E4M3 bit patterns (uint8, any shape) -> the same values as BF16 bit patterns
+        (exact: every E4M3 value is a BF16 value)."""
+        codes = np.ascontiguousarray(codes, dtype=np.uint8)
+        out = np.zeros(codes.shape, dtype=np.uint16)
+        self.lib.orc_e4m3_to_bf16(ptr(codes), C.c_uint64(codes.size), ptr(out))
+        return out
+
+    def f32_to_e4m3(self, values):
+        self.lib.orc_f32_to_e4m3.restype = C.c_uint8
+        flat = np.ascontiguousarray(values, dtype=np.float32).ravel()
+        return np.array([self.lib.orc_f32_to_e4m3(C.c_float(float(v))) for v in flat],
+                        dtype=np.uint8).reshape(np.shape(values))
+
     def grouped_gemm(self, a_bits, w_bits, counts, n, k, *, want_f32=False, want_f64=False,
                      row_stride=1, row_phase=0, threads=0):
         """a_bits [sum M, k], w_bits [E, n, k] uint16 -> dict of outputs."""

@@ -60,7 +60,10 @@ def test_plan_rejects_bad_arguments_without_a_gpu(engine):
         assert plan.initialize(ok_ptr, ok_ptr, ok_ptr, counts, 32, 20) == cap.INVALID_ARGUMENT
         assert plan.initialize(ok_ptr, ok_ptr, ok_ptr, counts, 0, 32) == cap.INVALID_ARGUMENT
         assert plan.initialize(ok_ptr, ok_ptr, ok_ptr, counts, 32, 32,
-                               data_type=1) == cap.UNSUPPORTED_DATA_TYPE
+                               data_type=2) == cap.UNSUPPORTED_DATA_TYPE
+        # FP8 E4M3 (type 1, an engine extension): rows of k bytes need k % 16 == 0
+        assert plan.initialize(ok_ptr, ok_ptr, ok_ptr, counts, 32, 24,
+                               data_type=1) == cap.INVALID_ARGUMENT
         assert plan.initialize(ok_ptr, ok_ptr, ok_ptr, counts, 32, 32,
                                scheduler=17) == cap.UNSUPPORTED_SCHEDULER
         assert plan.run() == cap.INVALID_ARGUMENT  # never initialised successfully

@@ -205,3 +205,34 @@ def test_combine_topk_definition(oracle):
     assert not got[5].any()
     ones = oracle.combine_topk(src, rows, None)
     assert np.array_equal(ones, oracle.combine_topk(src, rows, np.ones_like(weights)))
+
+
+def test_e4m3_codec_equals_torch_float8(oracle):
+    """The oracle's FP8 E4M3 decode and encode against an independent implementation,
+    torch.float8_e4m3fn on the CPU: all 256 codes decode to the same value (the two NaN
+    codes to NaN), every decoded value is a BF16 value, and round-to-nearest-even encoding
+    of values inside the finite range (normals, subnormals, exact ties, +-0) gives the same
+    code. Beyond +-448 the oracle saturates to the largest finite code."""
+    import torch
+
+    codes = np.arange(256, dtype=np.uint8)
+    want = torch.from_numpy(codes.copy()).view(torch.float8_e4m3fn).to(torch.float32).numpy()
+    as_bf16 = support.bf16_bits_to_f32(oracle.e4m3_to_bf16(codes))
+    nan = np.isnan(want)
+    assert list(np.flatnonzero(nan)) == [0x7F, 0xFF]
+    assert np.array_equal(np.isnan(as_bf16), nan)
+    assert np.array_equal(as_bf16[~nan].view(np.uint32), want[~nan].view(np.uint32))
+
+    rng = np.random.default_rng(5)
+    finite = want[~nan]
+    ties = (np.sort(finite)[:-1] + np.sort(finite)[1:]) / 2.0          # exact midpoints
+    values = np.concatenate([
+        finite, ties.astype(np.float32), rng.normal(0, 1, 4000).astype(np.float32),
+        rng.normal(0, 0.01, 2000).astype(np.float32), rng.uniform(-448, 448, 2000).astype(
+            np.float32), np.array([0.0, -0.0, 2.0 ** -10, -(2.0 ** -10), 448.0, -448.0],
+                                  dtype=np.float32)])
+    mine = oracle.f32_to_e4m3(values)
+    theirs = torch.from_numpy(values).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    assert np.array_equal(mine, theirs)
+    assert list(oracle.f32_to_e4m3(np.array([1e6, -1e6, 460.0], dtype=np.float32))) == [
+        0x7E, 0xFE, 0x7E]
