@@ -7,10 +7,14 @@ built, and nothing here falls back to a CPU implementation.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
 PKG_DIR = Path(__file__).resolve().parent
-LIB_PATH = PKG_DIR / "lib" / "libbmoe_b200.so"
+# BMOE_CHECKS=1 in the environment selects the bounds-checked build of the same sources
+# (python -m ... _build --checks, or __graft_entry__.build()).
+LIB_PATH = PKG_DIR / "lib" / ("libbmoe_b200_checks.so" if os.environ.get("BMOE_CHECKS") == "1"
+                              else "libbmoe_b200.so")
 
 # ---- status codes / enums (bmoe_b200.h) ----
 OK = 0

@@ -250,6 +250,8 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   }
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = misc->tmem_base;
+  // time line of the CTA for the trace (cycles since the kernel's first instruction)
+  const uint64_t stamp_setup = tracing ? static_cast<uint64_t>(clock64() - kernel_t0) : 0;
 
   // ---------------------------------------------------------- scheduler --
   if (warp == 2) {
@@ -325,8 +327,41 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         const uint32_t round = (published / kSchedSlots) & 1u;
         bmoe_tile t{};
         if (tile_index != kSentinel) {
+#ifdef BMOE_CHECKS
+          if (static_cast<uint32_t>(tile_index) < tile_count)   // else: reported below, not read
+#endif
           t = static_cast<uint32_t>(tile_index) == first_index ? first_rec : p.tiles[tile_index];
         }
+#ifdef BMOE_CHECKS
+        if (tile_index != kSentinel) {
+          uint32_t failed = 0, value = 0;
+          const uint32_t tile_rows = kCtaRows * Cfg::kGroup;
+          if (static_cast<uint32_t>(tile_index) >= tile_count) {
+            failed = kCheckTileIndex; value = static_cast<uint32_t>(tile_index);
+          } else if (t.expert_id >= p.check_experts) {
+            failed = kCheckExpert; value = t.expert_id;
+          } else if (t.valid_n == 0 || t.valid_n > TILE_N ||
+                     static_cast<uint64_t>(t.tile_n) * TILE_N + t.valid_n > p.check_n) {
+            failed = kCheckColumns; value = t.tile_n;
+          } else if (t.valid_m == 0 || t.valid_m > tile_rows) {
+            failed = kCheckRows; value = t.valid_m;
+          } else if (p.a_row_offsets != nullptr &&
+                     p.a_row_offsets[t.expert_id] + static_cast<uint64_t>(t.tile_m) * tile_rows +
+                             t.valid_m > p.check_a_rows) {
+            failed = kCheckPackedRows; value = t.tile_m;
+          } else if (static_cast<uint64_t>(p.k_blocks) * 128u < p.check_k_bytes ||
+                     static_cast<uint64_t>(p.k_blocks - 1) * 128u >= p.check_k_bytes) {
+            failed = kCheckKBlocks; value = p.k_blocks;
+          } else if (2 * TILE_N > Cfg::kTmemCols) {
+            failed = kCheckTmemColumns; value = 2 * TILE_N;
+          }
+          if (failed != 0) {
+            *abort_word = 1;
+            report(p, kSiteCheck, 0, static_cast<uint32_t>(tile_index), failed, value);
+            return false;
+          }
+        }
+#endif
         if (p.gate_flags != nullptr && tile_index != kSentinel && !gate(t.expert_id)) {
           return false;
         }
@@ -532,6 +567,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       uint32_t stage = 0, stage_round = 0;
       uint32_t buf = 0, buf_round = 0;
       uint64_t t_info = 0, t_accum = 0, t_operands = 0, t_issue = 0;
+      uint64_t stamp_first_operands = 0, stamp_last_issue = 0;
       while (true) {
         const uint32_t slot = reads % kSchedSlots;
         const uint32_t round = (reads / kSchedSlots) & 1u;
@@ -562,6 +598,9 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             break;
           }
           ptx::tc_fence_after_sync();
+          if (tracing && stamp_first_operands == 0) {
+            stamp_first_operands = static_cast<uint64_t>(clock64() - kernel_t0);
+          }
           const uint64_t a_desc =
               ptx::make_kmajor_sw128_desc(base + Cfg::kOffA + stage * kABytes);
           const uint64_t b_desc =
@@ -609,7 +648,11 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
               }
             }
           }
-          if (tracing) t_issue += static_cast<uint64_t>(clock64() - issue_t0);
+          if (tracing) {
+            const long long now = clock64();
+            t_issue += static_cast<uint64_t>(now - issue_t0);
+            stamp_last_issue = static_cast<uint64_t>(now - kernel_t0);
+          }
           if (++stage == Cfg::kStages) { stage = 0; stage_round ^= 1u; }
         }
         if (!ok) break;
@@ -620,6 +663,9 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         p.trace[blockIdx.x * kTraceWords + 3] = t_accum;
         p.trace[blockIdx.x * kTraceWords + 4] = t_operands;
         p.trace[blockIdx.x * kTraceWords + 10] = t_issue;
+        p.trace[blockIdx.x * kTraceWords + 11] = stamp_setup;
+        p.trace[blockIdx.x * kTraceWords + 12] = stamp_first_operands;
+        p.trace[blockIdx.x * kTraceWords + 13] = stamp_last_issue;
       }
     }
     __syncwarp();
@@ -706,6 +752,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     const uint32_t quad = warp & 3u;  // TMEM lane quadrant this warp may read
     const uint32_t staging = base + Cfg::kOffStaging + quad * 2 * kStoreBytes;
     const uint32_t row_in_tile = cta_rank * kCtaRows + quad * kStoreRows;
+    uint64_t stamp_last_accum = 0;
     uint32_t reads = 0;
     uint32_t buf = 0, buf_round = 0;
     uint32_t sbuf = 0;
@@ -752,6 +799,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         break;
       }
       ptx::tc_fence_after_sync();
+      if (tracing) stamp_last_accum = static_cast<uint64_t>(clock64() - kernel_t0);
 
       const CUtensorMap* const map_d = p.tmap_d + expert;
       if (lane == 0 && expert != last_expert) ptx::tensormap_acquire(map_d);
@@ -859,6 +907,8 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       p.trace[blockIdx.x * kTraceWords + 6] = t_accum;
       p.trace[blockIdx.x * kTraceWords + 7] = t_drain;
       p.trace[blockIdx.x * kTraceWords + 8] = tiles_done;
+      p.trace[blockIdx.x * kTraceWords + 14] = stamp_last_accum;
+      p.trace[blockIdx.x * kTraceWords + 15] = static_cast<uint64_t>(clock64() - kernel_t0);
     }
     __syncwarp();
   }

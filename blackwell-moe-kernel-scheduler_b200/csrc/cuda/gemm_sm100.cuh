@@ -32,6 +32,22 @@ enum DeviceSite : uint32_t {
   kSiteSchedGate = 11,    // scheduler waiting for another rank's rows (stage = group, aux = rank)
   kSiteExpandFlag = 12,   // row expansion waiting for a source's flag (stage = group, aux = rank)
   kSiteSchedExpand = 13,  // scheduler waiting for a group's row expansion (stage = group)
+  kSiteCheck = 14,        // -DBMOE_CHECKS build: a tile record failed a bounds check
+                          // (stage = DeviceCheck, aux = the offending value)
+};
+
+// What a -DBMOE_CHECKS build verifies for every tile record before publishing it to the
+// roles (everything the TMA coordinates, descriptor indices and Tensor Memory columns of the
+// tile derive from). A failure is reported through DeviceStatus and ends the launch through
+// the abort path of the bounded waits; nothing traps.
+enum DeviceCheck : uint32_t {
+  kCheckTileIndex = 1,   // worklist index >= tile total
+  kCheckExpert = 2,      // expert id >= experts (indexes the descriptor arrays)
+  kCheckColumns = 3,     // col0 / valid_n outside [0, n] or wider than the tile
+  kCheckRows = 4,        // valid_m outside [1, tile rows]
+  kCheckPackedRows = 5,  // packed A: rows beyond the buffer
+  kCheckKBlocks = 6,     // k-blocks do not cover k (TMA x coordinate = multiples of 128 B)
+  kCheckTmemColumns = 7, // accumulator buffers exceed the allocated Tensor Memory columns
 };
 
 // Device-side error record; zero-initialised by the host.
@@ -121,6 +137,11 @@ struct GemmParams {
   // instruction covers 32 of them, so the shared-memory layout, the descriptors and the
   // pipeline are the same; only the tensor maps, k_blocks and the instruction differ.
   uint32_t fp8;
+  // Extents for the -DBMOE_CHECKS build (always filled in by the plan, read by that build only).
+  uint32_t check_experts;
+  uint32_t check_n;
+  uint32_t check_k_bytes;     // bytes of an operand row
+  uint64_t check_a_rows;      // rows of the packed A buffer (0 = per-expert A maps)
 };
 
 // Words per CTA of GemmParams::trace (SM cycles):
@@ -130,6 +151,10 @@ struct GemmParams {
 //   6 epilogue waiting for an accumulator 7 epilogue draining (ld, convert, store)
 //   8 tiles run by this CTA               9 kernel cycles of this CTA
 //   10 MMA lane issuing tcgen05.mma / commit
+// and a time line of the CTA, in cycles since its first instruction:
+//   11 set-up done (barriers, Tensor Memory)   12 first operand stage landed
+//   13 last MMA of the last tile issued         14 last accumulator complete
+//   15 epilogue done (stores of the last tile issued and drained)
 constexpr uint32_t kTraceWords = 16;
 
 // Dynamic shared memory / operand stages for a tile width (64, 128 or 256) and CTA

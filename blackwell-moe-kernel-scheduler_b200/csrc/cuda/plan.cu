@@ -499,6 +499,10 @@ int bmoe_plan_initialize(bmoe_plan* plan, const bmoe_gemm_args* args) {
   p.tile_count = tiles;
   p.k_blocks = fp8 ? (a.k + 127) / 128 : (a.k + 63) / 64;   // 128 bytes of a row each
   p.fp8 = fp8 ? 1u : 0u;
+  p.check_experts = a.experts;
+  p.check_n = a.n;
+  p.check_k_bytes = fp8 ? a.k : 2u * a.k;
+  p.check_a_rows = packed ? a.packed_rows : 0;
   p.sched_mode = policy.sched_mode;
   p.claim_size = policy.claim_size;
   p.main_end = main_end;
