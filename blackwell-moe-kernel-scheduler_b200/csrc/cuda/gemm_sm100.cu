@@ -59,7 +59,6 @@ struct Config {
   // the pair), 8 of 24 KiB (128 x 64, the narrow tile that spreads a small-M weight
   // stream over all SMs and keeps 64 KiB of it in flight per SM).
   static constexpr uint32_t kStages = (192u * 1024u) / kCtaStageBytes;
-  static constexpr uint32_t kTxBytes = kCtaStageBytes * kGroup;  // bytes counted on the full barrier
   static constexpr uint32_t kTmemCols = 2 * TILE_N;
   // Offsets from the 1024-byte aligned base of dynamic shared memory.
   static constexpr uint32_t kOffA = 0;
