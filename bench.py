@@ -857,6 +857,67 @@ def run_dense_sweep(args):
                       "sweep": rows}), flush=True)
 
 
+def run_dense_timeline(args):
+    """Where the time of a small dense launch goes: the per-CTA wait accounting and time line
+    (bmoe_plan_set_trace, 16 words per CTA, SM cycles) of one launch after warm-up, median
+    over the CTAs, for the small-M points of the dense sweep and a one-tile problem; beside
+    each the median of 200 event pairs around single launches. One JSON line."""
+    import numpy as np
+    import torch
+
+    import bmoe_b200 as engine
+
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(0)
+    stream = torch.cuda.current_stream()
+    words = ["producer_wait_info", "producer_wait_stage", "mma_wait_info", "mma_wait_accumulator",
+             "mma_wait_operands", "epilogue_wait_info", "epilogue_wait_accumulator",
+             "epilogue_drain", "tiles", "kernel", "mma_issue", "t_setup_done",
+             "t_first_operands", "t_last_mma_issued", "t_last_accumulator", "t_epilogue_done"]
+    gen = torch.Generator(device=dev).manual_seed(1)
+    rows = []
+    for m, n, k in ((16, 128, 64), (128, 7168, 64), (64, 7168, 2048), (128, 7168, 2048),
+                    (256, 7168, 2048)):
+        w = (torch.randn(1, n, k, generator=gen, device=dev) * k ** -0.5).to(torch.bfloat16)
+        a = torch.randn(m, k, generator=gen, device=dev).to(torch.bfloat16)
+        d = torch.zeros(m, n, dtype=torch.bfloat16, device=dev)
+        plan = engine.GroupedGemmPlan()
+        status = plan.initialize_packed(a, w, d, [m], scheduler="expert_order", cta_group=1,
+                                        tile_n=128, stream=stream)
+        if status != 0:
+            raise RuntimeError(engine._capi.status_string(status))
+        for _ in range(20):
+            plan.run(stream)
+        pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                 for _ in range(200)]
+        torch.cuda.synchronize()
+        for e0, e1 in pairs:
+            e0.record(stream)
+            plan.run(stream)
+            e1.record(stream)
+        torch.cuda.synchronize()
+        stats = plan.stats()
+        trace = torch.zeros(stats.threadblock_count, 16, dtype=torch.int64, device=dev)
+        plan.set_trace(trace)
+        plan.run(stream)
+        status, _ = plan.poll()
+        if status != 0:
+            raise RuntimeError(engine._capi.status_string(status))
+        plan.set_trace(None)
+        t = trace.cpu().numpy().astype(np.float64)
+        rows.append({"m": m, "n": n, "k": k, "ctas": stats.threadblock_count,
+                     "tile": [stats.tile_m, stats.tile_n, 64], "k_blocks": (k + 63) // 64,
+                     "event_pair_median_us": percentile([x.elapsed_time(y) for x, y in pairs],
+                                                        0.5) * 1e3,
+                     "cycles_median_over_ctas": {name: float(np.median(t[:, i]))
+                                                 for i, name in enumerate(words)}})
+        plan.close()
+    print(json.dumps({"metric": "CTA time line of small dense launches", "unit": "SM cycles",
+                      "n_gpus": 1, "dtype": "bf16", "data": "synthetic",
+                      "config": {"workload": "dense_timeline_tile128x128"}, "rows": rows}),
+          flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -921,9 +982,14 @@ def main():
     ap.add_argument("--dense-sweep", action="store_true",
                     help="dense M-sweep (N=7168, K=2048): engine dense plans next to the "
                          "reference's own CUTLASS 1-SM kernel")
+    ap.add_argument("--dense-timeline", action="store_true",
+                    help="wait accounting and CTA time line of small dense launches")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
+    if args.dense_timeline:
+        run_dense_timeline(args)
+        return
     if args.sweep:
         run_skew_sweep(args)
         return
