@@ -999,12 +999,17 @@ def main():
     workload = args.workload or (DEFAULT_WORKLOAD if args.gpus == 1 else EP_WORKLOAD)
     spec = WORKLOADS[workload]
     if args.impl == "reference":
+        if args.dtype != "bf16":
+            raise SystemExit("--impl reference times the reference's BF16 contract only")
         run_reference_arm(args, spec, workload)
         return
     single = args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1
     if single and not workload.startswith(("ep_", "profile_ep_")):
         run_single_gpu(args, spec, workload)
     else:
+        if args.dtype != "bf16":
+            raise SystemExit("--dtype fp8 is a single-GPU option: the expert-parallel exchange "
+                             "moves BF16 rows")
         import ep_bench  # the multi-GPU arm, beside this file
 
         ep_bench.run(args, spec, workload)
